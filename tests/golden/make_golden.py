@@ -1,0 +1,157 @@
+"""Generate the golden fixtures in this directory by running the REFERENCE's own modules.
+
+Run where the reference checkout is importable (``TYBOK_REFERENCE`` or ``/root/reference``):
+
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py
+
+Inputs and weights are seeded (``tybok_b200.weights`` + the generators below), so the
+fixtures hold only outputs plus an fp64 checksum of the inputs they belong to.  The
+fixtures pin ``oracle/`` (tests/test_oracle.py) and, through it, the CUDA kernels.
+
+Reference entry points exercised:
+  * ``FP8Linear.from_linear``        tybok/policies/fastwam/models/fp8_linear.py:299-310
+  * ``_dequant_fp8_weight``          tybok/policies/fastwam/models/policy.py:48-58
+  * ``GemmaMLP`` / ``GemmaAttention`` / ``GemmaDecoderLayer``  tybok/policies/pi05/models/layers.py
+  * ``PI05FlowMatching.sample_actions``  tybok/policies/pi05/models/flow_matching.py:761-838
+"""
+
+from __future__ import annotations
+
+import os
+import sys
+
+import torch
+from torch import nn
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+sys.path.insert(0, os.environ.get("TYBOK_REFERENCE", "/root/reference"))
+sys.dont_write_bytecode = True
+
+from tybok_b200.shapes import PI05_TINY  # noqa: E402
+from tybok_b200.weights import quantize_hot_linears, random_pi05_params  # noqa: E402
+
+
+def checksum(*tensors) -> float:
+    return float(sum(t.double().abs().sum() for t in tensors))
+
+
+def tiny_inputs(shape, seed=0, batch=1):
+    """Seeded synthetic request: images in [-1,1], token ids, all-ones masks, zero noise."""
+    g = torch.Generator().manual_seed(seed)
+    images = [torch.rand(batch, 3, shape.vision.image, shape.vision.image, generator=g) * 2 - 1
+              for _ in range(shape.n_cams)]
+    img_masks = [torch.ones(batch, dtype=torch.bool) for _ in range(shape.n_cams)]
+    tokens = torch.randint(0, shape.vocab, (batch, shape.lang_len), generator=g)
+    masks = torch.ones(batch, shape.lang_len, dtype=torch.bool)
+    masks[:, shape.lang_len - 3:] = False  # a padded tail, so the pad mask is exercised
+    noise = torch.zeros(batch, shape.chunk, shape.max_action_dim)
+    return images, img_masks, tokens, masks, noise
+
+
+def linear_case(seed, m, n, k):
+    g = torch.Generator().manual_seed(seed)
+    w = torch.empty(n, k).normal_(0, 0.02, generator=g)
+    x = torch.empty(m, k).normal_(0, 1, generator=g).to(torch.bfloat16)
+    return w, x
+
+
+def main() -> None:
+    from tybok.policies.fastwam.models.fp8_linear import FP8Linear
+    from tybok.policies.fastwam.models.policy import _dequant_fp8_weight
+    from tybok.policies.pi05 import config as ref_config
+    from tybok.policies.pi05.models.flow_matching import PI05FlowMatching
+    from tybok.policies.pi05.models.layers import GemmaMLP
+    from tybok.policies.pi05.models.paligemma_with_expert import PaliGemmaMultiModalProjector
+    from tybok.policies.pi05.models.vision import SiglipVisionTransformer
+
+    out: dict[str, object] = {}
+
+    # ---- a1/a2: quantiser + dequant linear ------------------------------------------
+    for tag, (m, n, k) in {"lin_small": (50, 256, 512), "lin_ragged": (7, 192, 320)}.items():
+        w, x = linear_case(1, m, n, k)
+        lin = nn.Linear(k, n, bias=False)
+        lin.weight.data.copy_(w)
+        q = FP8Linear.from_linear(lin)
+        w8, scale = q.weight.data, q.weight_scale.data
+        y = torch.nn.functional.linear(x, _dequant_fp8_weight(w8, scale))
+        out[tag] = {"in_sum": checksum(w, x), "w8": w8.view(torch.uint8).clone(), "scale": scale.clone(), "y": y}
+
+    # ---- a4: gated MLP on dequantised weights ----------------------------------------
+    g = torch.Generator().manual_seed(2)
+    mlp = GemmaMLP(256, 512)
+    x = torch.empty(1, 50, 256).normal_(0, 1, generator=g).to(torch.bfloat16)
+    ws = {}
+    for name in ("gate_proj", "up_proj", "down_proj"):
+        lin = getattr(mlp, name)
+        w = torch.empty(lin.weight.shape).normal_(0, 0.02, generator=g)
+        src = nn.Linear(w.shape[1], w.shape[0], bias=False)
+        src.weight.data.copy_(w)
+        q = FP8Linear.from_linear(src)
+        lin.weight.data.copy_(_dequant_fp8_weight(q.weight.data, q.weight_scale.data))
+        ws[name] = w
+    with torch.no_grad():
+        out["mlp"] = {"in_sum": checksum(x, *ws.values()), "y": mlp(x)}
+
+    # ---- whole tiny policy -------------------------------------------------------------
+    shape = PI05_TINY
+    ref_config.GEMMA_VARIANTS["tiny_vlm"] = dict(vars(shape.vlm))
+    ref_config.GEMMA_VARIANTS["tiny_expert"] = dict(vars(shape.expert))
+    cfg = ref_config.PI05Config(
+        chunk_size=shape.chunk, n_action_steps=shape.chunk, max_action_dim=shape.max_action_dim,
+        paligemma_variant="tiny_vlm", action_expert_variant="tiny_expert",
+        image_resolution=(shape.vision.image, shape.vision.image),
+        tokenizer_max_length=shape.lang_len, num_steps=shape.steps,
+        min_period=shape.min_period, max_period=shape.max_period,
+    )
+    cfg._image_features = [f"observation.images.cam{i}" for i in range(shape.n_cams)]
+    torch.set_default_dtype(torch.bfloat16)  # as tybok/policies/pi05/engine.py:184-189
+    try:
+        model = PI05FlowMatching(cfg)
+        pg = model.paligemma_with_expert.paligemma.model
+        v = shape.vision
+        # The reference hard-codes the So400m tower and the PaliGemma vocabulary; swap in
+        # smaller instances of the same reference classes so the fixture stays small.
+        pg.vision_tower.vision_model = SiglipVisionTransformer(
+            hidden_size=v.hidden, num_heads=v.heads, num_layers=v.layers,
+            intermediate_size=v.mlp_dim, image_size=v.image, patch_size=v.patch)
+        pg.multi_modal_projector = PaliGemmaMultiModalProjector(v.hidden, shape.vlm.width)
+        pg.language_model.embed_tokens = nn.Embedding(shape.vocab, shape.vlm.width, dtype=torch.bfloat16)
+    finally:
+        torch.set_default_dtype(torch.float32)
+    model.eval()
+
+    params = quantize_hot_linears(random_pi05_params(shape, seed=0), shape)
+    sd = {}
+    for name, t in params.items():
+        if name.endswith(".scale_weight"):
+            continue
+        if t.dtype == torch.float8_e4m3fn:  # the loader's dequant path, policy.py:127-129
+            t = _dequant_fp8_weight(t, params[name[: -len("weight")] + "scale_weight"])
+        sd[name] = t
+    missing, unexpected = model.load_state_dict(sd, strict=False)
+    assert not unexpected, unexpected
+    assert all("position_ids" in m or "inv_freq" in m for m in missing), missing
+
+    images, img_masks, tokens, masks, noise = tiny_inputs(shape)
+    with torch.no_grad():
+        actions = model.sample_actions(images, img_masks, tokens, masks, noise=noise)
+        # intermediates for finer-grained pins
+        embs, pad, att = model.embed_prefix(images, img_masks, tokens, masks)
+    out["pi05_tiny"] = {
+        "in_sum": checksum(*images, tokens, *[t for t in params.values()]),
+        "actions": actions.clone(),
+        "prefix_embs": embs[:, ::37].clone(),
+    }
+    # batch-2 determinism of the eager path (the same oracle serves batched throughput)
+    images2, img_masks2, tokens2, masks2, noise2 = tiny_inputs(shape, seed=3, batch=2)
+    with torch.no_grad():
+        out["pi05_tiny_b2"] = {"actions": model.sample_actions(images2, img_masks2, tokens2, masks2, noise=noise2).clone()}
+
+    path = os.path.join(HERE, "pi05_golden.pt")
+    torch.save(out, path)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,116 @@
+"""Shape descriptions of the policies this package accelerates.
+
+The hot path is shape-generic; these dataclasses only name the configurations
+the parity tests and the benchmark run.  Field names follow the reference's
+``GEMMA_VARIANTS`` table and ``PI05Config`` (tybok/policies/pi05/config.py:15-32,54-90)
+so a checkpoint ``config.json`` maps onto them one to one.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field, replace
+
+
+@dataclass(frozen=True)
+class GemmaSpec:
+    """One Gemma decoder stack (tybok/policies/pi05/config.py:35-50)."""
+
+    width: int
+    depth: int
+    mlp_dim: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+
+
+@dataclass(frozen=True)
+class SiglipSpec:
+    """SigLIP tower geometry (tybok/policies/pi05/models/paligemma_with_expert.py:48-58)."""
+
+    hidden: int = 1152
+    heads: int = 16
+    layers: int = 27
+    mlp_dim: int = 4304
+    image: int = 224
+    patch: int = 14
+
+    @property
+    def tokens(self) -> int:
+        return (self.image // self.patch) ** 2
+
+
+@dataclass(frozen=True)
+class PI05Shape:
+    """A pi0.5-shaped policy: SigLIP -> projector -> VLM prefix -> AdaRMS expert."""
+
+    vlm: GemmaSpec
+    expert: GemmaSpec
+    vision: SiglipSpec = field(default_factory=SiglipSpec)
+    n_cams: int = 2
+    lang_len: int = 32
+    vocab: int = 257152
+    chunk: int = 50
+    steps: int = 10
+    max_action_dim: int = 32
+    action_dim: int = 32
+    min_period: float = 4e-3
+    max_period: float = 4.0
+
+    @property
+    def prefix_len(self) -> int:
+        return self.n_cams * self.vision.tokens + self.lang_len
+
+    def with_(self, **kw) -> "PI05Shape":
+        return replace(self, **kw)
+
+
+GEMMA_2B = GemmaSpec(2048, 18, 16384, 8, 1, 256)
+GEMMA_300M = GemmaSpec(1024, 18, 4096, 8, 1, 256)
+
+#: BASELINE config 2: the pi0.5-shaped policy the headline latency is quoted on.
+PI05_FULL = PI05Shape(vlm=GEMMA_2B, expert=GEMMA_300M)
+
+#: A tiny policy with the same structure (GQA 4:1... kept MQA like pi0.5), used by
+#: CPU parity tests and the smoke run.  Every dimension keeps the alignment the
+#: kernels need (K multiple of 64, head_dim 256 optional -> 64 here).
+PI05_TINY = PI05Shape(
+    vlm=GemmaSpec(256, 2, 512, 4, 1, 64),
+    expert=GemmaSpec(128, 2, 256, 4, 1, 64),
+    vision=SiglipSpec(hidden=128, heads=4, layers=2, mlp_dim=256, image=56, patch=14),
+    n_cams=2,
+    lang_len=16,
+    vocab=512,
+    chunk=10,
+    steps=3,
+)
+
+#: The W8 linear sweep of BASELINE config 1: (N, K) pairs and token counts M.
+W8_SWEEP_NK = ((16384, 2048), (2048, 16384), (2560, 2048), (4096, 1024), (1024, 4096))
+W8_SWEEP_M = (1, 50, 256, 800)
+
+
+@dataclass(frozen=True)
+class DiTShape:
+    """fastWAM-class DiT denoiser of BASELINE config 3
+    (tybok/policies/fastwam/models/dit_block.py:328-400)."""
+
+    hidden: int = 3072
+    heads: int = 24
+    head_dim: int = 128
+    ffn: int = 14336
+    blocks: int = 30
+    video_tokens: int = 4096
+    action_tokens: int = 50
+    steps: int = 4
+    state_dim: int = 14
+    context_len: int = 129
+    text_dim: int = 4096
+
+    @property
+    def seq(self) -> int:
+        return self.video_tokens + self.action_tokens
+
+
+DIT_FULL = DiTShape()
+DIT_TINY = DiTShape(hidden=256, heads=2, head_dim=128, ffn=512, blocks=2, video_tokens=96,
+                    action_tokens=10, steps=2, context_len=17, text_dim=64)
