@@ -1,0 +1,90 @@
+/* tybok_b200 -- C ABI of the B200-native fp8 hot path.
+ *
+ * Every entry point takes plain pointers and sizes (device pointers unless said otherwise),
+ * launches on the CUDA stream it is given (a cudaStream_t passed as void*), allocates
+ * nothing, and returns a status code: 0 on success, a TYBOK_ERR_* value otherwise, with a
+ * message retrievable through tybok_last_error().  Buffers are caller-owned; weights are
+ * referenced in place.  Nothing here falls back to a CPU or library path.
+ *
+ * The interface replaces, for the fp8 FFN/attention path, what the reference binds through
+ * its per-kernel extension modules: raw int64 pointers + stream + caller-owned scratch
+ * (tybok/policies/fastwam/kernels/adit_fused_bindings.cpp:21-30,121-127,163-206), where a
+ * failure is an exception rather than a process exit (kernels/coop_grid.h:20-27).
+ */
+#ifndef TYBOK_B200_H
+#define TYBOK_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TYBOK_OK 0
+#define TYBOK_ERR_ARG 1       /* bad shape, stride or alignment; nothing was launched */
+#define TYBOK_ERR_CUDA 2      /* a CUDA runtime/driver call failed */
+#define TYBOK_ERR_WORKSPACE 3 /* workspace missing or too small */
+#define TYBOK_ERR_ARCH 4      /* the current device is not sm_100 */
+
+/* Epilogues of the W8A16 linear. */
+#define TYBOK_EPI_NONE 0     /* y = bf16(acc*scale + bias) */
+#define TYBOK_EPI_GELU 1     /* y = bf16(gelu_tanh(bf16(acc*scale + bias))) */
+#define TYBOK_EPI_RESIDUAL 2 /* y = bf16(res + bf16(bf16(acc*scale + bias) * bf16(gate))) ; gate optional */
+
+/* Device-side status word values (written by a kernel whose bounded wait ran out). */
+#define TYBOK_DEV_OK 0
+#define TYBOK_DEV_TIMEOUT_PRODUCER 101
+#define TYBOK_DEV_TIMEOUT_MMA 102
+#define TYBOK_DEV_TIMEOUT_CONVERT 103
+#define TYBOK_DEV_TIMEOUT_EPILOGUE 104
+
+int tybok_version(void);
+/* Host pointer to a thread-local, NUL-terminated description of the last failure. */
+const char* tybok_last_error(void);
+/* Number of kernels this library has launched in this process (all threads, all streams). */
+long long tybok_launch_count(void);
+
+/* Bytes of scratch a W8A16 launch of this shape may need (split-K partials + tile counters).
+ * The first TYBOK_COUNTER_BYTES bytes hold arrival counters: zero them once after allocation;
+ * every launch leaves them zero again.  `dual` = 1 for the gated (two-matrix) form. */
+#define TYBOK_COUNTER_BYTES 16384
+size_t tybok_w8a16_workspace_bytes(int M, int N, int K, int dual);
+
+/* W8A16 linear: y[M,N] = epilogue(x[M,K] . (W8[N,K] * scale[N])^T + bias[N]).
+ *   x        bf16, row stride ldx elements (ldx % 8 == 0, pointer 16-byte aligned)
+ *   w8       e4m3 bytes, contiguous [N,K] (K % 16 == 0, pointer 16-byte aligned)
+ *   scale    fp32 [N]; bias bf16 [N] or NULL
+ *   y        bf16, row stride ldy
+ *   epilogue TYBOK_EPI_*; residual bf16 [M,N] stride ldres (EPI_RESIDUAL only)
+ *   gate     NULL, or per-row-group gate [ceil(M/rows_per_gate), N] with row stride ldgate:
+ *            fp32 when gate_is_bf16 == 0 (rounded to bf16 before use), bf16 otherwise
+ *   token_tile, splits  0 = choose automatically; otherwise force the token tile
+ *            (multiple of 16, <= 256) / the split-K factor
+ *   status_word  optional device int; set non-zero if a bounded device wait ran out
+ * Replaces the reference's dequant-then-F.linear path
+ * (tybok/policies/fastwam/models/policy.py:48-58,127-129) and its W8 GEMM body
+ * (tybok/policies/fastwam/kernels/vdit_gemm_core.cu:68, epilogues EPI/RESID). */
+int tybok_w8a16_linear(const void* x, const void* w8, const float* scale, const void* bias, void* y, int M, int N,
+                       int K, int64_t ldx, int64_t ldy, int epilogue, const void* residual, int64_t ldres,
+                       const void* gate, int64_t ldgate, int rows_per_gate, int gate_is_bf16, int token_tile,
+                       int splits, void* workspace, size_t workspace_bytes, int* status_word, void* stream);
+
+/* Gated FFN front half in one launch: h[M,I] = bf16(bf16(gelu_tanh(g)) * u) with
+ * g = bf16(x.Wg^T*sg), u = bf16(x.Wu^T*su); both weight matrices are e4m3 [I,K].
+ * Replaces gate_proj / up_proj / GELU-tanh / multiply of GemmaMLP.forward
+ * (tybok/policies/pi05/models/layers.py:87-95) and the reference's fused norm+gate/up kernel
+ * (tybok/policies/pi05/models/triton_expert_mlp_fp8.py:54-151) without the activation quantisation. */
+int tybok_w8a16_geglu(const void* x, const void* w8_gate, const float* scale_gate, const void* w8_up,
+                      const float* scale_up, void* h, int M, int I, int K, int64_t ldx, int64_t ldh, int token_tile,
+                      int splits, void* workspace, size_t workspace_bytes, int* status_word, void* stream);
+
+/* Enable (1) / disable (0) programmatic dependent launch for every kernel of this library
+ * (process-wide; default 1).  With it, a kernel's weight prefetch overlaps the tail of the
+ * previous kernel in the stream. */
+void tybok_set_pdl(int enabled);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TYBOK_B200_H */

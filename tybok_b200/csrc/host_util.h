@@ -1,0 +1,32 @@
+// Host-side helpers shared by the launchers: error reporting, device checks, TMA tensor maps.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace tb {
+namespace host {
+
+// Record `msg` as the calling thread's last error and return `code`.
+int fail(int code, const char* msg);
+// Record the pending CUDA error (cudaGetLastError) prefixed by `what`; returns TYBOK_ERR_CUDA.
+int fail_cuda(const char* what);
+
+int current_device();
+int sm_count();
+// TYBOK_OK when the current device is compute capability 10.x, TYBOK_ERR_ARCH otherwise.
+int require_sm100();
+
+bool pdl_enabled();
+void count_launch();
+
+// Encode a 2-D tiled tensor map with the 128-byte shared-memory swizzle.
+//   dim0/dim1: extent in elements (dim0 innermost), pitch_bytes: distance between rows,
+//   box0/box1: tile extent in elements; box0 * elem_bytes must be <= 128.
+int tensor_map_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, int elem_bytes, uint64_t dim0,
+                  uint64_t dim1, uint64_t pitch_bytes, uint32_t box0, uint32_t box1);
+
+}  // namespace host
+}  // namespace tb
