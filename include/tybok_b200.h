@@ -45,23 +45,30 @@ const char* tybok_last_error(void);
 /* Number of kernels this library has launched in this process (all threads, all streams). */
 long long tybok_launch_count(void);
 
-/* Bytes of scratch a W8A16 launch of this shape may need (split-K partials + tile counters).
- * The first TYBOK_COUNTER_BYTES bytes hold arrival counters: zero them once after allocation;
- * every launch leaves them zero again.  `dual` = 1 for the gated (two-matrix) form. */
-#define TYBOK_COUNTER_BYTES 16384
+/* ---- activation planes -------------------------------------------------------------------
+ * The GEMMs consume activations as three e5m2 byte planes [3][M][K] whose sum is
+ * x * 2^x_shift; for bf16 x the sum is exact whenever |x * 2^x_shift| lies in [2^-7, 57344]
+ * (below: absolute error <= 2^-17; above: the terms saturate).  Kernels of this library that
+ * produce activations can write the planes directly; tybok_split3 converts a bf16 tensor. */
+#define TYBOK_DEFAULT_X_SHIFT 4
+int tybok_split3(const void* x, int64_t ldx, void* planes, int M, int K, int x_shift, void* stream);
+
+/* Bytes of scratch tybok_w8a16_linear / tybok_w8a16_geglu need: the activation planes, 3*M*K. */
 size_t tybok_w8a16_workspace_bytes(int M, int N, int K, int dual);
 
 /* W8A16 linear: y[M,N] = epilogue(x[M,K] . (W8[N,K] * scale[N])^T + bias[N]).
  *   x        bf16, row stride ldx elements (ldx % 8 == 0, pointer 16-byte aligned)
- *   w8       e4m3 bytes, contiguous [N,K] (K % 16 == 0, pointer 16-byte aligned)
- *   scale    fp32 [N]; bias bf16 [N] or NULL
- *   y        bf16, row stride ldy
+ *   w8       e4m3 bytes, contiguous [N,K] (K % 16 == 0, N % 4 == 0, pointer 16-byte aligned)
+ *   scale    fp32 [N] (16-byte aligned); bias bf16 [N] or NULL
+ *   y        bf16, row stride ldy (ldy % 4 == 0, pointer 8-byte aligned)
  *   epilogue TYBOK_EPI_*; residual bf16 [M,N] stride ldres (EPI_RESIDUAL only)
  *   gate     NULL, or per-row-group gate [ceil(M/rows_per_gate), N] with row stride ldgate:
  *            fp32 when gate_is_bf16 == 0 (rounded to bf16 before use), bf16 otherwise
  *   token_tile, splits  0 = choose automatically; otherwise force the token tile
- *            (multiple of 16, <= 256) / the split-K factor
+ *            (multiple of 16, <= 256) / the split-K factor (<= 8, one cluster per output tile)
+ *   workspace  >= tybok_w8a16_workspace_bytes(...) bytes, 16-byte aligned
  *   status_word  optional device int; set non-zero if a bounded device wait ran out
+ * Two launches: tybok_split3 into the workspace, then tybok_w8x3_linear.
  * Replaces the reference's dequant-then-F.linear path
  * (tybok/policies/fastwam/models/policy.py:48-58,127-129) and its W8 GEMM body
  * (tybok/policies/fastwam/kernels/vdit_gemm_core.cu:68, epilogues EPI/RESID). */
@@ -70,14 +77,28 @@ int tybok_w8a16_linear(const void* x, const void* w8, const float* scale, const 
                        const void* gate, int64_t ldgate, int rows_per_gate, int gate_is_bf16, int token_tile,
                        int splits, void* workspace, size_t workspace_bytes, int* status_word, void* stream);
 
-/* Gated FFN front half in one launch: h[M,I] = bf16(bf16(gelu_tanh(g)) * u) with
- * g = bf16(x.Wg^T*sg), u = bf16(x.Wu^T*su); both weight matrices are e4m3 [I,K].
- * Replaces gate_proj / up_proj / GELU-tanh / multiply of GemmaMLP.forward
- * (tybok/policies/pi05/models/layers.py:87-95) and the reference's fused norm+gate/up kernel
- * (tybok/policies/pi05/models/triton_expert_mlp_fp8.py:54-151) without the activation quantisation. */
+/* Gated FFN front half: h[M,I] = bf16(bf16(gelu_tanh(g)) * u) with g = bf16(x.Wg^T*sg),
+ * u = bf16(x.Wu^T*su); both weight matrices are e4m3 [I,K].  Replaces gate_proj / up_proj /
+ * GELU-tanh / multiply of GemmaMLP.forward (tybok/policies/pi05/models/layers.py:87-95) and
+ * the reference's fused norm+gate/up kernel
+ * (tybok/policies/pi05/models/triton_expert_mlp_fp8.py:54-151) without its activation quantisation. */
 int tybok_w8a16_geglu(const void* x, const void* w8_gate, const float* scale_gate, const void* w8_up,
                       const float* scale_up, void* h, int M, int I, int K, int64_t ldx, int64_t ldh, int token_tile,
                       int splits, void* workspace, size_t workspace_bytes, int* status_word, void* stream);
+
+/* The same two operations on activation planes (one launch each).  Either output may be NULL:
+ *   y / h        bf16 result, row stride ldy / ldh
+ *   y_planes / h_planes  [3][M][N] planes of result * 2^out_shift, ready for the next GEMM
+ * These are what the fused layer chains call: a producer kernel writes planes, so the FFN
+ * intermediate reaches the down projection without a bf16 round trip
+ * (the role of P3 "requant" in tybok/policies/fastwam/kernels/adit_ffn.cu:65-432). */
+int tybok_w8x3_linear(const void* x_planes, int x_shift, const void* w8, const float* scale, const void* bias, void* y,
+                      int64_t ldy, void* y_planes, int out_shift, int M, int N, int K, int epilogue,
+                      const void* residual, int64_t ldres, const void* gate, int64_t ldgate, int rows_per_gate,
+                      int gate_is_bf16, int token_tile, int splits, int* status_word, void* stream);
+int tybok_w8x3_geglu(const void* x_planes, int x_shift, const void* w8_gate, const float* scale_gate, const void* w8_up,
+                     const float* scale_up, void* h, int64_t ldh, void* h_planes, int out_shift, int M, int I, int K,
+                     int token_tile, int splits, int* status_word, void* stream);
 
 /* Enable (1) / disable (0) programmatic dependent launch for every kernel of this library
  * (process-wide; default 1).  With it, a kernel's weight prefetch overlaps the tail of the

@@ -1,8 +1,9 @@
 """W8A16 linear / gated FFN front half on the GPU against the CPU oracle.
 
-Tolerance (BASELINE north_star): rel-L2 <= 1e-2 on bf16 outputs.  The kernel applies the
-per-channel scale to the fp32 accumulator, the oracle rounds ``w8*scale`` to bf16 per weight
-before the GEMM; that difference measures ~2.6e-3 rel-L2.
+Tolerance (BASELINE north_star): rel-L2 <= 1e-2 on bf16 outputs.  The kernel multiplies the
+exact e4m3 weights with the exact bf16 activations and applies the per-channel scale to the
+fp32 accumulator; the oracle rounds ``w8*scale`` to bf16 per weight before the GEMM.  That
+difference measures ~2.6e-3 rel-L2.
 """
 
 import pytest
@@ -112,7 +113,7 @@ def test_residual_epilogue(gated, splits):
 
 
 @pytest.mark.parametrize("m,i,k,splits", [(50, 256, 512, 1), (50, 4096, 1024, 0), (544, 1024, 256, 1), (10, 384, 128, 1),
-                                          (50, 256, 1024, 4)])
+                                          (50, 256, 1024, 4), (50, 256, 2048, 8)])
 def test_geglu(m, i, k, splits):
     ops = _ops()
     g = torch.Generator().manual_seed(9)
@@ -123,6 +124,61 @@ def test_geglu(m, i, k, splits):
     h = ops.w8a16_geglu(x.cuda(), gate[0].cuda(), gate[1].cuda(), up[0].cuda(), up[1].cuda(), splits=splits)
     ops.check_status()
     assert w8_ref.rel_l2(h.cpu(), ref) <= TOL
+
+
+def test_split3_planes_are_exact():
+    """The three e5m2 planes sum to x * 2**shift exactly inside the documented window."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(4)
+    x = (torch.empty(37, 256).normal_(0, 1, generator=g) * torch.exp(torch.empty(37, 256).normal_(0, 2, generator=g)))
+    x = x.clamp(-3000, 3000).to(torch.bfloat16)
+    planes = ops.split3(x.cuda(), 4).cpu()
+    total = planes.view(torch.float8_e5m2).float().sum(0)
+    want = x.float() * 16.0
+    inside = want.abs() >= 2.0**-7
+    assert torch.equal(total[inside], want[inside])
+    assert float((total - want).abs().max()) <= 2.0**-17
+
+
+def test_planes_in_planes_out_chain():
+    """geglu -> planes -> down projection, never materialising the bf16 intermediate:
+    the gated FFN of tybok/policies/pi05/models/layers.py:87-95."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(12)
+    m, k, i = 50, 256, 512
+    x = torch.empty(m, k).normal_(0, 1, generator=g).to(torch.bfloat16)
+    gate, up, down = (w8_ref.quantize_w8(torch.empty(s).normal_(0, 0.02, generator=g)) for s in ((i, k), (i, k), (k, i)))
+    ref = w8_ref.gemma_mlp(x, gate, up, down)
+    cu = lambda t: tuple(a.cuda() for a in t)  # noqa: E731
+    xp = ops.split3(x.cuda(), 4)
+    h, hp = ops.w8x3_geglu(xp, 4, *cu(gate), *cu(up), out_bf16=True, out_planes=True, out_shift=6)
+    y, _ = ops.w8x3_linear(hp, 6, *cu(down))
+    ops.check_status()
+    assert w8_ref.rel_l2(y.cpu(), ref) <= TOL
+    # the planes hold exactly the bf16 intermediate
+    got, want = hp.cpu().view(torch.float8_e5m2).float().sum(0), h.cpu().float() * 64.0
+    inside = want.abs() >= 2.0**-7
+    assert torch.equal(got[inside], want[inside]) and float((got - want).abs().max()) <= 2.0**-17
+
+
+def test_c_abi_bf16_entry_point_with_workspace():
+    """``tybok_w8a16_linear`` as a C caller sees it: bf16 in, caller-owned workspace."""
+    ops = _ops()
+    lib = ops._lib.load()
+    x, w8, scale, _ = _case(21, 50, 256, 512)
+    xd, wd, sd = x.cuda(), w8.cuda(), scale.cuda()
+    y = torch.empty(50, 256, dtype=torch.bfloat16, device="cuda")
+    need = lib.tybok_w8a16_workspace_bytes(50, 256, 512, 0)
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    rc = lib.tybok_w8a16_linear(xd.data_ptr(), wd.data_ptr(), sd.data_ptr(), None, y.data_ptr(), 50, 256, 512, 512, 256,
+                                0, None, 0, None, 0, 1, 0, 0, 0, ws.data_ptr(), need, None, stream)
+    assert rc == 0, lib.tybok_last_error()
+    torch.cuda.synchronize()
+    assert w8_ref.rel_l2(y.cpu(), w8_ref.w8_linear(x, w8, scale)) <= TOL
+    rc = lib.tybok_w8a16_linear(xd.data_ptr(), wd.data_ptr(), sd.data_ptr(), None, y.data_ptr(), 50, 256, 512, 512, 256,
+                                0, None, 0, None, 0, 1, 0, 0, 0, ws.data_ptr(), need - 1, None, stream)
+    assert rc == 3 and b"workspace" in lib.tybok_last_error()
 
 
 def test_bad_arguments_raise():

@@ -20,6 +20,17 @@ SIGNATURES = {
     "tybok_last_error": (ctypes.c_char_p, []),
     "tybok_launch_count": (ctypes.c_longlong, []),
     "tybok_set_pdl": (None, [c_int]),
+    "tybok_split3": (c_int, [c_void_p, c_i64, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "tybok_w8x3_linear": (
+        c_int,
+        [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_i64, c_void_p, c_int, c_int, c_int, c_int, c_int,
+         c_void_p, c_i64, c_void_p, c_i64, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    ),
+    "tybok_w8x3_geglu": (
+        c_int,
+        [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_i64, c_void_p, c_int, c_int, c_int,
+         c_int, c_int, c_int, c_void_p, c_void_p],
+    ),
     "tybok_w8a16_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "tybok_w8a16_linear": (
         c_int,

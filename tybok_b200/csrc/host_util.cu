@@ -108,6 +108,31 @@ int tensor_map_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype,
   return TYBOK_OK;
 }
 
+int tensor_map_3d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, int elem_bytes, uint64_t dim0,
+                  uint64_t dim1, uint64_t dim2, uint64_t pitch1, uint64_t pitch2, uint32_t box0, uint32_t box1,
+                  uint32_t box2) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(TYBOK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (pitch1 & 15) || (pitch2 & 15) || box0 * elem_bytes > 128 ||
+      box1 > 256 || box2 > 256)
+    return fail(TYBOK_ERR_ARG, "tensor map: base/pitches must be 16-byte aligned, box <= 128 bytes x 256 x 256");
+  cuuint64_t dims[3] = {dim0, dim1, dim2};
+  cuuint64_t strides[2] = {pitch1, pitch2};
+  cuuint32_t box[3] = {box0, box1, box2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = fn(out, dtype, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char msg[160];
+    std::snprintf(msg, sizeof(msg), "cuTensorMapEncodeTiled (3-D) failed with CUresult %d (dims %llu x %llu x %llu)",
+                  static_cast<int>(r), static_cast<unsigned long long>(dim0), static_cast<unsigned long long>(dim1),
+                  static_cast<unsigned long long>(dim2));
+    return fail(TYBOK_ERR_CUDA, msg);
+  }
+  return TYBOK_OK;
+}
+
 }  // namespace host
 }  // namespace tb
 

@@ -28,5 +28,10 @@ void count_launch();
 int tensor_map_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, int elem_bytes, uint64_t dim0,
                   uint64_t dim1, uint64_t pitch_bytes, uint32_t box0, uint32_t box1);
 
+// 3-D variant: dim0 innermost; pitch1/pitch2 are the byte strides of dim1 and dim2.
+int tensor_map_3d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, int elem_bytes, uint64_t dim0,
+                  uint64_t dim1, uint64_t dim2, uint64_t pitch1, uint64_t pitch2, uint32_t box0, uint32_t box1,
+                  uint32_t box2);
+
 }  // namespace host
 }  // namespace tb

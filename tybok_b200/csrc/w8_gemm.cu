@@ -1,0 +1,641 @@
+// W8A16 linear for sm_100a: e4m3 weights with per-output-channel fp32 scales, bf16
+// activations, fp32 accumulation in tensor memory -- with no per-weight ALU work.
+//
+// The activations arrive as three e5m2 planes whose sum is the bf16 value exactly
+// (split3.cuh).  The weight tile goes TMA -> shared memory -> tcgen05.mma (kind::f8f6f4,
+// A = e4m3, B = e5m2) untouched; each 32-wide K slice is multiplied by the three planes into
+// the same fp32 accumulator.  Products of an e4m3 and an e5m2 number are exact in fp32, so
+// the result is the bf16-activation x e4m3-weight dot product up to fp32 summation order.
+//
+// Orientation: the weight tile is the 128-row M side of the UMMA and the tokens are its N
+// side, D[n, m] = sum_k W[n,k] x[m,k], so any token count from 1 to 256 fills all 128
+// tensor-memory lanes.
+//
+// Per CTA (one 128 x token_tile output tile, one K range when split-K is on):
+//   warp 0     TMA producer: weight tile(s) (128 rows x 128 bytes, 128B swizzle) and the three
+//              activation planes of the same K range into an n-stage shared-memory ring.
+//              Weights are requested before the programmatic-dependency wait, activations after.
+//   warp 1     one elected lane issues the MMAs (12 per weight tile and K block) and one
+//              tcgen05.commit per K block.
+//   warps 2-9  epilogue: accumulator -> fp32 staging tile in shared memory; then, 4 channels
+//              per thread: split-K sum, scale/bias, activation, gate/residual and 8-byte stores
+//              (bf16, and/or the three e5m2 planes the next GEMM consumes).
+// Split-K runs as a thread-block cluster along z: every CTA stages its partial tile in its
+// own shared memory, the cluster meets at a hardware barrier, and CTA r sums token rows
+// r*R..(r+1)*R-1 over all ranks in rank order through distributed shared memory.  No global
+// scratch, no atomics, bit-reproducible.
+//
+// Algorithmic HBM bytes per launch: N*K (weights) + 4*N (scales) + 2*M*K (x) + 2*M*N (y).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "../../include/tybok_b200.h"
+#include "host_util.h"
+#include "ptx.cuh"
+#include "split3.cuh"
+
+namespace tb {
+
+constexpr int BN = 128;  // weight rows per tile = UMMA M
+constexpr int BK = 128;  // K per pipeline stage (one 128-byte swizzle row of 8-bit elements)
+constexpr int W_TILE_BYTES = BN * BK;
+constexpr int MAX_STAGES = 8;
+constexpr int EPI_WARPS = 8;
+constexpr int EPI_THREADS = EPI_WARPS * 32;
+constexpr int THREADS = 32 * (2 + EPI_WARPS);
+constexpr int DYN_SMEM_MAX = 226 * 1024;  // 227 KB per CTA minus 1 KB left for static shared memory
+constexpr int MAX_SPLITS = 8;             // portable cluster size
+
+enum : int { EPI_NONE = 0, EPI_GELU = 1, EPI_RESIDUAL = 2, EPI_GEGLU = 3 };
+
+struct GemmParams {
+  int M, N, K;
+  int bt;        // token tile (UMMA N), multiple of 16, <= 256 (<= 128 when nw == 2)
+  int nw;        // weight matrices per CTA: 1, or 2 for the gated form
+  int splits;    // split-K factor == cluster size along z
+  int kb_total;  // ceil(K / BK)
+  int kb_per_split;
+  int nstages;
+  int tmem_cols;
+  int merge;     // 1: the three planes are one UMMA of N = 3*bt whose column groups the epilogue adds
+  int epi;
+  int pdl;
+  float out_scale;   // 2^-x_shift: undoes the power-of-two pre-scale of the activation planes
+  float plane_scale; // 2^out_shift applied to the values written as output planes
+  const float* scale0;
+  const float* scale1;
+  const __nv_bfloat16* bias0;
+  __nv_bfloat16* y;  // bf16 output or NULL
+  long long ldy;
+  uint8_t* y_planes;  // [3][M][N] e5m2 output planes or NULL
+  const __nv_bfloat16* res;
+  long long ldres;
+  const void* gate;
+  long long ldgate;
+  int rows_per_gate;
+  int gate_bf16;
+  int* status;
+};
+
+struct __align__(8) Barriers {
+  uint64_t full[MAX_STAGES];
+  uint64_t empty[MAX_STAGES];
+  uint64_t tmem_full;
+  uint32_t tmem_base;
+  volatile int abort;
+};
+
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitLimitCycles) return false;
+  }
+  return true;
+}
+
+__device__ __forceinline__ void fail(Barriers* b, int* status, int code) {
+  b->abort = 1;
+  if (status) atomicCAS(status, 0, code);
+}
+
+__device__ __forceinline__ float4 ld_stage(uint32_t local_addr, int rank, bool remote) {
+  if (remote) return ld_dsmem_f4(dsmem_addr(local_addr, rank));
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(local_addr));
+  return v;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1,
+               const __grid_constant__ CUtensorMap tm_x, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ Barriers bars;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  const int ns = p.nstages;
+  const int x_bytes = 3 * p.bt * 128;                 // three planes of bt rows x 128 bytes
+  const int x_off = p.nw * W_TILE_BYTES;              // activation planes follow the weight tile(s)
+  const int stage_bytes = x_off + x_bytes;
+
+  const int t_tile = blockIdx.x, n_tile = blockIdx.y, split = blockIdx.z;
+  const int kb0 = split * p.kb_per_split;
+  const int nkb = min(p.kb_total, kb0 + p.kb_per_split) - kb0;
+
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tm_w0);
+    if (p.nw == 2) tma_prefetch_desc(&tm_w1);
+    tma_prefetch_desc(&tm_x);
+    for (int i = 0; i < MAX_STAGES; ++i) {
+      mbar_init(&bars.full[i], 1);
+      mbar_init(&bars.empty[i], 1);
+    }
+    mbar_init(&bars.tmem_full, 1);
+    bars.abort = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars.tmem_base, p.tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars.tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int issued = 0;
+      bool ok = true;
+      // Weights do not depend on the previous kernel in the stream: request them before waiting
+      // for it; the activation planes are requested once the dependency has resolved.
+      const int pre = min(ns, nkb);
+      for (int i = 0; i < pre; ++i) {
+        uint8_t* st = smem + i * stage_bytes;
+        mbar_arrive_expect_tx(&bars.full[i], stage_bytes);
+        const int k0 = (kb0 + i) * BK;
+        tma_load_2d(st, &tm_w0, &bars.full[i], k0, n_tile * BN);
+        if (p.nw == 2) tma_load_2d(st + W_TILE_BYTES, &tm_w1, &bars.full[i], k0, n_tile * BN);
+      }
+      if (p.pdl) pdl_wait();
+      for (int i = 0; i < pre; ++i)
+        tma_load_3d(smem + i * stage_bytes + x_off, &tm_x, &bars.full[i], (kb0 + i) * BK, t_tile * p.bt, 0);
+      issued = pre;
+      for (int i = pre; i < nkb; ++i) {
+        const int s = i % ns;
+        if (!wait_or_abort(&bars.empty[s], ((i / ns) & 1) ^ 1, &bars.abort)) {
+          fail(&bars, p.status, TYBOK_DEV_TIMEOUT_PRODUCER);
+          ok = false;
+          break;
+        }
+        uint8_t* st = smem + s * stage_bytes;
+        mbar_arrive_expect_tx(&bars.full[s], stage_bytes);
+        const int k0 = (kb0 + i) * BK;
+        tma_load_2d(st, &tm_w0, &bars.full[s], k0, n_tile * BN);
+        if (p.nw == 2) tma_load_2d(st + W_TILE_BYTES, &tm_w1, &bars.full[s], k0, n_tile * BN);
+        tma_load_3d(st + x_off, &tm_x, &bars.full[s], k0, t_tile * p.bt, 0);
+        issued = i + 1;
+      }
+      if (p.pdl) pdl_launch_dependents();
+      if (!ok || bars.abort) {
+        // Unwinding: do not leave the CTA while its own bulk copies may still land in its
+        // shared memory. Wait (bounded) for the newest copy of every stage.
+        for (int i = max(0, issued - ns); i < issued; ++i) mbar_wait(&bars.full[i % ns], (i / ns) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    // The whole warp runs the loop, so every operand is warp-uniform; one elected lane issues.
+    const bool leader = elect_one();
+    // Small token tiles: the three planes are contiguous rows in shared memory, so one UMMA
+    // with N = 3*bt multiplies a K slice by all of them (one column group per plane) -- 4
+    // instead of 12 instructions per weight tile and K block.  Larger tiles issue one UMMA per
+    // plane into the same accumulator.
+    const uint32_t idesc = idesc_e4m3_e5m2_f32(BN, p.merge ? 3 * p.bt : p.bt);
+    const uint64_t desc_const = smem_desc_sw128(0);
+    const uint32_t plane16 = static_cast<uint32_t>(p.bt * 128) >> 4;  // plane pitch in 16-byte units
+    const int acc_cols = p.merge ? 3 * p.bt : p.bt;
+    bool ok = true;
+    for (int i = 0; i < nkb; ++i) {
+      const int s = i % ns;
+      const bool ready = wait_or_abort(&bars.full[s], (i / ns) & 1, &bars.abort);
+      if (!__all_sync(0xffffffffu, ready)) {
+        if (lane == 0) fail(&bars, p.status, TYBOK_DEV_TIMEOUT_MMA);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t st16 = (smem_u32(smem + s * stage_bytes) & 0x3FFFFu) >> 4;
+      const uint32_t x16 = st16 + (x_off >> 4);
+      for (int w = 0; w < p.nw; ++w) {
+        const uint32_t w16 = st16 + w * (W_TILE_BYTES >> 4);
+        const uint32_t d_addr = tmem + w * acc_cols;
+        if (p.merge) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {  // K = 32 per instruction: 32 bytes = 2 sixteen-byte units
+            const uint64_t a_desc = desc_const | (w16 + j * 2);
+            const uint64_t b_desc = desc_const | (x16 + j * 2);
+            if (leader) umma_ss_f8(d_addr, a_desc, b_desc, idesc, (i > 0 || j > 0) ? 1u : 0u);
+          }
+        } else {
+#pragma unroll
+          for (int pl = 0; pl < 3; ++pl) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint64_t a_desc = desc_const | (w16 + j * 2);
+              const uint64_t b_desc = desc_const | (x16 + pl * plane16 + j * 2);
+              if (leader) umma_ss_f8(d_addr, a_desc, b_desc, idesc, (i > 0 || pl > 0 || j > 0) ? 1u : 0u);
+            }
+          }
+        }
+      }
+      if (leader) tc_commit(&bars.empty[s]);  // frees the stage once these MMAs have read it
+      __syncwarp();
+    }
+    if (ok && leader) tc_commit(&bars.tmem_full);
+  } else {
+    // ------------------------------------------------------------ epilogue, phase A
+    // Accumulator (lane = channel, column = token) -> fp32 staging tile [w][token][128 channels]
+    // at the start of the (by now idle) stage ring.
+    const int ew = warp - 2;
+    const int q = warp & 3;   // TMEM lane quadrant this warp may access
+    const int half = ew >> 2;
+    const int row = q * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    bool ok = __all_sync(0xffffffffu, wait_or_abort(&bars.tmem_full, 0, &bars.abort));
+    if (!ok && lane == 0) fail(&bars, p.status, TYBOK_DEV_TIMEOUT_EPILOGUE);
+    if (ok) {
+      tc_fence_after();
+      float* stage = reinterpret_cast<float*>(smem);
+      const int ngroups = p.bt / 16;
+      const int acc_cols = p.merge ? 3 * p.bt : p.bt;
+      for (int w = 0; w < p.nw; ++w) {
+        for (int g = half; g < ngroups; g += 2) {
+          uint32_t v[16];
+          const uint32_t col = tmem + lane_addr + w * acc_cols + g * 16;
+          tmem_ld16(col, v);
+          if (p.merge) {  // add the per-plane column groups in plane order
+            uint32_t v2[16], v3[16];
+            tmem_ld16(col + p.bt, v2);
+            tmem_ld16(col + 2 * p.bt, v3);
+            tc_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 16; ++e)
+              v[e] = __float_as_uint((__uint_as_float(v[e]) + __uint_as_float(v2[e])) + __uint_as_float(v3[e]));
+          } else {
+            tc_wait_ld();
+          }
+#pragma unroll
+          for (int e = 0; e < 16; ++e) stage[(w * p.bt + g * 16 + e) * BN + row] = __uint_as_float(v[e]);
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------ meet: staging tiles complete
+  tc_fence_before();
+  if (p.splits > 1) {
+    __syncwarp();
+    cluster_sync_all();
+  } else {
+    __syncthreads();
+  }
+
+  if (warp >= 2 && !bars.abort) {
+    // ---------------------------------------------------------- epilogue, phase B
+    // 4 consecutive channels per thread, 8 token rows per pass; with split-K, rank r owns token
+    // rows [r*R, (r+1)*R) and sums them over all ranks in rank order.
+    if (p.pdl) pdl_wait();  // outputs / residual may still be in use by the previous kernel
+    const int et = tid - 64;
+    const int v4 = et & 31;
+    const int rgrp = et >> 5;
+    const int n = n_tile * BN + v4 * 4;
+    const bool n_ok = n < p.N;  // N % 4 == 0, so all four channels are valid together
+    float s0[4] = {0, 0, 0, 0}, s1[4] = {0, 0, 0, 0}, b0[4] = {0, 0, 0, 0};
+    if (n_ok) {
+      const float4 t = *reinterpret_cast<const float4*>(p.scale0 + n);
+      s0[0] = t.x * p.out_scale; s0[1] = t.y * p.out_scale; s0[2] = t.z * p.out_scale; s0[3] = t.w * p.out_scale;
+      if (p.nw == 2) {
+        const float4 u = *reinterpret_cast<const float4*>(p.scale1 + n);
+        s1[0] = u.x * p.out_scale; s1[1] = u.y * p.out_scale; s1[2] = u.z * p.out_scale; s1[3] = u.w * p.out_scale;
+      }
+      if (p.bias0) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) b0[e] = __bfloat162float(p.bias0[n + e]);
+      }
+    }
+    const int rank = p.splits > 1 ? static_cast<int>(cluster_ctarank()) : 0;
+    const int rpr = (p.bt + p.splits - 1) / p.splits;
+    const int r0 = rank * rpr, r1 = min(p.bt, r0 + rpr);
+    const uint32_t stage_addr = smem_u32(smem);
+    const int m_base = t_tile * p.bt;
+    const bool remote = p.splits > 1;
+    for (int t = r0 + rgrp; t < r1; t += 8) {
+      const int m = m_base + t;
+      if (!n_ok || m >= p.M) continue;
+      float a0[4] = {0, 0, 0, 0}, a1[4] = {0, 0, 0, 0};
+      for (int sp = 0; sp < p.splits; ++sp) {  // rank order: bit-reproducible
+        const float4 f = ld_stage(stage_addr + (t * BN + v4 * 4) * 4, sp, remote);
+        a0[0] += f.x; a0[1] += f.y; a0[2] += f.z; a0[3] += f.w;
+        if (p.nw == 2) {
+          const float4 g = ld_stage(stage_addr + ((p.bt + t) * BN + v4 * 4) * 4, sp, remote);
+          a1[0] += g.x; a1[1] += g.y; a1[2] += g.z; a1[3] += g.w;
+        }
+      }
+      // Every rounding point is the one the reference's bf16 torch modules have: linear output,
+      // GELU output, product, gated value, residual sum.
+      float o[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[e] = bf16_round(a0[e] * s0[e] + b0[e]);
+      if (p.epi == EPI_GELU) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[e] = gelu_tanh_fast(o[e]);
+      } else if (p.epi == EPI_GEGLU) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[e] = bf16_round(gelu_tanh_fast(o[e])) * bf16_round(a1[e] * s1[e]);
+      } else if (p.epi == EPI_RESIDUAL) {
+        if (p.gate) {
+          const long long gi = static_cast<long long>(m / p.rows_per_gate) * p.ldgate + n;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float gv = p.gate_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.gate)[gi + e])
+                                         : bf16_round(static_cast<const float*>(p.gate)[gi + e]);
+            o[e] = bf16_round(o[e] * gv);
+          }
+        }
+        const uint2 rr = *reinterpret_cast<const uint2*>(p.res + static_cast<long long>(m) * p.ldres + n);
+        const __nv_bfloat162 r01 = *reinterpret_cast<const __nv_bfloat162*>(&rr.x);
+        const __nv_bfloat162 r23 = *reinterpret_cast<const __nv_bfloat162*>(&rr.y);
+        o[0] += __bfloat162float(r01.x); o[1] += __bfloat162float(r01.y);
+        o[2] += __bfloat162float(r23.x); o[3] += __bfloat162float(r23.y);
+      }
+      const __nv_bfloat162 o01 = __floats2bfloat162_rn(o[0], o[1]);
+      const __nv_bfloat162 o23 = __floats2bfloat162_rn(o[2], o[3]);
+      if (p.y) {
+        uint2 st;
+        st.x = *reinterpret_cast<const uint32_t*>(&o01);
+        st.y = *reinterpret_cast<const uint32_t*>(&o23);
+        *reinterpret_cast<uint2*>(p.y + static_cast<long long>(m) * p.ldy + n) = st;
+      }
+      if (p.y_planes) {
+        // The next GEMM's activation planes, from the bf16-rounded values just produced.
+        const float xs[4] = {__bfloat162float(o01.x) * p.plane_scale, __bfloat162float(o01.y) * p.plane_scale,
+                             __bfloat162float(o23.x) * p.plane_scale, __bfloat162float(o23.y) * p.plane_scale};
+        uint32_t w1, w2, w3;
+        split3_quad(xs, w1, w2, w3);
+        const long long plane = static_cast<long long>(p.M) * p.N;
+        uint8_t* dst = p.y_planes + static_cast<long long>(m) * p.N + n;
+        *reinterpret_cast<uint32_t*>(dst) = w1;
+        *reinterpret_cast<uint32_t*>(dst + plane) = w2;
+        *reinterpret_cast<uint32_t*>(dst + 2 * plane) = w3;
+      }
+    }
+  }
+
+  // Peers may still be reading this CTA's staging tile: leave together.
+  if (p.splits > 1) {
+    __syncwarp();
+    cluster_sync_all();
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, p.tmem_cols);
+  }
+}
+
+// ------------------------------------------------------------------------------------ split kernel
+// x[M,K] (bf16, row stride ldx) -> three e5m2 planes [3][M][K] holding x * 2^shift.
+__global__ void split3_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ planes, int M,
+                              int K, float mult, int pdl) {
+  if (pdl) pdl_wait();
+  const long long plane = static_cast<long long>(M) * K;
+  const int kv = K / 8;  // 8 elements per thread
+  const long long total = static_cast<long long>(M) * kv;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int m = static_cast<int>(i / kv), c = static_cast<int>(i % kv);
+    const uint4 raw = *reinterpret_cast<const uint4*>(x + m * ldx + c * 8);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    float lo[4] = {__bfloat162float(h[0].x) * mult, __bfloat162float(h[0].y) * mult, __bfloat162float(h[1].x) * mult,
+                   __bfloat162float(h[1].y) * mult};
+    float hi[4] = {__bfloat162float(h[2].x) * mult, __bfloat162float(h[2].y) * mult, __bfloat162float(h[3].x) * mult,
+                   __bfloat162float(h[3].y) * mult};
+    uint2 w1, w2, w3;
+    split3_quad(lo, w1.x, w2.x, w3.x);
+    split3_quad(hi, w1.y, w2.y, w3.y);
+    uint8_t* dst = planes + static_cast<long long>(m) * K + c * 8;
+    *reinterpret_cast<uint2*>(dst) = w1;
+    *reinterpret_cast<uint2*>(dst + plane) = w2;
+    *reinterpret_cast<uint2*>(dst + 2 * plane) = w3;
+  }
+  if (pdl) pdl_launch_dependents();
+}
+
+// ------------------------------------------------------------------------------------ host
+struct Plan {
+  int bt, t_tiles, n_tiles, splits, kb_total, kb_per_split, nstages, smem_bytes, tmem_cols, merge;
+};
+
+static int round_up(int a, int b) { return (a + b - 1) / b * b; }
+
+static bool make_plan(int M, int N, int K, int nw, int force_bt, int force_splits, Plan& pl) {
+  const int max_bt = nw == 2 ? 128 : 256;
+  int bt;
+  if (force_bt > 0) {
+    bt = force_bt;
+  } else {
+    const int cap = 128;
+    const int tiles = (M + cap - 1) / cap;
+    bt = round_up((M + tiles - 1) / tiles, 16);
+  }
+  if (bt % 16 != 0 || bt < 16 || bt > max_bt) return false;
+  pl.bt = bt;
+  pl.t_tiles = (M + bt - 1) / bt;
+  pl.n_tiles = (N + BN - 1) / BN;
+  pl.kb_total = (K + BK - 1) / BK;
+  int splits = force_splits;
+  if (splits <= 0) {
+    const int sms = host::sm_count();
+    const int tiles = pl.t_tiles * pl.n_tiles;
+    splits = 1;
+    if (tiles * 2 <= sms) splits = std::min(sms / tiles, std::max(1, pl.kb_total / 2));  // >= 2 K blocks per split
+  }
+  splits = std::max(1, std::min(std::min(splits, MAX_SPLITS), pl.kb_total));
+  pl.kb_per_split = (pl.kb_total + splits - 1) / splits;
+  pl.splits = (pl.kb_total + pl.kb_per_split - 1) / pl.kb_per_split;  // no empty split
+  const int stage_bytes = nw * W_TILE_BYTES + 3 * bt * 128;
+  pl.nstages = std::min(MAX_STAGES, (DYN_SMEM_MAX - 1024) / stage_bytes);  // 1 KB of alignment slack
+  pl.nstages = std::min(pl.nstages, std::max(2, pl.kb_per_split));
+  if (pl.nstages < 2) return false;
+  pl.smem_bytes = pl.nstages * stage_bytes + 1024;
+  pl.merge = (3 * bt <= 256 && nw * 3 * bt <= 512) ? 1 : 0;
+  pl.tmem_cols = 32;
+  while (pl.tmem_cols < nw * bt * (pl.merge ? 3 : 1)) pl.tmem_cols *= 2;
+  return true;
+}
+
+static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, const float* s0, const float* s1,
+                       const void* bias, void* y, void* y_planes, int M, int N, int K, long long ldy, int epi,
+                       const void* res, long long ldres, const void* gate, long long ldgate, int rows_per_gate,
+                       int gate_bf16, int x_shift, int out_shift, int force_bt, int force_splits, int* status,
+                       cudaStream_t stream) {
+  const int nw = w1 ? 2 : 1;
+  if (!planes || !w0 || !s0 || (!y && !y_planes)) return host::fail(TYBOK_ERR_ARG, "w8 gemm: null pointer argument");
+  if (M <= 0 || N <= 0 || K <= 0) return host::fail(TYBOK_ERR_ARG, "w8 gemm: M, N, K must be positive");
+  if (K % 16 != 0) return host::fail(TYBOK_ERR_ARG, "w8 gemm: K must be a multiple of 16 (TMA row pitch)");
+  if (N % 4 != 0) return host::fail(TYBOK_ERR_ARG, "w8 gemm: N must be a multiple of 4 (vector epilogue)");
+  if ((reinterpret_cast<uintptr_t>(planes) | reinterpret_cast<uintptr_t>(w0) | reinterpret_cast<uintptr_t>(w1) |
+       reinterpret_cast<uintptr_t>(s0) | reinterpret_cast<uintptr_t>(s1)) & 15)
+    return host::fail(TYBOK_ERR_ARG, "w8 gemm: planes, w8 and scale must be 16-byte aligned");
+  if (y && ((reinterpret_cast<uintptr_t>(y) & 7) || ldy % 4 != 0 || ldy < N))
+    return host::fail(TYBOK_ERR_ARG, "w8 gemm: y must be 8-byte aligned with ldy >= N, ldy % 4 == 0");
+  if (y_planes && (reinterpret_cast<uintptr_t>(y_planes) & 3))
+    return host::fail(TYBOK_ERR_ARG, "w8 gemm: output planes must be 4-byte aligned");
+  if (epi == EPI_RESIDUAL && (!res || (reinterpret_cast<uintptr_t>(res) & 7) || ldres % 4 != 0))
+    return host::fail(TYBOK_ERR_ARG, "w8 gemm: residual epilogue needs an 8-byte aligned residual, ldres % 4 == 0");
+  if (gate && rows_per_gate <= 0) return host::fail(TYBOK_ERR_ARG, "w8 gemm: rows_per_gate must be positive");
+  if (x_shift < -60 || x_shift > 60 || out_shift < -60 || out_shift > 60)
+    return host::fail(TYBOK_ERR_ARG, "w8 gemm: exponent shift out of range");
+  if (int rc = host::require_sm100()) return rc;
+
+  Plan pl;
+  if (!make_plan(M, N, K, nw, force_bt, force_splits, pl))
+    return host::fail(TYBOK_ERR_ARG, "w8 gemm: unsupported token tile (multiple of 16, <= 256, <= 128 when gated)");
+  if (force_splits > MAX_SPLITS) return host::fail(TYBOK_ERR_ARG, "w8 gemm: at most 8 K splits (cluster size)");
+  if (pl.n_tiles > 65535) return host::fail(TYBOK_ERR_ARG, "w8 gemm: grid too large");
+
+  CUtensorMap tm_w0, tm_w1, tm_x;
+  if (int rc = host::tensor_map_2d(&tm_w0, w0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, N, K, BK, BN)) return rc;
+  tm_w1 = tm_w0;
+  if (nw == 2)
+    if (int rc = host::tensor_map_2d(&tm_w1, w1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, N, K, BK, BN)) return rc;
+  if (int rc = host::tensor_map_3d(&tm_x, planes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, M, 3, K,
+                                   static_cast<uint64_t>(M) * K, BK, pl.bt, 3))
+    return rc;
+
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.bt = pl.bt; p.nw = nw; p.splits = pl.splits; p.kb_total = pl.kb_total; p.kb_per_split = pl.kb_per_split;
+  p.nstages = pl.nstages; p.tmem_cols = pl.tmem_cols; p.merge = pl.merge; p.epi = epi; p.pdl = host::pdl_enabled() ? 1 : 0;
+  p.out_scale = ldexpf(1.0f, -x_shift);
+  p.plane_scale = ldexpf(1.0f, out_shift);
+  p.scale0 = s0; p.scale1 = s1; p.bias0 = static_cast<const __nv_bfloat16*>(bias);
+  p.y = static_cast<__nv_bfloat16*>(y); p.ldy = ldy; p.y_planes = static_cast<uint8_t*>(y_planes);
+  p.res = static_cast<const __nv_bfloat16*>(res); p.ldres = ldres;
+  p.gate = gate; p.ldgate = ldgate; p.rows_per_gate = rows_per_gate > 0 ? rows_per_gate : 1; p.gate_bf16 = gate_bf16;
+  p.status = status;
+
+  static bool attr_set[64] = {};
+  const int dev = host::current_device();
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(w8_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DYN_SMEM_MAX) != cudaSuccess)
+      return host::fail_cuda("cudaFuncSetAttribute(w8_gemm_kernel)");
+    attr_set[dev] = true;
+  }
+
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(pl.t_tiles, pl.n_tiles, pl.splits);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = pl.smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (p.pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (pl.splits > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = pl.splits;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  if (cudaLaunchKernelEx(&cfg, w8_gemm_kernel, tm_w0, tm_w1, tm_x, p) != cudaSuccess)
+    return host::fail_cuda("launch w8_gemm_kernel");
+  host::count_launch();
+  return TYBOK_OK;
+}
+
+static int launch_split3(const void* x, long long ldx, void* planes, int M, int K, int shift, cudaStream_t stream) {
+  if (!x || !planes) return host::fail(TYBOK_ERR_ARG, "split3: null pointer argument");
+  if (M <= 0 || K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldx < K)
+    return host::fail(TYBOK_ERR_ARG, "split3: K and ldx must be multiples of 8, ldx >= K");
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(planes) & 15) ||
+      (static_cast<long long>(M) * K) % 8 != 0)
+    return host::fail(TYBOK_ERR_ARG, "split3: x and planes must be 16-byte aligned");
+  if (shift < -60 || shift > 60) return host::fail(TYBOK_ERR_ARG, "split3: exponent shift out of range");
+  const long long total = static_cast<long long>(M) * (K / 8);
+  const int threads = 256;
+  const int blocks = static_cast<int>(std::min<long long>((total + threads - 1) / threads, 4 * host::sm_count()));
+  const int pdl = host::pdl_enabled() ? 1 : 0;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(blocks);
+  cfg.blockDim = dim3(threads);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl;
+  if (cudaLaunchKernelEx(&cfg, split3_kernel, static_cast<const __nv_bfloat16*>(x), ldx, static_cast<uint8_t*>(planes),
+                         M, K, ldexpf(1.0f, shift), pdl) != cudaSuccess)
+    return host::fail_cuda("launch split3_kernel");
+  host::count_launch();
+  return TYBOK_OK;
+}
+
+}  // namespace tb
+
+extern "C" {
+
+size_t tybok_w8a16_workspace_bytes(int M, int N, int K, int dual) {
+  (void)N;
+  (void)dual;
+  return static_cast<size_t>(3) * static_cast<size_t>(M > 0 ? M : 0) * static_cast<size_t>(K > 0 ? K : 0);
+}
+
+int tybok_split3(const void* x, int64_t ldx, void* planes, int M, int K, int x_shift, void* stream) {
+  return tb::launch_split3(x, ldx, planes, M, K, x_shift, static_cast<cudaStream_t>(stream));
+}
+
+int tybok_w8x3_linear(const void* x_planes, int x_shift, const void* w8, const float* scale, const void* bias, void* y,
+                      int64_t ldy, void* y_planes, int out_shift, int M, int N, int K, int epilogue,
+                      const void* residual, int64_t ldres, const void* gate, int64_t ldgate, int rows_per_gate,
+                      int gate_is_bf16, int token_tile, int splits, int* status_word, void* stream) {
+  if (epilogue != TYBOK_EPI_NONE && epilogue != TYBOK_EPI_GELU && epilogue != TYBOK_EPI_RESIDUAL)
+    return tb::host::fail(TYBOK_ERR_ARG, "w8x3_linear: unknown epilogue");
+  return tb::launch_gemm(static_cast<const uint8_t*>(x_planes), w8, nullptr, scale, nullptr, bias, y, y_planes, M, N, K,
+                         ldy, epilogue, residual, ldres, gate, ldgate, rows_per_gate, gate_is_bf16, x_shift, out_shift,
+                         token_tile, splits, status_word, static_cast<cudaStream_t>(stream));
+}
+
+int tybok_w8x3_geglu(const void* x_planes, int x_shift, const void* w8_gate, const float* scale_gate, const void* w8_up,
+                     const float* scale_up, void* h, int64_t ldh, void* h_planes, int out_shift, int M, int I, int K,
+                     int token_tile, int splits, int* status_word, void* stream) {
+  if (!w8_up || !scale_up) return tb::host::fail(TYBOK_ERR_ARG, "w8x3_geglu: null up-projection");
+  return tb::launch_gemm(static_cast<const uint8_t*>(x_planes), w8_gate, w8_up, scale_gate, scale_up, nullptr, h,
+                         h_planes, M, I, K, ldh, tb::EPI_GEGLU, nullptr, 0, nullptr, 0, 1, 0, x_shift, out_shift,
+                         token_tile, splits, status_word, static_cast<cudaStream_t>(stream));
+}
+
+int tybok_w8a16_linear(const void* x, const void* w8, const float* scale, const void* bias, void* y, int M, int N,
+                       int K, int64_t ldx, int64_t ldy, int epilogue, const void* residual, int64_t ldres,
+                       const void* gate, int64_t ldgate, int rows_per_gate, int gate_is_bf16, int token_tile,
+                       int splits, void* workspace, size_t workspace_bytes, int* status_word, void* stream) {
+  if (!workspace || workspace_bytes < tybok_w8a16_workspace_bytes(M, N, K, 0))
+    return tb::host::fail(TYBOK_ERR_WORKSPACE, "w8a16_linear: workspace must hold 3*M*K bytes of activation planes");
+  const int shift = TYBOK_DEFAULT_X_SHIFT;
+  if (int rc = tybok_split3(x, ldx, workspace, M, K, shift, stream)) return rc;
+  return tybok_w8x3_linear(workspace, shift, w8, scale, bias, y, ldy, nullptr, 0, M, N, K, epilogue, residual, ldres,
+                           gate, ldgate, rows_per_gate, gate_is_bf16, token_tile, splits, status_word, stream);
+}
+
+int tybok_w8a16_geglu(const void* x, const void* w8_gate, const float* scale_gate, const void* w8_up,
+                      const float* scale_up, void* h, int M, int I, int K, int64_t ldx, int64_t ldh, int token_tile,
+                      int splits, void* workspace, size_t workspace_bytes, int* status_word, void* stream) {
+  if (!workspace || workspace_bytes < tybok_w8a16_workspace_bytes(M, I, K, 1))
+    return tb::host::fail(TYBOK_ERR_WORKSPACE, "w8a16_geglu: workspace must hold 3*M*K bytes of activation planes");
+  const int shift = TYBOK_DEFAULT_X_SHIFT;
+  if (int rc = tybok_split3(x, ldx, workspace, M, K, shift, stream)) return rc;
+  return tybok_w8x3_geglu(workspace, shift, w8_gate, scale_gate, w8_up, scale_up, h, ldh, nullptr, 0, M, I, K,
+                          token_tile, splits, status_word, stream);
+}
+
+}  // extern "C"

@@ -1,8 +1,13 @@
 """torch custom ops over the C ABI (``torch.ops.tybok_b200.*``), CUDA only.
 
-Each op validates tensors, allocates its output with torch (so CUDA-graph capture sees an
-ordinary allocation), and launches on the current torch stream.  The split-K scratch is one
-per-device buffer owned by this module; it is allocated on first use, before any capture.
+Each op validates tensors, allocates its outputs with torch (so CUDA-graph capture sees
+ordinary allocations) and launches on the current torch stream.  There is no CPU
+implementation: calling an op with CPU tensors raises ``NotImplementedError``.
+
+Activation planes: the GEMMs take activations as a ``uint8 [3, M, K]`` tensor of e5m2 bytes
+whose three planes sum to ``x * 2**shift`` (exactly, for bf16 ``x`` in the window documented in
+``include/tybok_b200.h``).  ``split3`` makes them from bf16; the fused producers write them
+directly.
 """
 
 from __future__ import annotations
@@ -12,35 +17,35 @@ import torch
 from . import _lib
 
 EPI_NONE, EPI_GELU, EPI_RESIDUAL = 0, 1, 2
+DEFAULT_SHIFT = 4
 
 _L = torch.library.Library("tybok_b200", "DEF")
+_L.define("split3(Tensor x, int shift) -> Tensor")
 _L.define(
-    "w8a16_linear(Tensor x, Tensor w8, Tensor scale, Tensor? bias, int epilogue, Tensor? residual, Tensor? gate, "
-    "int rows_per_gate, int token_tile, int splits) -> Tensor"
+    "w8x3_linear(Tensor planes, int shift, Tensor w8, Tensor scale, Tensor? bias, int epilogue, Tensor? residual, "
+    "Tensor? gate, int rows_per_gate, bool out_bf16, bool out_planes, int out_shift, int token_tile, int splits) "
+    "-> (Tensor, Tensor)"
 )
-_L.define("w8a16_geglu(Tensor x, Tensor w8_gate, Tensor scale_gate, Tensor w8_up, Tensor scale_up, int token_tile, "
-          "int splits) -> Tensor")
+_L.define(
+    "w8x3_geglu(Tensor planes, int shift, Tensor w8_gate, Tensor scale_gate, Tensor w8_up, Tensor scale_up, "
+    "bool out_bf16, bool out_planes, int out_shift, int token_tile, int splits) -> (Tensor, Tensor)"
+)
 
-_workspaces: dict[int, torch.Tensor] = {}
 _status: dict[int, torch.Tensor] = {}
-WORKSPACE_BYTES = 96 << 20
 
 
-def workspace(device: torch.device) -> torch.Tensor:
-    """The per-device scratch (arrival counters + split-K partials), zeroed once."""
-    idx = device.index if device.index is not None else torch.cuda.current_device()
-    ws = _workspaces.get(idx)
-    if ws is None:
-        ws = torch.zeros(WORKSPACE_BYTES, dtype=torch.uint8, device=torch.device("cuda", idx))
-        _workspaces[idx] = ws
-        _status[idx] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
-    return ws
+def _dev_index(device: torch.device) -> int:
+    return device.index if device.index is not None else torch.cuda.current_device()
 
 
 def status_word(device: torch.device) -> torch.Tensor:
-    workspace(device)
-    idx = device.index if device.index is not None else torch.cuda.current_device()
-    return _status[idx]
+    """Per-device int32 that kernels set when one of their bounded waits runs out."""
+    idx = _dev_index(device)
+    word = _status.get(idx)
+    if word is None:
+        word = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status[idx] = word
+    return word
 
 
 def check_status(device: torch.device | None = None) -> None:
@@ -58,87 +63,135 @@ def _ptr(t: torch.Tensor | None) -> int | None:
     return None if t is None else t.data_ptr()
 
 
-def _rows(x: torch.Tensor) -> tuple[torch.Tensor, int]:
-    k = x.shape[-1]
-    x2 = x.reshape(-1, k)
-    if x2.stride(-1) != 1:
-        x2 = x2.contiguous()
-    return x2, x2.shape[0]
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
 
 
-def _w8a16_linear_cuda(x, w8, scale, bias, epilogue, residual, gate, rows_per_gate, token_tile, splits):
+def _rows(x: torch.Tensor) -> torch.Tensor:
+    x2 = x.reshape(-1, x.shape[-1])
+    return x2 if x2.stride(-1) == 1 else x2.contiguous()
+
+
+def _check_w8(w8: torch.Tensor, what: str) -> None:
+    if w8.dtype not in (torch.float8_e4m3fn, torch.uint8) or not w8.is_contiguous() or w8.dim() != 2:
+        raise TypeError(f"{what}: weight must be a contiguous e4m3 (or raw uint8) [N, K] tensor")
+
+
+def _split3_cuda(x: torch.Tensor, shift: int) -> torch.Tensor:
     lib = _lib.load()
     if x.dtype != torch.bfloat16:
-        raise TypeError(f"w8a16_linear: x must be bf16, got {x.dtype}")
-    if w8.dtype not in (torch.float8_e4m3fn, torch.uint8) or not w8.is_contiguous():
-        raise TypeError("w8a16_linear: w8 must be a contiguous e4m3 (or raw uint8) [N, K] tensor")
+        raise TypeError(f"split3: x must be bf16, got {x.dtype}")
+    x2 = _rows(x)
+    m, k = x2.shape
+    planes = torch.empty((3, m, k), dtype=torch.uint8, device=x.device)
+    rc = lib.tybok_split3(x2.data_ptr(), x2.stride(0), planes.data_ptr(), m, k, int(shift), _stream(x))
+    _lib.check(rc, "tybok_split3")
+    return planes
+
+
+def _outputs(m, n, device, out_bf16, out_planes):
+    if not (out_bf16 or out_planes):
+        raise ValueError("at least one of out_bf16 / out_planes must be set")
+    y = torch.empty((m, n) if out_bf16 else (0,), dtype=torch.bfloat16, device=device)
+    yp = torch.empty((3, m, n) if out_planes else (0,), dtype=torch.uint8, device=device)
+    return y, yp
+
+
+def _w8x3_linear_cuda(planes, shift, w8, scale, bias, epilogue, residual, gate, rows_per_gate, out_bf16, out_planes,
+                      out_shift, token_tile, splits):
+    lib = _lib.load()
+    _check_w8(w8, "w8x3_linear")
+    if planes.dtype != torch.uint8 or planes.dim() != 3 or planes.shape[0] != 3 or not planes.is_contiguous():
+        raise TypeError("w8x3_linear: planes must be a contiguous uint8 [3, M, K] tensor")
     if scale.dtype != torch.float32:
-        raise TypeError("w8a16_linear: scale must be fp32")
+        raise TypeError("w8x3_linear: scale must be fp32")
     n, k = w8.shape
-    x2, m = _rows(x)
-    if x2.shape[1] != k:
-        raise ValueError(f"w8a16_linear: x has K={x2.shape[1]}, weight has K={k}")
-    y = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    m = planes.shape[1]
+    if planes.shape[2] != k:
+        raise ValueError(f"w8x3_linear: planes have K={planes.shape[2]}, weight has K={k}")
+    y, yp = _outputs(m, n, planes.device, out_bf16, out_planes)
     res2 = None
     if residual is not None:
-        res2, mr = _rows(residual)
-        if mr != m or res2.shape[1] != n or res2.dtype != torch.bfloat16:
-            raise ValueError("w8a16_linear: residual must be bf16 [M, N]")
-    gate_bf16 = 0
-    ldgate = 0
+        res2 = _rows(residual)
+        if res2.shape != (m, n) or res2.dtype != torch.bfloat16:
+            raise ValueError("w8x3_linear: residual must be bf16 [M, N]")
+    gate_bf16 = ldgate = 0
     if gate is not None:
-        if gate.dtype not in (torch.float32, torch.bfloat16) or gate.stride(-1) != 1:
-            raise TypeError("w8a16_linear: gate must be fp32 or bf16 with unit inner stride")
+        if gate.dtype not in (torch.float32, torch.bfloat16) or gate.stride(-1) != 1 or gate.shape[-1] != n:
+            raise TypeError("w8x3_linear: gate must be fp32 or bf16 [groups, N] with unit inner stride")
         gate_bf16 = int(gate.dtype == torch.bfloat16)
-        gate = gate.reshape(-1, n) if gate.is_contiguous() else gate
-        ldgate = gate.stride(0) if gate.dim() > 1 else n
-    ws = workspace(x.device)
-    rc = lib.tybok_w8a16_linear(
-        x2.data_ptr(), w8.data_ptr(), scale.data_ptr(), _ptr(bias), y.data_ptr(), m, n, k, x2.stride(0), y.stride(0),
-        int(epilogue), _ptr(res2), res2.stride(0) if res2 is not None else 0, _ptr(gate), ldgate,
-        int(rows_per_gate), gate_bf16, int(token_tile), int(splits), ws.data_ptr(), ws.numel(),
-        status_word(x.device).data_ptr(), torch.cuda.current_stream(x.device).cuda_stream,
+        ldgate = gate.stride(-2) if gate.dim() > 1 else n
+    rc = lib.tybok_w8x3_linear(
+        planes.data_ptr(), int(shift), w8.data_ptr(), scale.data_ptr(), _ptr(bias), y.data_ptr() if out_bf16 else None,
+        n, yp.data_ptr() if out_planes else None, int(out_shift), m, n, k, int(epilogue), _ptr(res2),
+        res2.stride(0) if res2 is not None else 0, _ptr(gate), ldgate, int(rows_per_gate), gate_bf16, int(token_tile),
+        int(splits), status_word(planes.device).data_ptr(), _stream(planes),
     )
-    _lib.check(rc, "tybok_w8a16_linear")
-    return y.reshape(*x.shape[:-1], n)
+    _lib.check(rc, "tybok_w8x3_linear")
+    return y, yp
 
 
-def _w8a16_geglu_cuda(x, w8_gate, scale_gate, w8_up, scale_up, token_tile, splits):
+def _w8x3_geglu_cuda(planes, shift, w8_gate, scale_gate, w8_up, scale_up, out_bf16, out_planes, out_shift, token_tile,
+                     splits):
     lib = _lib.load()
-    if x.dtype != torch.bfloat16:
-        raise TypeError(f"w8a16_geglu: x must be bf16, got {x.dtype}")
-    for w in (w8_gate, w8_up):
-        if w.dtype not in (torch.float8_e4m3fn, torch.uint8) or not w.is_contiguous():
-            raise TypeError("w8a16_geglu: weights must be contiguous e4m3 [I, K] tensors")
+    _check_w8(w8_gate, "w8x3_geglu")
+    _check_w8(w8_up, "w8x3_geglu")
     if w8_gate.shape != w8_up.shape:
-        raise ValueError("w8a16_geglu: gate and up weights differ in shape")
+        raise ValueError("w8x3_geglu: gate and up weights differ in shape")
+    if planes.dtype != torch.uint8 or planes.dim() != 3 or planes.shape[0] != 3 or not planes.is_contiguous():
+        raise TypeError("w8x3_geglu: planes must be a contiguous uint8 [3, M, K] tensor")
     i, k = w8_gate.shape
-    x2, m = _rows(x)
-    h = torch.empty((m, i), dtype=torch.bfloat16, device=x.device)
-    ws = workspace(x.device)
-    rc = lib.tybok_w8a16_geglu(
-        x2.data_ptr(), w8_gate.data_ptr(), scale_gate.data_ptr(), w8_up.data_ptr(), scale_up.data_ptr(), h.data_ptr(),
-        m, i, k, x2.stride(0), h.stride(0), int(token_tile), int(splits), ws.data_ptr(), ws.numel(),
-        status_word(x.device).data_ptr(), torch.cuda.current_stream(x.device).cuda_stream,
+    m = planes.shape[1]
+    if planes.shape[2] != k:
+        raise ValueError(f"w8x3_geglu: planes have K={planes.shape[2]}, weights have K={k}")
+    h, hp = _outputs(m, i, planes.device, out_bf16, out_planes)
+    rc = lib.tybok_w8x3_geglu(
+        planes.data_ptr(), int(shift), w8_gate.data_ptr(), scale_gate.data_ptr(), w8_up.data_ptr(),
+        scale_up.data_ptr(), h.data_ptr() if out_bf16 else None, i, hp.data_ptr() if out_planes else None,
+        int(out_shift), m, i, k, int(token_tile), int(splits), status_word(planes.device).data_ptr(), _stream(planes),
     )
-    _lib.check(rc, "tybok_w8a16_geglu")
-    return h.reshape(*x.shape[:-1], i)
+    _lib.check(rc, "tybok_w8x3_geglu")
+    return h, hp
 
 
-_L.impl("w8a16_linear", _w8a16_linear_cuda, "CUDA")
-_L.impl("w8a16_geglu", _w8a16_geglu_cuda, "CUDA")
+_L.impl("split3", _split3_cuda, "CUDA")
+_L.impl("w8x3_linear", _w8x3_linear_cuda, "CUDA")
+_L.impl("w8x3_geglu", _w8x3_geglu_cuda, "CUDA")
+
+
+def split3(x: torch.Tensor, shift: int = DEFAULT_SHIFT) -> torch.Tensor:
+    """bf16 ``[..., K]`` -> uint8 ``[3, M, K]`` e5m2 planes of ``x * 2**shift``."""
+    return torch.ops.tybok_b200.split3(x, shift)
+
+
+def w8x3_linear(planes, shift, w8, scale, bias=None, *, epilogue=EPI_NONE, residual=None, gate=None, rows_per_gate=1,
+                out_bf16=True, out_planes=False, out_shift=DEFAULT_SHIFT, token_tile=0, splits=0):
+    """W8 linear on activation planes; returns ``(y_bf16 [M,N], y_planes [3,M,N])`` (an output
+    that was not requested is an empty tensor).  See ``tybok_w8x3_linear`` in the C header."""
+    return torch.ops.tybok_b200.w8x3_linear(planes, shift, w8, scale, bias, epilogue, residual, gate, rows_per_gate,
+                                            out_bf16, out_planes, out_shift, token_tile, splits)
+
+
+def w8x3_geglu(planes, shift, w8_gate, scale_gate, w8_up, scale_up, *, out_bf16=True, out_planes=False,
+               out_shift=DEFAULT_SHIFT, token_tile=0, splits=0):
+    """``gelu_tanh(x@Wg.T) * (x@Wu.T)`` on activation planes; see ``tybok_w8x3_geglu``."""
+    return torch.ops.tybok_b200.w8x3_geglu(planes, shift, w8_gate, scale_gate, w8_up, scale_up, out_bf16, out_planes,
+                                           out_shift, token_tile, splits)
 
 
 def w8a16_linear(x, w8, scale, bias=None, *, epilogue=EPI_NONE, residual=None, gate=None, rows_per_gate=1,
-                 token_tile=0, splits=0) -> torch.Tensor:
-    """``epilogue(x @ (w8*scale).T + bias)`` in bf16; see ``tybok_w8a16_linear`` in the C header."""
-    return torch.ops.tybok_b200.w8a16_linear(x, w8, scale, bias, epilogue, residual, gate, rows_per_gate, token_tile,
-                                             splits)
+                 token_tile=0, splits=0, shift=DEFAULT_SHIFT) -> torch.Tensor:
+    """``epilogue(x @ (w8*scale).T + bias)`` for bf16 ``x``: ``split3`` then ``w8x3_linear``."""
+    y, _ = w8x3_linear(split3(x, shift), shift, w8, scale, bias, epilogue=epilogue, residual=residual, gate=gate,
+                       rows_per_gate=rows_per_gate, token_tile=token_tile, splits=splits)
+    return y.reshape(*x.shape[:-1], w8.shape[0])
 
 
-def w8a16_geglu(x, w8_gate, scale_gate, w8_up, scale_up, *, token_tile=0, splits=0) -> torch.Tensor:
-    """``gelu_tanh(x@Wg.T) * (x@Wu.T)`` in one launch; see ``tybok_w8a16_geglu``."""
-    return torch.ops.tybok_b200.w8a16_geglu(x, w8_gate, scale_gate, w8_up, scale_up, token_tile, splits)
+def w8a16_geglu(x, w8_gate, scale_gate, w8_up, scale_up, *, token_tile=0, splits=0, shift=DEFAULT_SHIFT):
+    """``gelu_tanh(x@Wg.T) * (x@Wu.T)`` for bf16 ``x``."""
+    h, _ = w8x3_geglu(split3(x, shift), shift, w8_gate, scale_gate, w8_up, scale_up, token_tile=token_tile,
+                      splits=splits)
+    return h.reshape(*x.shape[:-1], w8_gate.shape[0])
 
 
 def launch_count() -> int:
