@@ -100,10 +100,26 @@ int tybok_w8x3_geglu(const void* x_planes, int x_shift, const void* w8_gate, con
                      const float* scale_up, void* h, int64_t ldh, void* h_planes, int out_shift, int M, int I, int K,
                      int token_tile, int splits, int* status_word, void* stream);
 
+/* RMS normalisation feeding a W8 GEMM (fp32 statistics, one warp per row).
+ *   weight != NULL: plain Gemma norm    y = bf16(x * rsqrt(mean(x^2)+eps) * (1 + weight))
+ *   mod    != NULL: AdaRMS norm         y = bf16(x * rsqrt(mean(x^2)+eps) * (1 + scale) + shift),
+ *                   scale = mod[g, 0:W], shift = mod[g, W:2W], g = row / rows_per_group
+ *                   (mod is the precomputed dense(cond) output, fp32, row stride ldmod)
+ * Outputs: y (bf16, may be NULL) and/or y_planes ([3][M][W] planes of y * 2^out_shift).
+ * Replaces GemmaRMSNorm.forward (tybok/policies/pi05/models/layers.py:34-84) and the norm
+ * prologues of the reference's fused kernels (triton_expert_mlp.py:29-111). */
+int tybok_rmsnorm(const void* x, int64_t ldx, const float* weight, const float* mod, int64_t ldmod,
+                  int rows_per_group, int M, int W, float eps, void* y, int64_t ldy, void* y_planes,
+                  int out_shift, void* stream);
+
 /* Enable (1) / disable (0) programmatic dependent launch for every kernel of this library
  * (process-wide; default 1).  With it, a kernel's weight prefetch overlaps the tail of the
  * previous kernel in the stream. */
 void tybok_set_pdl(int enabled);
+
+/* Tuning aid: with a device buffer of 16 int64 per CTA of the following GEMM launches, the
+ * kernels record SM clock samples at their phase boundaries into it.  NULL (default) = off. */
+void tybok_debug_set_trace(void* device_buffer);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,128 @@
+"""The pi0.5-shaped policy on the GPU kernels against the CPU oracle (torch dequant path).
+
+Tolerances (BASELINE north_star): final action chunk with zero noise max-abs <= 2e-2;
+per-kernel outputs rel-L2 <= 1e-2.
+"""
+
+import os
+import sys
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+from make_golden import tiny_inputs  # noqa: E402
+
+from oracle import pi05_ref, w8_ref  # noqa: E402
+from tybok_b200.shapes import PI05_TINY  # noqa: E402
+from tybok_b200.weights import quantize_hot_linears, random_pi05_params  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("m,w,ada", [(50, 1024, True), (544, 2048, False), (7, 128, True), (3, 4096, False)])
+def test_rmsnorm_planes_and_bf16(m, w, ada):
+    """tybok/policies/pi05/models/layers.py:51-84 on the GPU: bf16 output bit-exact up to one
+    bf16 ulp of rounding-order difference, planes exactly equal to the bf16 output."""
+    from tybok_b200 import ops
+
+    g = torch.Generator().manual_seed(m + w)
+    x = torch.empty(m, w).normal_(0, 2, generator=g).to(torch.bfloat16)
+    if ada:
+        rows = 25 if m % 25 == 0 else m
+        mod = torch.empty(m // rows, 3 * w).normal_(0, 0.3, generator=g)
+        ref, _ = w8_ref.adarms_norm(x.view(m // rows, rows, w), mod)
+        ref = ref.reshape(m, w)
+        y, yp = ops.rmsnorm(x.cuda(), mod=mod.cuda(), rows_per_group=rows, out_bf16=True, out_planes=True, out_shift=4)
+    else:
+        weight = torch.empty(w).normal_(0, 0.3, generator=g)
+        ref = w8_ref.gemma_norm(x, weight)
+        y, yp = ops.rmsnorm(x.cuda(), weight=weight.cuda(), out_bf16=True, out_planes=True, out_shift=4)
+    y, yp = y.cpu(), yp.cpu()
+    assert w8_ref.rel_l2(y, ref) <= 2e-3
+    assert float((y.float() - ref.float()).abs().max()) <= 2 * float(ref.float().abs().max()) * 2.0**-8
+    got, want = yp.view(torch.float8_e5m2).float().sum(0), y.float() * 16.0
+    inside = want.abs() >= 2.0**-7
+    assert torch.equal(got[inside], want[inside])
+
+
+def _tiny_model():
+    from tybok_b200.pi05 import PI05Model
+
+    params = quantize_hot_linears(random_pi05_params(PI05_TINY, seed=0), PI05_TINY)
+    return params, PI05Model(params, PI05_TINY, device="cuda", vision_dtype=torch.float32)
+
+
+def test_tiny_policy_chunk_matches_oracle():
+    from tybok_b200 import ops
+
+    params, model = _tiny_model()
+    images, img_masks, tokens, masks, noise = tiny_inputs(PI05_TINY)
+    ref, inter = pi05_ref.sample_actions(params, PI05_TINY, images, img_masks, tokens, masks, noise,
+                                         return_intermediates=True)
+    cu = lambda ts: [t.cuda() for t in ts]  # noqa: E731
+    embs, pad = model.embed_prefix(cu(images), cu(img_masks), tokens.cuda(), masks.cuda())
+    assert w8_ref.rel_l2(embs.cpu(), inter["prefix_embs"].to(torch.bfloat16)) <= 1e-2
+    kv = model.prefill(embs, pad)
+    valid = pad[0].cpu()
+    for (k, v), (rk, rv) in zip(kv, inter["kv"]):
+        assert w8_ref.rel_l2(k.cpu()[0, :, valid], rk[0, :, valid]) <= 2e-2
+        assert w8_ref.rel_l2(v.cpu()[0, :, valid], rv[0, :, valid]) <= 2e-2
+    out = model.sample_actions(cu(images), cu(img_masks), tokens.cuda(), masks.cuda(), noise.cuda())
+    ops.check_status()
+    assert float((out.cpu() - ref).abs().max()) <= 2e-2
+    assert w8_ref.rel_l2(out.cpu(), ref) <= 2e-2
+
+
+def test_tiny_policy_batch2_and_graph_replay():
+    """Batched requests equal the oracle; a captured graph replays bit-identically and follows
+    new inputs (the reference's graph contract, tests/fastwam/graph_replay.py:200-330)."""
+    params, model = _tiny_model()
+    images, img_masks, tokens, masks, noise = tiny_inputs(PI05_TINY, seed=3, batch=2)
+    ref = pi05_ref.sample_actions(params, PI05_TINY, images, img_masks, tokens, masks, noise)
+    st = [[t.cuda() for t in images], [t.cuda() for t in img_masks], tokens.cuda(), masks.cuda(), noise.cuda()]
+    eager = model.sample_actions(*st)
+    assert float((eager.cpu() - ref).abs().max()) <= 2e-2
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        model.sample_actions(*st)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = model.sample_actions(*st)
+    graph.replay()
+    torch.cuda.synchronize()
+    first = out.clone()
+    assert torch.equal(first, eager)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, first)
+    st[4].copy_(torch.randn_like(st[4]))  # new noise through the static buffer
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, model.sample_actions(*st))
+    assert not torch.equal(out, first) and torch.isfinite(out).all()
+
+
+def test_engine_interface_on_synthetic_checkpoint():
+    from tybok_b200.engine import PI05B200Engine
+
+    eng = PI05B200Engine("synthetic:pi05_tiny", device="cuda", graph=True, seed=0)
+    spec = eng.describe()
+    assert spec["model_type"] == "pi05_b200" and spec["chunk_size"] == PI05_TINY.chunk and eng.graph_enabled
+    g = torch.Generator().manual_seed(1)
+    frame = eng.make_frame({c: torch.rand(3, 56, 56, generator=g) for c in spec["cameras"]},
+                           torch.rand(8, generator=g), "pick up the cube")
+    noise = torch.zeros(1, PI05_TINY.chunk, PI05_TINY.max_action_dim)
+    a = eng.predict_action_chunk(frame, noise=noise)
+    b = eng.predict_action_chunk(frame, noise=noise)
+    assert a.shape == (PI05_TINY.chunk, spec["action_dim"]) and (a == b).all() and abs(a).max() > 0
+    one = eng.select_action(frame, noise=noise)
+    assert (one == a[0]).all() and len(eng._queue) == PI05_TINY.chunk - 1
+    with pytest.raises(NotImplementedError):
+        PI05B200Engine("synthetic:pi05_tiny", device="cuda", tl_fused_expert=True)
+    with pytest.raises(NotImplementedError):
+        PI05B200Engine("synthetic:pi05_tiny", device="cuda", compile_model=True)
+    with pytest.raises(RuntimeError):
+        PI05B200Engine("synthetic:pi05_tiny", device="cuda", require_fused=True, action_fused=False)

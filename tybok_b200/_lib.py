@@ -20,6 +20,7 @@ SIGNATURES = {
     "tybok_last_error": (ctypes.c_char_p, []),
     "tybok_launch_count": (ctypes.c_longlong, []),
     "tybok_set_pdl": (None, [c_int]),
+    "tybok_debug_set_trace": (None, [c_void_p]),
     "tybok_split3": (c_int, [c_void_p, c_i64, c_void_p, c_int, c_int, c_int, c_void_p]),
     "tybok_w8x3_linear": (
         c_int,
@@ -31,6 +32,8 @@ SIGNATURES = {
         [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_i64, c_void_p, c_int, c_int, c_int,
          c_int, c_int, c_int, c_void_p, c_void_p],
     ),
+    "tybok_rmsnorm": (c_int, [c_void_p, c_i64, c_void_p, c_void_p, c_i64, c_int, c_int, c_int, ctypes.c_float,
+                              c_void_p, c_i64, c_void_p, c_int, c_void_p]),
     "tybok_w8a16_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "tybok_w8a16_linear": (
         c_int,

@@ -12,6 +12,7 @@ namespace host {
 static thread_local char g_err[512] = "";
 static std::atomic<int> g_pdl{1};
 static std::atomic<long long> g_launches{0};
+static std::atomic<long long*> g_trace{nullptr};
 
 int fail(int code, const char* msg) {
   std::snprintf(g_err, sizeof(g_err), "%s", msg);
@@ -67,6 +68,7 @@ int require_sm100() {
 }
 
 bool pdl_enabled() { return g_pdl.load(std::memory_order_relaxed) != 0; }
+long long* trace_buffer() { return g_trace.load(std::memory_order_relaxed); }
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -140,5 +142,6 @@ extern "C" {
 int tybok_version(void) { return 100; }
 const char* tybok_last_error(void) { return tb::host::last_error(); }
 void tybok_set_pdl(int enabled) { tb::host::g_pdl.store(enabled ? 1 : 0); }
+void tybok_debug_set_trace(void* device_buffer) { tb::host::g_trace.store(static_cast<long long*>(device_buffer)); }
 long long tybok_launch_count(void) { return tb::host::g_launches.load(); }
 }

@@ -1,0 +1,135 @@
+// RMS normalisation that feeds a W8 GEMM: one warp per token row, fp32 statistics, output as
+// the three e5m2 activation planes (and/or bf16).
+//
+// Two forms, both from tybok/policies/pi05/models/layers.py:34-84:
+//   plain Gemma norm   y = bf16( x * rsqrt(mean(x^2) + eps) * (1 + weight) )
+//   AdaRMS norm        y = bf16( x * rsqrt(mean(x^2) + eps) * (1 + scale) + shift )
+// where scale/shift are the first two thirds of a precomputed dense(cond) row
+// ([groups, 3*W] or [groups, 2*W], fp32), one row per group of `rows_per_group` tokens.
+// Algorithmic bytes per row: 2*W read, 3*W (+2*W) written.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "../../include/tybok_b200.h"
+#include "host_util.h"
+#include "ptx.cuh"
+#include "split3.cuh"
+
+namespace tb {
+
+constexpr int NORM_MAX_VEC = 16;  // 16 vectors of 8 elements per lane: W <= 4096
+
+struct NormParams {
+  const __nv_bfloat16* x;
+  long long ldx;
+  const float* weight;  // [W] or NULL
+  const float* mod;     // [groups, ldmod] or NULL; scale at [0,W), shift at [W,2W)
+  long long ldmod;
+  int rows_per_group;
+  int M, W;
+  float eps;
+  float plane_scale;
+  uint8_t* planes;       // [3][M][W] or NULL
+  __nv_bfloat16* y;      // [M, ldy] or NULL
+  long long ldy;
+  int pdl;
+};
+
+__global__ void __launch_bounds__(128) rmsnorm_kernel(const NormParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m = blockIdx.x * 4 + warp;
+  if (p.pdl) pdl_wait();
+  if (m < p.M) {
+    const int nvec = p.W / 8;  // 8-element vectors per row
+    const __nv_bfloat16* row = p.x + m * p.ldx;
+    float v[NORM_MAX_VEC][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_MAX_VEC; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nvec) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(row + c * 8);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          v[i][2 * e] = __bfloat162float(h[e].x);
+          v[i][2 * e + 1] = __bfloat162float(h[e].y);
+          ss += v[i][2 * e] * v[i][2 * e] + v[i][2 * e + 1] * v[i][2 * e + 1];
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float rstd = rsqrtf(ss / static_cast<float>(p.W) + p.eps);
+    const float* mod = p.mod ? p.mod + static_cast<long long>(m / p.rows_per_group) * p.ldmod : nullptr;
+    const long long plane = static_cast<long long>(p.M) * p.W;
+#pragma unroll
+    for (int i = 0; i < NORM_MAX_VEC; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nvec) {
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int k = c * 8 + e;
+          // x * rstd is formed in fp32 (the bf16 x promotes), as in the reference's _norm
+          float t = v[i][e] * rstd;
+          if (mod) t = t * (1.0f + mod[k]) + mod[p.W + k];
+          else if (p.weight) t = t * (1.0f + p.weight[k]);
+          o[e] = t;
+        }
+        __nv_bfloat162 b[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) b[e] = __floats2bfloat162_rn(o[2 * e], o[2 * e + 1]);
+        if (p.y) *reinterpret_cast<uint4*>(p.y + m * p.ldy + c * 8) = *reinterpret_cast<const uint4*>(b);
+        if (p.planes) {
+          const float lo[4] = {__bfloat162float(b[0].x) * p.plane_scale, __bfloat162float(b[0].y) * p.plane_scale,
+                               __bfloat162float(b[1].x) * p.plane_scale, __bfloat162float(b[1].y) * p.plane_scale};
+          const float hi[4] = {__bfloat162float(b[2].x) * p.plane_scale, __bfloat162float(b[2].y) * p.plane_scale,
+                               __bfloat162float(b[3].x) * p.plane_scale, __bfloat162float(b[3].y) * p.plane_scale};
+          uint2 w1, w2, w3;
+          split3_quad(lo, w1.x, w2.x, w3.x);
+          split3_quad(hi, w1.y, w2.y, w3.y);
+          uint8_t* dst = p.planes + static_cast<long long>(m) * p.W + c * 8;
+          *reinterpret_cast<uint2*>(dst) = w1;
+          *reinterpret_cast<uint2*>(dst + plane) = w2;
+          *reinterpret_cast<uint2*>(dst + 2 * plane) = w3;
+        }
+      }
+    }
+  }
+  if (p.pdl) pdl_launch_dependents();
+}
+
+}  // namespace tb
+
+extern "C" int tybok_rmsnorm(const void* x, int64_t ldx, const float* weight, const float* mod, int64_t ldmod,
+                             int rows_per_group, int M, int W, float eps, void* y, int64_t ldy, void* y_planes,
+                             int out_shift, void* stream) {
+  using namespace tb;
+  if (!x || (!y && !y_planes)) return host::fail(TYBOK_ERR_ARG, "rmsnorm: null pointer argument");
+  if (M <= 0 || W <= 0 || W % 8 != 0 || W > NORM_MAX_VEC * 256)
+    return host::fail(TYBOK_ERR_ARG, "rmsnorm: W must be a multiple of 8 and <= 4096");
+  if (ldx % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (y && ((reinterpret_cast<uintptr_t>(y) & 15) || ldy % 8 != 0)) ||
+      (y_planes && (reinterpret_cast<uintptr_t>(y_planes) & 7)))
+    return host::fail(TYBOK_ERR_ARG, "rmsnorm: rows must be 16-byte aligned (ld % 8 == 0)");
+  if (mod && rows_per_group <= 0) return host::fail(TYBOK_ERR_ARG, "rmsnorm: rows_per_group must be positive");
+  if (out_shift < -60 || out_shift > 60) return host::fail(TYBOK_ERR_ARG, "rmsnorm: exponent shift out of range");
+  if (int rc = host::require_sm100()) return rc;
+  NormParams p{};
+  p.x = static_cast<const __nv_bfloat16*>(x); p.ldx = ldx; p.weight = weight; p.mod = mod; p.ldmod = ldmod;
+  p.rows_per_group = rows_per_group > 0 ? rows_per_group : 1; p.M = M; p.W = W; p.eps = eps;
+  p.plane_scale = ldexpf(1.0f, out_shift); p.planes = static_cast<uint8_t*>(y_planes);
+  p.y = static_cast<__nv_bfloat16*>(y); p.ldy = ldy; p.pdl = host::pdl_enabled() ? 1 : 0;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((M + 3) / 4);
+  cfg.blockDim = dim3(128);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = p.pdl;
+  if (cudaLaunchKernelEx(&cfg, rmsnorm_kernel, p) != cudaSuccess) return host::fail_cuda("launch rmsnorm_kernel");
+  host::count_launch();
+  return TYBOK_OK;
+}

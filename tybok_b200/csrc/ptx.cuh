@@ -130,10 +130,11 @@ __device__ __forceinline__ uint32_t dsmem_addr(uint32_t local, uint32_t rank) {
 }
 __device__ __forceinline__ float4 ld_dsmem_f4(uint32_t addr) {
   float4 v;
+  // volatile (ordered after the cluster barrier, itself a volatile asm) but without a memory
+  // clobber, so that ordinary loads/stores around it can still be scheduled freely.
   asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
                : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "r"(addr)
-               : "memory");
+               : "r"(addr));
   return v;
 }
 

@@ -81,6 +81,7 @@ struct GemmParams {
   int rows_per_gate;
   int gate_bf16;
   int* status;
+  long long* trace;  // tuning aid: [CTA][16] SM-clock samples, NULL in production
 };
 
 struct __align__(8) Barriers {
@@ -106,19 +107,13 @@ __device__ __forceinline__ void fail(Barriers* b, int* status, int code) {
   if (status) atomicCAS(status, 0, code);
 }
 
-__device__ __forceinline__ float4 ld_stage(uint32_t local_addr, int rank, bool remote) {
-  if (remote) return ld_dsmem_f4(dsmem_addr(local_addr, rank));
-  float4 v;
-  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(local_addr));
-  return v;
-}
-
 __global__ void __launch_bounds__(THREADS, 1)
 w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1,
                const __grid_constant__ CUtensorMap tm_x, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ Barriers bars;
 
+  const long long t_start = clock64();
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
@@ -153,6 +148,10 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bars.tmem_base;
+  // Per-thread epilogue constants (4 consecutive channels), fetched while the main loop runs.
+  float s0[4] = {0, 0, 0, 0}, s1[4] = {0, 0, 0, 0}, b0[4] = {0, 0, 0, 0};
+  long long* tr = p.trace ? p.trace + 16ll * ((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) : nullptr;
+  if (tr && tid == 0) { tr[0] = t_start; tr[1] = clock64(); }
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -210,7 +209,9 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     bool ok = true;
     for (int i = 0; i < nkb; ++i) {
       const int s = i % ns;
+      const long long c0 = tr ? clock64() : 0;
       const bool ready = wait_or_abort(&bars.full[s], (i / ns) & 1, &bars.abort);
+      if (tr && leader) { const long long c1 = clock64(); tr[8] += c1 - c0; if (i == 0) tr[2] = c1; }
       if (!__all_sync(0xffffffffu, ready)) {
         if (lane == 0) fail(&bars, p.status, TYBOK_DEV_TIMEOUT_MMA);
         ok = false;
@@ -245,6 +246,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
       __syncwarp();
     }
     if (ok && leader) tc_commit(&bars.tmem_full);
+    if (tr && leader) tr[3] = clock64();
   } else {
     // ------------------------------------------------------------ epilogue, phase A
     // Accumulator (lane = channel, column = token) -> fp32 staging tile [w][token][128 channels]
@@ -254,8 +256,24 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     const int half = ew >> 2;
     const int row = q * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    {
+      const int n = n_tile * BN + ((tid - 64) & 31) * 4;
+      if (n < p.N) {  // weights-side data: independent of the previous kernel in the stream
+        const float4 t = *reinterpret_cast<const float4*>(p.scale0 + n);
+        s0[0] = t.x * p.out_scale; s0[1] = t.y * p.out_scale; s0[2] = t.z * p.out_scale; s0[3] = t.w * p.out_scale;
+        if (p.nw == 2) {
+          const float4 u = *reinterpret_cast<const float4*>(p.scale1 + n);
+          s1[0] = u.x * p.out_scale; s1[1] = u.y * p.out_scale; s1[2] = u.z * p.out_scale; s1[3] = u.w * p.out_scale;
+        }
+        if (p.bias0) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) b0[e] = __bfloat162float(p.bias0[n + e]);
+        }
+      }
+    }
     bool ok = __all_sync(0xffffffffu, wait_or_abort(&bars.tmem_full, 0, &bars.abort));
     if (!ok && lane == 0) fail(&bars, p.status, TYBOK_DEV_TIMEOUT_EPILOGUE);
+    if (tr && ew == 0 && lane == 0) tr[4] = clock64();
     if (ok) {
       tc_fence_after();
       float* stage = reinterpret_cast<float*>(smem);
@@ -285,6 +303,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
   }
 
   // ------------------------------------------------------------ meet: staging tiles complete
+  if (tr && tid == 64) tr[5] = clock64();
   tc_fence_before();
   if (p.splits > 1) {
     __syncwarp();
@@ -293,6 +312,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     __syncthreads();
   }
 
+  if (tr && tid == 64) tr[6] = clock64();
   if (warp >= 2 && !bars.abort) {
     // ---------------------------------------------------------- epilogue, phase B
     // 4 consecutive channels per thread, 8 token rows per pass; with split-K, rank r owns token
@@ -303,57 +323,73 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     const int rgrp = et >> 5;
     const int n = n_tile * BN + v4 * 4;
     const bool n_ok = n < p.N;  // N % 4 == 0, so all four channels are valid together
-    float s0[4] = {0, 0, 0, 0}, s1[4] = {0, 0, 0, 0}, b0[4] = {0, 0, 0, 0};
-    if (n_ok) {
-      const float4 t = *reinterpret_cast<const float4*>(p.scale0 + n);
-      s0[0] = t.x * p.out_scale; s0[1] = t.y * p.out_scale; s0[2] = t.z * p.out_scale; s0[3] = t.w * p.out_scale;
-      if (p.nw == 2) {
-        const float4 u = *reinterpret_cast<const float4*>(p.scale1 + n);
-        s1[0] = u.x * p.out_scale; s1[1] = u.y * p.out_scale; s1[2] = u.z * p.out_scale; s1[3] = u.w * p.out_scale;
-      }
-      if (p.bias0) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) b0[e] = __bfloat162float(p.bias0[n + e]);
-      }
-    }
     const int rank = p.splits > 1 ? static_cast<int>(cluster_ctarank()) : 0;
     const int rpr = (p.bt + p.splits - 1) / p.splits;
     const int r0 = rank * rpr, r1 = min(p.bt, r0 + rpr);
-    const uint32_t stage_addr = smem_u32(smem);
     const int m_base = t_tile * p.bt;
-    const bool remote = p.splits > 1;
-    for (int t = r0 + rgrp; t < r1; t += 8) {
-      const int m = m_base + t;
-      if (!n_ok || m >= p.M) continue;
-      float a0[4] = {0, 0, 0, 0}, a1[4] = {0, 0, 0, 0};
-      for (int sp = 0; sp < p.splits; ++sp) {  // rank order: bit-reproducible
-        const float4 f = ld_stage(stage_addr + (t * BN + v4 * 4) * 4, sp, remote);
-        a0[0] += f.x; a0[1] += f.y; a0[2] += f.z; a0[3] += f.w;
-        if (p.nw == 2) {
-          const float4 g = ld_stage(stage_addr + ((p.bt + t) * BN + v4 * 4) * 4, sp, remote);
-          a1[0] += g.x; a1[1] += g.y; a1[2] += g.z; a1[3] += g.w;
+    const float* stage = reinterpret_cast<const float*>(smem);
+    const uint32_t stage_addr = smem_u32(smem);
+    const long long plane = static_cast<long long>(p.M) * p.N;
+    // Rows are handled in batches of four (t, t+8, t+16, t+24): all staging loads of a batch are
+    // issued before any arithmetic, so their latencies overlap.
+    for (int tb = r0 + rgrp; tb < r1; tb += 32) {
+      float4 a0b[4], a1b[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int t = tb + 8 * u;
+        a0b[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        a1b[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (t >= r1 || m_base + t >= p.M || !n_ok) continue;
+        if (p.splits == 1) {
+          a0b[u] = *reinterpret_cast<const float4*>(stage + t * BN + v4 * 4);
+          if (p.nw == 2) a1b[u] = *reinterpret_cast<const float4*>(stage + (p.bt + t) * BN + v4 * 4);
+        } else {
+          const uint32_t off0 = stage_addr + (t * BN + v4 * 4) * 4;
+          const uint32_t off1 = stage_addr + ((p.bt + t) * BN + v4 * 4) * 4;
+          for (int sp = 0; sp < p.splits; ++sp) {  // rank order: bit-reproducible
+            const float4 f = ld_dsmem_f4(dsmem_addr(off0, sp));
+            a0b[u].x += f.x; a0b[u].y += f.y; a0b[u].z += f.z; a0b[u].w += f.w;
+            if (p.nw == 2) {
+              const float4 g = ld_dsmem_f4(dsmem_addr(off1, sp));
+              a1b[u].x += g.x; a1b[u].y += g.y; a1b[u].z += g.z; a1b[u].w += g.w;
+            }
+          }
         }
       }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+      const int t = tb + 8 * u;
+      const int m = m_base + t;
+      if (t >= r1 || !n_ok || m >= p.M) continue;
+      const float4 a0 = a0b[u], a1 = a1b[u];
       // Every rounding point is the one the reference's bf16 torch modules have: linear output,
       // GELU output, product, gated value, residual sum.
-      float o[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) o[e] = bf16_round(a0[e] * s0[e] + b0[e]);
+      float o[4] = {bf16_round(a0.x * s0[0] + b0[0]), bf16_round(a0.y * s0[1] + b0[1]),
+                    bf16_round(a0.z * s0[2] + b0[2]), bf16_round(a0.w * s0[3] + b0[3])};
       if (p.epi == EPI_GELU) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[e] = gelu_tanh_fast(o[e]);
       } else if (p.epi == EPI_GEGLU) {
+        const float u[4] = {bf16_round(a1.x * s1[0]), bf16_round(a1.y * s1[1]), bf16_round(a1.z * s1[2]),
+                            bf16_round(a1.w * s1[3])};
 #pragma unroll
-        for (int e = 0; e < 4; ++e) o[e] = bf16_round(gelu_tanh_fast(o[e])) * bf16_round(a1[e] * s1[e]);
+        for (int e = 0; e < 4; ++e) o[e] = bf16_round(gelu_tanh_fast(o[e])) * u[e];
       } else if (p.epi == EPI_RESIDUAL) {
         if (p.gate) {
           const long long gi = static_cast<long long>(m / p.rows_per_gate) * p.ldgate + n;
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float gv = p.gate_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.gate)[gi + e])
-                                         : bf16_round(static_cast<const float*>(p.gate)[gi + e]);
-            o[e] = bf16_round(o[e] * gv);
+          float gv[4];
+          if (p.gate_bf16) {
+            const uint2 gr = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(p.gate) + gi);
+            const __nv_bfloat162 g01 = *reinterpret_cast<const __nv_bfloat162*>(&gr.x);
+            const __nv_bfloat162 g23 = *reinterpret_cast<const __nv_bfloat162*>(&gr.y);
+            gv[0] = __bfloat162float(g01.x); gv[1] = __bfloat162float(g01.y);
+            gv[2] = __bfloat162float(g23.x); gv[3] = __bfloat162float(g23.y);
+          } else {
+            const float4 gr = *reinterpret_cast<const float4*>(static_cast<const float*>(p.gate) + gi);
+            gv[0] = bf16_round(gr.x); gv[1] = bf16_round(gr.y); gv[2] = bf16_round(gr.z); gv[3] = bf16_round(gr.w);
           }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) o[e] = bf16_round(o[e] * gv[e]);
         }
         const uint2 rr = *reinterpret_cast<const uint2*>(p.res + static_cast<long long>(m) * p.ldres + n);
         const __nv_bfloat162 r01 = *reinterpret_cast<const __nv_bfloat162*>(&rr.x);
@@ -375,15 +411,16 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
                              __bfloat162float(o23.x) * p.plane_scale, __bfloat162float(o23.y) * p.plane_scale};
         uint32_t w1, w2, w3;
         split3_quad(xs, w1, w2, w3);
-        const long long plane = static_cast<long long>(p.M) * p.N;
         uint8_t* dst = p.y_planes + static_cast<long long>(m) * p.N + n;
         *reinterpret_cast<uint32_t*>(dst) = w1;
         *reinterpret_cast<uint32_t*>(dst + plane) = w2;
         *reinterpret_cast<uint32_t*>(dst + 2 * plane) = w3;
       }
+      }
     }
   }
 
+  if (tr && tid == 64) tr[7] = clock64();
   // Peers may still be reading this CTA's staging tile: leave together.
   if (p.splits > 1) {
     __syncwarp();
@@ -517,6 +554,7 @@ static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, co
   p.res = static_cast<const __nv_bfloat16*>(res); p.ldres = ldres;
   p.gate = gate; p.ldgate = ldgate; p.rows_per_gate = rows_per_gate > 0 ? rows_per_gate : 1; p.gate_bf16 = gate_bf16;
   p.status = status;
+  p.trace = host::trace_buffer();
 
   static bool attr_set[64] = {};
   const int dev = host::current_device();

@@ -31,6 +31,9 @@ _L.define(
     "bool out_bf16, bool out_planes, int out_shift, int token_tile, int splits) -> (Tensor, Tensor)"
 )
 
+_L.define("rmsnorm(Tensor x, Tensor? weight, Tensor? mod, int rows_per_group, float eps, bool out_bf16, "
+          "bool out_planes, int out_shift) -> (Tensor, Tensor)")
+
 _status: dict[int, torch.Tensor] = {}
 
 
@@ -154,6 +157,28 @@ def _w8x3_geglu_cuda(planes, shift, w8_gate, scale_gate, w8_up, scale_up, out_bf
     return h, hp
 
 
+def _rmsnorm_cuda(x, weight, mod, rows_per_group, eps, out_bf16, out_planes, out_shift):
+    lib = _lib.load()
+    if x.dtype != torch.bfloat16:
+        raise TypeError(f"rmsnorm: x must be bf16, got {x.dtype}")
+    x2 = _rows(x)
+    m, w = x2.shape
+    if weight is not None and (weight.dtype != torch.float32 or weight.numel() != w or not weight.is_contiguous()):
+        raise TypeError("rmsnorm: weight must be contiguous fp32 [W]")
+    ldmod = 0
+    if mod is not None:
+        if mod.dtype != torch.float32 or mod.stride(-1) != 1 or mod.shape[-1] < 2 * w:
+            raise TypeError("rmsnorm: mod must be fp32 [groups, >= 2*W] with unit inner stride")
+        ldmod = mod.stride(-2) if mod.dim() > 1 else mod.shape[-1]
+    y, yp = _outputs(m, w, x.device, out_bf16, out_planes)
+    rc = lib.tybok_rmsnorm(x2.data_ptr(), x2.stride(0), _ptr(weight), _ptr(mod), ldmod, int(rows_per_group), m, w,
+                           float(eps), y.data_ptr() if out_bf16 else None, w, yp.data_ptr() if out_planes else None,
+                           int(out_shift), _stream(x))
+    _lib.check(rc, "tybok_rmsnorm")
+    return y, yp
+
+
+_L.impl("rmsnorm", _rmsnorm_cuda, "CUDA")
 _L.impl("split3", _split3_cuda, "CUDA")
 _L.impl("w8x3_linear", _w8x3_linear_cuda, "CUDA")
 _L.impl("w8x3_geglu", _w8x3_geglu_cuda, "CUDA")
@@ -192,6 +217,13 @@ def w8a16_geglu(x, w8_gate, scale_gate, w8_up, scale_up, *, token_tile=0, splits
     h, _ = w8x3_geglu(split3(x, shift), shift, w8_gate, scale_gate, w8_up, scale_up, token_tile=token_tile,
                       splits=splits)
     return h.reshape(*x.shape[:-1], w8_gate.shape[0])
+
+
+def rmsnorm(x, weight=None, mod=None, *, rows_per_group=1, eps=1e-6, out_bf16=False, out_planes=True,
+            out_shift=DEFAULT_SHIFT):
+    """Gemma RMSNorm (``weight``) or AdaRMS norm (``mod`` = precomputed ``dense(cond)``); returns
+    ``(y_bf16, y_planes)``; see ``tybok_rmsnorm``."""
+    return torch.ops.tybok_b200.rmsnorm(x, weight, mod, rows_per_group, eps, out_bf16, out_planes, out_shift)
 
 
 def launch_count() -> int:

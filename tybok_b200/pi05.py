@@ -1,0 +1,275 @@
+"""pi0.5-shaped policy on the B200 kernels: VLM prefix prefill + action-expert Euler loop.
+
+Structure follows the reference's eager path (tybok/policies/pi05/models/flow_matching.py:761-838,
+505-556; gemma.py:61-125; layers.py:268-308) with these substitutions on the hot path:
+
+* every decoder linear is an e4m3 weight with per-channel fp32 scale run by the W8 GEMM of
+  this package (q/k/v are packed into one weight, as the reference's ``--tl-llm-flash-attn``
+  tier does, layers.py:207-214);
+* the RMS / AdaRMS norms write the GEMM's activation planes directly; gate/up/GELU/multiply is
+  one kernel that writes the planes of the FFN intermediate, so the down projection reads it
+  without a bf16 round trip; residual adds (and AdaRMS gates) are GEMM epilogues;
+* per-step constants (time embedding -> AdaRMS conditioning -> per-layer modulations) are
+  precomputed once, exactly as the reference's graph path does (flow_matching.py:321-407).
+
+The SigLIP tower, the projector, the embedding lookup and the fp32 action/time projections
+are not part of the fp8 path; they run as torch ops.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F  # noqa: N812
+
+from . import ops
+from .shapes import GemmaSpec, PI05Shape
+from .weights import EXPERT, PROJECTOR, VISION, VLM, quantize_w8
+
+#: Exponent shifts of the activation planes per producer (planes hold value * 2**shift and are
+#: exact for |value * 2**shift| in [2**-7, 57344]).
+SHIFT_NORMED = 4  # RMS-normalised activations, O(1)
+SHIFT_ATTN = 6  # attention outputs (convex combinations of V rows)
+SHIFT_FFN = 4  # gelu(gate) * up
+
+
+class _Layer:
+    """Packed weights of one Gemma decoder layer."""
+
+    __slots__ = ("qkv", "o", "gate", "up", "down", "norm_in", "norm_post")
+
+
+def _q(params: dict, name: str, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """(e4m3 weight, fp32 scale) of ``name``: taken as stored when the checkpoint is fp8
+    (``<name>.scale_weight`` present), quantised with the reference recipe otherwise."""
+    w = params[f"{name}.weight"]
+    if w.dtype == torch.float8_e4m3fn:
+        return w.to(device).contiguous(), params[f"{name}.scale_weight"].to(device).float().contiguous()
+    w8, s = quantize_w8(w.to(device))
+    return w8, s
+
+
+def _pack_decoder(params: dict, root: str, spec: GemmaSpec, adarms: bool, device) -> list[_Layer]:
+    layers = []
+    for i in range(spec.depth):
+        base = f"{root}.layers.{i}"
+        lay = _Layer()
+        q, k, v = (_q(params, f"{base}.self_attn.{n}_proj", device) for n in ("q", "k", "v"))
+        lay.qkv = (torch.cat([q[0].view(torch.uint8), k[0].view(torch.uint8), v[0].view(torch.uint8)]).contiguous(),
+                   torch.cat([q[1], k[1], v[1]]).contiguous())
+        lay.o = _q(params, f"{base}.self_attn.o_proj", device)
+        lay.gate = _q(params, f"{base}.mlp.gate_proj", device)
+        lay.up = _q(params, f"{base}.mlp.up_proj", device)
+        lay.down = _q(params, f"{base}.mlp.down_proj", device)
+        if adarms:
+            lay.norm_in = (params[f"{base}.input_layernorm.dense.weight"].to(device).float(),
+                           params[f"{base}.input_layernorm.dense.bias"].to(device).float())
+            lay.norm_post = (params[f"{base}.post_attention_layernorm.dense.weight"].to(device).float(),
+                             params[f"{base}.post_attention_layernorm.dense.bias"].to(device).float())
+        else:
+            lay.norm_in = params[f"{base}.input_layernorm.weight"].to(device).float().contiguous()
+            lay.norm_post = params[f"{base}.post_attention_layernorm.weight"].to(device).float().contiguous()
+        layers.append(lay)
+    return layers
+
+
+def _rope_table(head_dim: int, max_pos: int, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """cos/sin ``[max_pos, D]`` in bf16 from bf16-rounded inverse frequencies
+    (tybok/policies/pi05/models/rope.py:24-46,55-64)."""
+    inv = 1.0 / (10000.0 ** (torch.arange(0, head_dim, 2, dtype=torch.int64).float() / head_dim))
+    inv = inv.to(torch.bfloat16).float().to(device)
+    freqs = torch.arange(max_pos, dtype=torch.float32, device=device)[:, None] * inv[None, :]
+    emb = torch.cat((freqs, freqs), dim=-1)
+    return emb.cos().to(torch.bfloat16), emb.sin().to(torch.bfloat16)
+
+
+def _additive(allowed: torch.Tensor) -> torch.Tensor:
+    """Boolean mask -> additive bf16 mask with the reference's large finite negative
+    (flow_matching.py:24,179-182): a fully masked (padding) query row then softmaxes to a
+    uniform, finite row instead of NaN, exactly as in the reference."""
+    return torch.where(allowed, 0.0, -2.3819763e38).to(torch.bfloat16)
+
+
+def _rotate_half(x: torch.Tensor) -> torch.Tensor:
+    h = x.shape[-1] // 2
+    return torch.cat((-x[..., h:], x[..., :h]), dim=-1)
+
+
+class PI05Model:
+    """Weights + forward of a pi0.5-shaped policy on one GPU (inference only)."""
+
+    def __init__(self, params: dict[str, torch.Tensor], shape: PI05Shape, device: str = "cuda",
+                 vision_dtype: torch.dtype = torch.bfloat16):
+        if not str(device).startswith("cuda"):
+            raise RuntimeError("tybok_b200 has no CPU path: PI05Model needs a CUDA (sm_100) device")
+        self.shape = shape
+        self.device = torch.device(device)
+        dev = self.device
+        self.vision_dtype = vision_dtype
+        self.vision = {k: v.to(dev, vision_dtype) for k, v in params.items() if k.startswith(VISION)}
+        self.proj_w = params[f"{PROJECTOR}.weight"].to(dev, vision_dtype)
+        self.proj_b = params[f"{PROJECTOR}.bias"].to(dev, vision_dtype)
+        self.embed = params[f"{VLM}.embed_tokens.weight"].to(dev)
+        self.embed_scale = torch.tensor(shape.vlm.width**0.5, dtype=self.embed.dtype, device=dev)
+        self.vlm_layers = _pack_decoder(params, VLM, shape.vlm, False, dev)
+        self.exp_layers = _pack_decoder(params, EXPERT, shape.expert, True, dev)
+        self.final_norm = (params[f"{EXPERT}.norm.dense.weight"].to(dev).float(),
+                           params[f"{EXPERT}.norm.dense.bias"].to(dev).float())
+        f32 = lambda n: params[n].to(dev).float()  # noqa: E731
+        self.action_in = (f32("action_in_proj.weight"), f32("action_in_proj.bias"))
+        self.action_out = (f32("action_out_proj.weight"), f32("action_out_proj.bias"))
+        self.time_in = (f32("time_mlp_in.weight"), f32("time_mlp_in.bias"))
+        self.time_out = (f32("time_mlp_out.weight"), f32("time_mlp_out.bias"))
+        self.cos, self.sin = _rope_table(shape.vlm.head_dim, shape.prefix_len + shape.chunk + 8, dev)
+        self._precompute_step_constants()
+
+    # ------------------------------------------------------------------ constants
+    def _precompute_step_constants(self) -> None:
+        """Per-step AdaRMS modulations ``dense(silu(time_mlp_out(silu(time_mlp_in(temb)))))``
+        for every expert norm: ``mods[step][layer] = (in [1,3W], post [1,3W])`` and the final
+        norm's ``[1,3W]`` (tybok/policies/pi05/models/flow_matching.py:321-407)."""
+        s = self.shape
+        w = s.expert.width
+        dt = -1.0 / s.steps
+        times = torch.tensor([1.0 + i * dt for i in range(s.steps)], dtype=torch.float32)
+        frac = torch.linspace(0.0, 1.0, w // 2, dtype=torch.float64)
+        period = s.min_period * (s.max_period / s.min_period) ** frac
+        ang = (1.0 / period * 2 * math.pi)[None, :] * times[:, None]
+        temb = torch.cat([torch.sin(ang), torch.cos(ang)], dim=1).float().to(self.device)
+        cond = F.silu(F.linear(F.silu(F.linear(temb, *self.time_in)), *self.time_out))  # [steps, W]
+        self.mods = []
+        for i in range(s.steps):
+            c = cond[i : i + 1]
+            self.mods.append([(F.linear(c, *lay.norm_in).contiguous(), F.linear(c, *lay.norm_post).contiguous())
+                              for lay in self.exp_layers])
+        self.final_mods = [F.linear(cond[i : i + 1], *self.final_norm).contiguous() for i in range(s.steps)]
+
+    # ------------------------------------------------------------------ non-fp8 front end
+    def embed_image(self, image: torch.Tensor) -> torch.Tensor:
+        """SigLIP tower + projector (torch ops; tybok/policies/pi05/models/vision.py:200-289)."""
+        v, p, dt = self.shape.vision, self.vision, self.vision_dtype
+        x = F.conv2d(image.to(dt), p[f"{VISION}.embeddings.patch_embedding.weight"],
+                     p[f"{VISION}.embeddings.patch_embedding.bias"], stride=v.patch)
+        x = x.flatten(2).transpose(1, 2) + p[f"{VISION}.embeddings.position_embedding.weight"][None]
+        b, l, hid = x.shape
+        hd = hid // v.heads
+        for i in range(v.layers):
+            base = f"{VISION}.encoder.layers.{i}"
+            h = F.layer_norm(x, (hid,), p[f"{base}.layer_norm1.weight"], p[f"{base}.layer_norm1.bias"], 1e-6)
+            q = F.linear(h, p[f"{base}.self_attn.q_proj.weight"], p[f"{base}.self_attn.q_proj.bias"])
+            k = F.linear(h, p[f"{base}.self_attn.k_proj.weight"], p[f"{base}.self_attn.k_proj.bias"])
+            val = F.linear(h, p[f"{base}.self_attn.v_proj.weight"], p[f"{base}.self_attn.v_proj.bias"])
+            q, k, val = (t.view(b, l, v.heads, hd).transpose(1, 2) for t in (q, k, val))
+            a = F.scaled_dot_product_attention(q, k, val, scale=hd**-0.5).transpose(1, 2).reshape(b, l, hid)
+            x = x + F.linear(a, p[f"{base}.self_attn.out_proj.weight"], p[f"{base}.self_attn.out_proj.bias"])
+            h = F.layer_norm(x, (hid,), p[f"{base}.layer_norm2.weight"], p[f"{base}.layer_norm2.bias"], 1e-6)
+            h = F.gelu(F.linear(h, p[f"{base}.mlp.fc1.weight"], p[f"{base}.mlp.fc1.bias"]), approximate="tanh")
+            x = x + F.linear(h, p[f"{base}.mlp.fc2.weight"], p[f"{base}.mlp.fc2.bias"])
+        x = F.layer_norm(x, (hid,), p[f"{VISION}.post_layernorm.weight"], p[f"{VISION}.post_layernorm.bias"], 1e-6)
+        return F.linear(x, self.proj_w, self.proj_b)
+
+    def embed_prefix(self, images, img_masks, tokens, masks) -> tuple[torch.Tensor, torch.Tensor]:
+        """Prefix embeddings ``[B, L, W]`` bf16 and pad mask ``[B, L]`` bool
+        (flow_matching.py:410-461; paligemma_with_expert.py:134-161)."""
+        embs, pads = [], []
+        # all cameras in one tower pass: [n_cams*B, 3, H, W]
+        feats = self.embed_image(torch.cat(list(images), dim=0)).to(torch.bfloat16)
+        b = tokens.shape[0]
+        for i, m in enumerate(img_masks):
+            e = feats[i * b : (i + 1) * b]
+            embs.append(e)
+            pads.append(m[:, None].expand(b, e.shape[1]))
+        embs.append(F.embedding(tokens, self.embed) * self.embed_scale)
+        pads.append(masks.bool())
+        return torch.cat(embs, dim=1), torch.cat(pads, dim=1)
+
+    # ------------------------------------------------------------------ decoder pieces
+    def _rope(self, t: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+        """t ``[B, L, H, D]`` bf16, pos ``[B, L]`` -> rotate-half RoPE in bf16 (rope.py:67-75)."""
+        cos = self.cos[pos][:, :, None, :]
+        sin = self.sin[pos][:, :, None, :]
+        return t * cos + _rotate_half(t) * sin
+
+    def _attention(self, spec: GemmaSpec, qkv: torch.Tensor, b: int, l: int, pos, mask, prefix_kv):
+        """Packed qkv ``[B*L, (H+2Hkv)*D]`` -> attention output ``[B*L, H*D]`` and this layer's
+        post-RoPE ``(K, V)`` ``[B, Hkv, L, D]``.  GQA over ``[prefix ; own]`` keys with a boolean
+        mask (layers.py:145-191).  torch SDPA for now (library call)."""
+        h, g, d = spec.num_heads, spec.num_kv_heads, spec.head_dim
+        qkv = qkv.view(b, l, h + 2 * g, d)
+        q = self._rope(qkv[:, :, :h], pos).transpose(1, 2)
+        k = self._rope(qkv[:, :, h : h + g], pos).transpose(1, 2)
+        v = qkv[:, :, h + g :].transpose(1, 2)
+        kk, vv = k, v
+        if prefix_kv is not None:
+            kk = torch.cat([prefix_kv[0], k], dim=2)
+            vv = torch.cat([prefix_kv[1], v], dim=2)
+        a = F.scaled_dot_product_attention(q, kk, vv, attn_mask=mask, scale=d**-0.5, enable_gqa=(g != h))
+        return a.transpose(1, 2).reshape(b * l, h * d), k, v
+
+    def _layer(self, spec, lay: _Layer, x, b, l, pos, mask, prefix_kv, mods):
+        """One decoder layer on ``x [B*L, W]`` bf16 (layers.py:268-308). ``mods`` is None for the
+        VLM (plain norms) or ``(mod_in, mod_post)`` ``[1, 3W]`` AdaRMS modulations."""
+        w = spec.width
+        m = x.shape[0]
+        if mods is None:
+            _, xp = ops.rmsnorm(x, weight=lay.norm_in, out_shift=SHIFT_NORMED)
+            gate_in = gate_post = None
+        else:
+            _, xp = ops.rmsnorm(x, mod=mods[0], rows_per_group=m, out_shift=SHIFT_NORMED)
+            gate_in, gate_post = mods[0][:, 2 * w :], mods[1][:, 2 * w :]
+        qkv, _ = ops.w8x3_linear(xp, SHIFT_NORMED, *lay.qkv)
+        a, k, v = self._attention(spec, qkv, b, l, pos, mask, prefix_kv)
+        ap = ops.split3(a, SHIFT_ATTN)
+        x, _ = ops.w8x3_linear(ap, SHIFT_ATTN, *lay.o, epilogue=ops.EPI_RESIDUAL, residual=x, gate=gate_in,
+                               rows_per_gate=m)
+        if mods is None:
+            _, xp = ops.rmsnorm(x, weight=lay.norm_post, out_shift=SHIFT_NORMED)
+        else:
+            _, xp = ops.rmsnorm(x, mod=mods[1], rows_per_group=m, out_shift=SHIFT_NORMED)
+        _, hp = ops.w8x3_geglu(xp, SHIFT_NORMED, *lay.gate, *lay.up, out_bf16=False, out_planes=True,
+                               out_shift=SHIFT_FFN)
+        x, _ = ops.w8x3_linear(hp, SHIFT_FFN, *lay.down, epilogue=ops.EPI_RESIDUAL, residual=x, gate=gate_post,
+                               rows_per_gate=m)
+        return x, k, v
+
+    # ------------------------------------------------------------------ prefix + denoise
+    def prefill(self, prefix_embs: torch.Tensor, pad: torch.Tensor):
+        """VLM prefix pass collecting per-layer post-RoPE (K, V) (gemma.py:61-125, use_cache)."""
+        spec = self.shape.vlm
+        b, l, w = prefix_embs.shape
+        mask = _additive(pad[:, None, :, None] & pad[:, None, None, :])  # [B,1,L,L]: all-zero att masks
+        pos = torch.cumsum(pad, dim=1) - 1
+        pos = pos.clamp_min(0)
+        x = prefix_embs.reshape(b * l, w)
+        kv = []
+        for lay in self.vlm_layers:
+            x, k, v = self._layer(spec, lay, x, b, l, pos, mask, None, None)
+            kv.append((k, v))
+        return kv
+
+    def denoise_step(self, step: int, x_t: torch.Tensor, pad: torch.Tensor, kv) -> torch.Tensor:
+        """One expert pass -> velocity ``[B, chunk, A]`` fp32 (flow_matching.py:505-556)."""
+        s = self.shape
+        spec = s.expert
+        b, l = x_t.shape[0], x_t.shape[1]
+        x = F.linear(x_t, *self.action_in).to(torch.bfloat16).reshape(b * l, spec.width)
+        mask = _additive(torch.cat([pad[:, None, None, :].expand(b, 1, l, pad.shape[1]),
+                                    torch.ones(b, 1, l, l, dtype=torch.bool, device=x.device)], dim=3))
+        pos = pad.sum(dim=-1, keepdim=True) + torch.arange(l, device=x.device)[None, :]
+        for i, lay in enumerate(self.exp_layers):
+            x, _, _ = self._layer(spec, lay, x, b, l, pos, mask, kv[i], self.mods[step][i])
+        y, _ = ops.rmsnorm(x, mod=self.final_mods[step], rows_per_group=b * l, out_bf16=True, out_planes=False)
+        y = y.view(b, l, spec.width)[:, -s.chunk :].float()
+        return F.linear(y, *self.action_out)
+
+    @torch.no_grad()
+    def sample_actions(self, images, img_masks, tokens, masks, noise: torch.Tensor) -> torch.Tensor:
+        """Prefix prefill + ``steps`` forward-Euler updates from ``noise`` (flow_matching.py:761-838)."""
+        embs, pad = self.embed_prefix(images, img_masks, tokens, masks)
+        kv = self.prefill(embs, pad)
+        dt = -1.0 / self.shape.steps
+        x_t = noise
+        for step in range(self.shape.steps):
+            x_t = x_t + dt * self.denoise_step(step, x_t, pad, kv)
+        return x_t
