@@ -1,0 +1,303 @@
+"""Benchmark of the fp8 hot path: pi0.5-shaped action-chunk latency on B200 (BASELINE config 2).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--batch B]
+    torchrun --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One "step" = one action chunk (prefix prefill + 10 denoise steps) of the pi0.5-shaped random-init
+fp8 policy on synthetic inputs.  ``value`` is the p50 of K CUDA-event-timed graph replays with
+inputs resident in HBM; ``e2e`` is the same chunk through ``engine.predict_action_chunk`` from
+host frames (pinned H2D of images/tokens/noise and D2H of the chunk inside the timed region).
+With N > 1 every rank runs an independent replica (no data-path collective); the time is the
+max over ranks.  ``--impl reference`` times the CPU oracle (the reference's eager torch path on
+dequantised weights) on the host cores.  Prints one JSON line on rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "pi05_fp8_action_chunk_p50_ms"
+WORKLOAD = "pi05_full: SigLIP-So400m 2x224^2 + Gemma-2B prefix (544 tok) + Gemma-300M expert, chunk 50, 10 steps"
+
+
+def _peaks() -> tuple[dict, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return json.load(open(path)), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz, self._halt = index, [], set(), None, threading.Event()
+
+    def run(self):
+        try:
+            import pynvml as nv
+
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            names = {nv.nvmlClocksEventReasonHwSlowdown: "hw_slowdown",
+                     nv.nvmlClocksEventReasonHwThermalSlowdown: "hw_thermal_slowdown",
+                     nv.nvmlClocksEventReasonSwThermalSlowdown: "sw_thermal_slowdown",
+                     nv.nvmlClocksEventReasonSwPowerCap: "sw_power_cap"}
+            while not self._halt.is_set():
+                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                self.reasons |= {n for bit, n in names.items() if mask & bit}
+                time.sleep(0.02)
+        except Exception as e:  # NVML missing: report that instead of clocks
+            self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
+
+    def stop(self) -> dict:
+        self._halt.set()
+        self.join(timeout=2)
+        med = statistics.median(self.samples) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+def _synthetic_frame(engine, seed: int):
+    spec = engine.describe()
+    g = torch.Generator().manual_seed(seed)
+    images = {c: torch.rand(3, spec["resize"][1], spec["resize"][0], generator=g).pin_memory() for c in spec["cameras"]}
+    frame = engine.make_frame(images, torch.randn(8, generator=g), "pick up the red block")
+    s = engine.config.shape
+    frame["observation.language.tokens"] = torch.randint(0, s.vocab, (s.lang_len,), generator=g)
+    frame["observation.language.attention_mask"] = torch.ones(s.lang_len, dtype=torch.bool)
+    return frame
+
+
+def _gemm_roofline(engine, peaks, peaks_kind) -> dict:
+    """One extra eager chunk with every W8 GEMM launch bracketed by CUDA events on the launching
+    stream: achieved = sum of algorithmic bytes (N*K + 4N + 2MK + 2MN per launch; gated form two
+    weight matrices) / sum of launch durations."""
+    from tybok_b200 import ops
+
+    lib = ops._lib.load()
+    lib.tybok_set_pdl(0)  # serialise launches so an event pair brackets exactly one kernel
+    rec = []
+    orig_lin, orig_geglu = ops.w8x3_linear, ops.w8x3_geglu
+
+    def timed(fn, nw):
+        def wrapper(planes, shift, w8, *a, **kw):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = fn(planes, shift, w8, *a, **kw)
+            e1.record()
+            m, k, n = planes.shape[1], planes.shape[2], w8.shape[0]
+            rec.append((e0, e1, nw * (n * k + 4 * n) + 2 * m * k + 2 * m * n, 2.0 * nw * m * n * k))
+            return out
+        return wrapper
+
+    import tybok_b200.pi05 as P
+
+    P.ops.w8x3_linear, P.ops.w8x3_geglu = timed(orig_lin, 1), timed(orig_geglu, 2)
+    try:
+        engine.model.sample_actions(*engine._dummy_inputs(engine.batch_size))
+        torch.cuda.synchronize()
+        rec.clear()
+        engine.model.sample_actions(*engine._dummy_inputs(engine.batch_size))
+        torch.cuda.synchronize()
+    finally:
+        P.ops.w8x3_linear, P.ops.w8x3_geglu = orig_lin, orig_geglu
+        lib.tybok_set_pdl(1)
+    ms = sum(a.elapsed_time(b) for a, b, _, _ in rec)
+    byts = sum(r[2] for r in rec)
+    flops = sum(r[3] for r in rec)
+    achieved = byts / (ms * 1e-3) / 1e9
+    return {"bound": "hbm", "kernel": "w8_gemm_kernel", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
+            "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None, "peak_source": peaks_kind,
+            "launches": len(rec), "gemm_ms_per_chunk": round(ms, 3), "algorithmic_bytes": byts,
+            "tensor_tflops": round(flops / (ms * 1e-3) / 1e12, 1)}
+
+
+def _cpu_chunk_times(reps: int, seed: int = 0) -> tuple[list[float], dict]:
+    """Time the CPU oracle (reference eager path on dequantised weights) on the full config."""
+    from oracle import pi05_ref
+    from tybok_b200.shapes import PI05_FULL
+    from tybok_b200.weights import quantize_hot_linears, random_pi05_params
+
+    dev = "cuda" if torch.cuda.is_available() else "cpu"  # weights are generated where it is fast
+    params = quantize_hot_linears(random_pi05_params(PI05_FULL, seed=seed, device=dev), PI05_FULL)
+    params = {k: v.cpu() for k, v in params.items()}
+    if dev == "cuda":
+        torch.cuda.empty_cache()
+    s = PI05_FULL
+    g = torch.Generator().manual_seed(seed)
+    images = [torch.rand(1, 3, 224, 224, generator=g) * 2 - 1 for _ in range(s.n_cams)]
+    img_masks = [torch.ones(1, dtype=torch.bool) for _ in range(s.n_cams)]
+    tokens = torch.randint(0, s.vocab, (1, s.lang_len), generator=g)
+    masks = torch.ones(1, s.lang_len, dtype=torch.bool)
+    noise = torch.randn(1, s.chunk, s.max_action_dim, generator=g)
+    # dequantise once (what the reference's loader does), then time the unmodified eager math
+    from oracle import w8_ref
+    deq = {}
+    for k, v in params.items():
+        if k.endswith(".scale_weight"):
+            continue
+        deq[k] = w8_ref.dequant_w8(v, params[k[: -len("weight")] + "scale_weight"]) if v.dtype == torch.float8_e4m3fn else v
+    del params
+    times = []
+    pi05_ref.sample_actions(deq, s, images, img_masks, tokens, masks, noise)  # warm-up
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        pi05_ref.sample_actions(deq, s, images, img_masks, tokens, masks, noise)
+        times.append((time.perf_counter() - t0) * 1e3)
+    info = {"cores": torch.get_num_threads(), "nproc": os.cpu_count(), "torch": torch.__version__}
+    return times, info
+
+
+def run_reference(args, rank: int) -> None:
+    if rank != 0:
+        return
+    times, info = _cpu_chunk_times(max(1, args.steps))
+    p50 = statistics.median(times)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(p50, 2), "unit": "ms", "n_gpus": args.gpus,
+        "steps": len(times), "warmup": 1, "ms_per_step": round(sum(times) / len(times), 2), "higher_is_better": False,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16 activations x e4m3 weights dequantised to bf16, fp32 accumulate",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "batch": 1},
+        "cpu_baseline": {"value": round(p50, 2), "unit": "ms", "cores": info["cores"], "kind": "port",
+                         "sample": f"{len(times)} full chunks of the config (oracle/pi05_ref.py, torch {info['torch']}, "
+                                   f"{info['nproc']} logical CPUs)"},
+        "e2e": {"value": round(p50, 2), "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, rank: int, world: int) -> None:
+    import torch.distributed as dist
+
+    from tybok_b200 import ops
+    from tybok_b200.engine import PI05B200Engine
+
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    peaks, peaks_kind = _peaks()
+
+    l0 = ops.launch_count()
+    engine = PI05B200Engine(f"synthetic:pi05_full@{rank}", device=f"cuda:{local}", graph=False, warmup=True,
+                            seed=rank, batch_size=args.batch)
+    l1 = ops.launch_count()
+    engine._capture()
+    launches_per_chunk = ops.launch_count() - l1
+    launches_per_chunk //= 3  # two warm-up passes + the captured pass
+    del l0
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    graph = engine._graph
+    for _ in range(max(3, args.warmup)):
+        graph.replay()
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    t_all0, t_all1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_all0.record()
+    for e0, e1 in evs:
+        e0.record()
+        graph.replay()
+        e1.record()
+    t_all1.record()
+    barrier()
+    clocks = sampler.stop()
+    per = sorted(a.elapsed_time(b) for a, b in evs)
+    p50 = statistics.median(per)
+    total_ms = t_all0.elapsed_time(t_all1)
+    if world > 1:
+        t = torch.tensor([p50, total_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        p50, total_ms = float(t[0]), float(t[1])
+
+    # end to end through the public call: host frame -> numpy chunk
+    frames = [_synthetic_frame(engine, 100 + i) for i in range(4)]
+    for i in range(3):
+        engine.predict_action_chunk(frames[i % 4])
+    barrier()
+    e2e = []
+    for i in range(args.steps):
+        t0 = time.perf_counter()
+        engine.predict_action_chunk(frames[i % 4])
+        e2e.append((time.perf_counter() - t0) * 1e3)
+    e2e_p50 = statistics.median(e2e)
+    if world > 1:
+        t = torch.tensor([e2e_p50], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_p50 = float(t[0])
+    s = engine.config.shape
+    h2d = s.n_cams * 3 * 224 * 224 * 4 + s.n_cams + s.lang_len * 9 + s.chunk * s.max_action_dim * 4
+    d2h = s.chunk * engine.config.action_dim * 4
+
+    line = None
+    if rank == 0:
+        roof = _gemm_roofline(engine, peaks, peaks_kind) if world == 1 else None
+        ops.check_status()
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            del engine
+            torch.cuda.empty_cache()
+            times, info = _cpu_chunk_times(2)
+            cpu = {"value": round(statistics.median(times), 1), "unit": "ms", "cores": info["cores"], "kind": "port",
+                   "sample": f"2 full chunks of the same config after 1 warm-up (oracle/pi05_ref.py, {info['nproc']} logical CPUs)"}
+        line = {
+            "metric": METRIC, "value": round(p50, 4), "unit": "ms", "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": round(total_ms / args.steps, 4), "higher_is_better": False,
+            "scaling": "weak", "vs_baseline": None, "dtype": "e4m3 weights x bf16 activations (3 exact e5m2 planes), fp32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "batch_per_gpu": args.batch, "replicas": world, "cuda_graph": True,
+                       "l2": "weights streamed per chunk (3.4 GB) exceed the 126 MB L2"},
+            "chunks_per_s": round(world * args.batch / (total_ms / args.steps) * 1e3, 2),
+            "clocks": clocks, "gpu_launches": launches_per_chunk * args.steps,
+            "e2e": {"value": round(e2e_p50, 4), "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "roofline": roof, "cpu_baseline": cpu,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device -- the product path has no CPU fallback (use --impl reference "
+                         "for the CPU oracle timing)")
+    run_ours(args, rank, world)
+
+
+if __name__ == "__main__":
+    main()

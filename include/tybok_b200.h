@@ -112,6 +112,26 @@ int tybok_rmsnorm(const void* x, int64_t ldx, const float* weight, const float* 
                   int rows_per_group, int M, int W, float eps, void* y, int64_t ldy, void* y_planes,
                   int out_shift, void* stream);
 
+/* RoPE + KV store.  qkv is the packed projection output [B*L, (H+2G)*D] (row stride ldq); q and
+ * k are rotated (rotate-half form, bf16 cos/sin tables [max_pos, D], bf16 arithmetic with the
+ * reference's rounding points) at positions pos[B*L]; q goes to q_out [B*L, H*D], k and v to the
+ * caches [B, G, Lcap, D] at key offset key_off.  Replaces apply_rotary_pos_emb + the K/V
+ * concatenation of tybok/policies/pi05/models/layers.py:145-164 and rope.py:67-75. */
+int tybok_rope_store(const void* qkv, int64_t ldq, const int* pos, const void* cos_table, const void* sin_table,
+                     void* q_out, void* k_cache, void* v_cache, int B, int L, int H, int G, int D, int Lcap,
+                     int key_off, void* stream);
+
+/* GQA/MQA attention of L query tokens per batch element over the first Lk keys of the caches
+ * (head_dim 256, Lk <= 1024): softmax(q k^T * scale + mask) v with fp32 softmax, bf16 P.
+ *   q          [B*L, H*D] bf16 (already rotated);  k_cache / v_cache  [B, G, Lcap, D] bf16, finite
+ *   key_valid  NULL or uint8 [B, Lk]: 0 masks a key for every query of that batch element
+ *   out        bf16 [B*L, H*D] and/or out_planes [3][B*L][H*D] planes of out * 2^out_shift
+ * Replaces GemmaAttention._forward_eager (tybok/policies/pi05/models/layers.py:166-191) and the
+ * split-K flash kernels of tybok/policies/pi05/models/triton_expert_fused_qkv_rope_attn.py:322-433. */
+int tybok_attention(const void* q, const void* k_cache, const void* v_cache, const void* key_valid, void* out,
+                    void* out_planes, int out_shift, int B, int L, int H, int G, int D, int Lk, int Lcap, float scale,
+                    int* status_word, void* stream);
+
 /* Enable (1) / disable (0) programmatic dependent launch for every kernel of this library
  * (process-wide; default 1).  With it, a kernel's weight prefetch overlaps the tail of the
  * previous kernel in the stream. */

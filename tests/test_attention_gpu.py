@@ -1,0 +1,73 @@
+"""RoPE/KV-store + prefix-cache attention on the GPU against the oracle's eager GQA attention
+(tybok/policies/pi05/models/layers.py:145-191, rope.py:19-75).  Tolerance: rel-L2 <= 1e-2."""
+
+import pytest
+import torch
+
+from oracle import w8_ref
+
+pytestmark = pytest.mark.gpu
+D = 256
+
+
+def _tables(max_pos):
+    pos = torch.arange(max_pos)[None]
+    cos, sin = w8_ref.rope_cos_sin(pos, D, torch.bfloat16)
+    return cos[0].contiguous(), sin[0].contiguous()
+
+
+def _reference(qkv, b, l, h, g, pos, prefix_k, prefix_v, key_valid):
+    """Oracle path: split, RoPE, concat with the prefix cache, eager attention with additive mask."""
+    q = qkv[:, : h * D].view(b, l, h, D).transpose(1, 2)
+    k = qkv[:, h * D : (h + g) * D].view(b, l, g, D).transpose(1, 2)
+    v = qkv[:, (h + g) * D :].view(b, l, g, D).transpose(1, 2)
+    cos, sin = w8_ref.rope_cos_sin(pos, D, torch.bfloat16)
+    q, k = w8_ref.apply_rope(q, k, cos, sin)
+    kk = k if prefix_k is None else torch.cat([prefix_k, k], dim=2)
+    vv = v if prefix_v is None else torch.cat([prefix_v, v], dim=2)
+    mask = torch.where(key_valid[:, None, None, :].bool(), 0.0, w8_ref.MASK_VALUE).expand(b, 1, l, kk.shape[2])
+    return w8_ref.gqa_attention(q, kk, vv, mask, D**-0.5), k, v
+
+
+@pytest.mark.parametrize("b,l,lp,h,g", [(1, 50, 544, 8, 1), (2, 50, 300, 8, 1), (1, 544, 0, 8, 1), (2, 130, 0, 4, 2),
+                                        (1, 10, 968, 8, 1), (1, 7, 5, 2, 2)])
+def test_attention_matches_oracle(b, l, lp, h, g):
+    from tybok_b200 import ops
+
+    gen = torch.Generator().manual_seed(b * 1000 + l + lp)
+    qkv = torch.empty(b * l, (h + 2 * g) * D).normal_(0, 1, generator=gen).to(torch.bfloat16)
+    lk = lp + l
+    key_valid = torch.ones(b, lk, dtype=torch.uint8)
+    if lp > 8:
+        key_valid[:, lp - 5 : lp] = 0  # padded prefix tail
+    elif lp == 0 and l > 20:
+        key_valid[:, l - 9 :] = 0  # padded prompt tail during prefill
+    pos = (torch.arange(l)[None] + lp).expand(b, l).contiguous()
+    prefix_k = prefix_v = None
+    if lp:
+        prefix_k = torch.empty(b, g, lp, D).normal_(0, 1, generator=gen).to(torch.bfloat16)
+        prefix_v = torch.empty(b, g, lp, D).normal_(0, 1, generator=gen).to(torch.bfloat16)
+    ref, rk, rv = _reference(qkv, b, l, h, g, pos, prefix_k, prefix_v, key_valid)
+
+    lcap = lk + 3
+    kc = torch.zeros(b, g, lcap, D, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    if lp:
+        kc[:, :, :lp] = prefix_k.cuda()
+        vc[:, :, :lp] = prefix_v.cuda()
+    cos, sin = _tables(lk + 8)
+    q = ops.rope_store(qkv.cuda(), pos.reshape(-1).int().cuda(), cos.cuda(), sin.cuda(), kc, vc, heads=h, key_off=lp)
+    # RoPE uses the same bf16 operations as torch: the stored keys are bit-identical
+    assert torch.equal(kc[:, :, lp:lk].cpu(), rk) and torch.equal(vc[:, :, lp:lk].cpu(), rv)
+    out, planes = ops.attention(q, kc, vc, key_valid.cuda(), tokens=l, keys=lk, scale=D**-0.5, out_bf16=True,
+                                out_planes=True, out_shift=6)
+    ops.check_status()
+    out = out.cpu().view(b, l, h * D)
+    valid_q = torch.ones(b, l, dtype=torch.bool) if lp else key_valid.bool()
+    assert w8_ref.rel_l2(out[valid_q], ref[valid_q]) <= 1e-2
+    got, want = planes.cpu().view(torch.float8_e5m2).float().sum(0), out.reshape(b * l, h * D).float() * 64.0
+    inside = want.abs() >= 2.0**-7
+    assert torch.equal(got[inside], want[inside])
+    # bit-reproducible
+    out2, _ = ops.attention(q, kc, vc, key_valid.cuda(), tokens=l, keys=lk, scale=D**-0.5)
+    assert torch.equal(out2.cpu().view(b, l, h * D), out)

@@ -1,0 +1,509 @@
+// GQA/MQA attention over [prefix KV cache ; own keys] for sm_100a, plus the RoPE/KV-store
+// kernel that feeds it.
+//
+// rope_store_kernel: packed qkv rows (the qkv GEMM output) -> rotated q [tokens, H*D], rotated k
+// and v appended to the per-layer cache at key offset `key_off` (0 for the prefix prefill,
+// prefix length for the action suffix), so the attention kernel sees one contiguous key range
+// and nothing is ever concatenated or expanded per head.
+//
+// attention_kernel: one CTA per (128-query tile of one head, 128-key block, batch element).
+//   warp 0     TMA: Q tile, K block, V block (four 64-wide swizzled column chunks each).
+//   warp 1     tcgen05.mma: S = Q K^T (128x128x256), then O = P V (128x256x128) with P read from
+//              tensor memory and V as an MN-major shared-memory operand.
+//   warps 2-5  softmax on S straight out of tensor memory (one thread per query row, fp32,
+//              key-validity mask), P written back to tensor memory as bf16; epilogue.
+// The key blocks of one query tile form a thread-block cluster: each CTA stages its
+// un-normalised O and its (max, sum) row statistics in shared memory, the cluster meets at a
+// hardware barrier, and CTA r merges query rows r*R..(r+1)*R-1 over all key blocks in block
+// order through distributed shared memory (bit-reproducible, no global scratch).
+//
+// Algorithmic bytes: Q + O once per (layer, step), K + V once per (batch, kv head).
+// Flops: 4 * Mq * Lk * D * H.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "../../include/tybok_b200.h"
+#include "host_util.h"
+#include "ptx.cuh"
+#include "split3.cuh"
+
+namespace tb {
+
+constexpr int AT_D = 256;        // head dimension this kernel is built for
+constexpr int AT_BQ = 128;       // query rows per CTA (UMMA M)
+constexpr int AT_BK = 128;       // keys per CTA
+constexpr int AT_CHUNK = 16384;  // one 64-column chunk of a 128-row bf16 tile (128 rows x 128 bytes)
+constexpr int AT_TILE = 4 * AT_CHUNK;
+constexpr int AT_THREADS = 192;
+constexpr int AT_MAX_SPLITS = 8;
+constexpr int AT_SMEM = 3 * AT_TILE + 1024;
+
+struct RopeParams {
+  const __nv_bfloat16* qkv;
+  long long ldq;
+  const int* pos;
+  const __nv_bfloat16* cos;
+  const __nv_bfloat16* sin;
+  __nv_bfloat16* q_out;
+  __nv_bfloat16* kcache;
+  __nv_bfloat16* vcache;
+  int B, L, H, G, D, Lcap, key_off, pdl;
+};
+
+// bf16 arithmetic with the rounding points of the reference's torch ops (rope.py:67-75):
+// out = bf16(bf16(x*cos) + bf16(rot*sin)).
+__device__ __forceinline__ float rope1(float x, float rot, float c, float s) {
+  return bf16_round(bf16_round(x * c) + bf16_round(rot * s));
+}
+
+__global__ void rope_store_kernel(const RopeParams p) {
+  if (p.pdl) pdl_wait();
+  const int vec_per_head = p.D / 16;  // each thread: 8 elements of the first half + their partners
+  const int slots = p.H + 2 * p.G;
+  const long long total = static_cast<long long>(p.B) * p.L * slots * vec_per_head;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(i % vec_per_head);
+    const int s = static_cast<int>((i / vec_per_head) % slots);
+    const int m = static_cast<int>(i / (static_cast<long long>(vec_per_head) * slots));
+    const int b = m / p.L, t = m % p.L;
+    const __nv_bfloat16* src = p.qkv + m * p.ldq + s * p.D;
+    const int half = p.D / 2;
+    uint4 lo = *reinterpret_cast<const uint4*>(src + c * 8);
+    uint4 hi = *reinterpret_cast<const uint4*>(src + half + c * 8);
+    if (s < p.H + p.G) {
+      const int ps = p.pos[m];
+      const uint4 cl = *reinterpret_cast<const uint4*>(p.cos + static_cast<long long>(ps) * p.D + c * 8);
+      const uint4 sl = *reinterpret_cast<const uint4*>(p.sin + static_cast<long long>(ps) * p.D + c * 8);
+      const uint4 ch = *reinterpret_cast<const uint4*>(p.cos + static_cast<long long>(ps) * p.D + half + c * 8);
+      const uint4 sh = *reinterpret_cast<const uint4*>(p.sin + static_cast<long long>(ps) * p.D + half + c * 8);
+      __nv_bfloat16* xl = reinterpret_cast<__nv_bfloat16*>(&lo);
+      __nv_bfloat16* xh = reinterpret_cast<__nv_bfloat16*>(&hi);
+      const __nv_bfloat16* pcl = reinterpret_cast<const __nv_bfloat16*>(&cl);
+      const __nv_bfloat16* psl = reinterpret_cast<const __nv_bfloat16*>(&sl);
+      const __nv_bfloat16* pch = reinterpret_cast<const __nv_bfloat16*>(&ch);
+      const __nv_bfloat16* psh = reinterpret_cast<const __nv_bfloat16*>(&sh);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float a = __bfloat162float(xl[e]), bb = __bfloat162float(xh[e]);
+        // rotate_half(x) = (-x2, x1)
+        const float ol = rope1(a, -bb, __bfloat162float(pcl[e]), __bfloat162float(psl[e]));
+        const float oh = rope1(bb, a, __bfloat162float(pch[e]), __bfloat162float(psh[e]));
+        xl[e] = __float2bfloat16_rn(ol);
+        xh[e] = __float2bfloat16_rn(oh);
+      }
+    }
+    __nv_bfloat16* dst;
+    if (s < p.H) {
+      dst = p.q_out + (static_cast<long long>(m) * p.H + s) * p.D;
+    } else {
+      const int g = (s - p.H) % p.G;
+      __nv_bfloat16* cache = (s < p.H + p.G) ? p.kcache : p.vcache;
+      dst = cache + ((static_cast<long long>(b) * p.G + g) * p.Lcap + p.key_off + t) * p.D;
+    }
+    *reinterpret_cast<uint4*>(dst + c * 8) = lo;
+    *reinterpret_cast<uint4*>(dst + half + c * 8) = hi;
+  }
+  if (p.pdl) pdl_launch_dependents();
+}
+
+struct AttnParams {
+  int B, L, H, G, Lk, Lcap;
+  int nsplit;
+  float scale_log2e;  // softmax scale * log2(e)
+  const uint8_t* key_valid;  // [B][Lk] or NULL (all keys valid)
+  __nv_bfloat16* out;        // [B*L][H*D] or NULL
+  uint8_t* out_planes;       // [3][B*L][H*D] or NULL
+  float plane_scale;
+  int* status;
+  int pdl;
+};
+
+struct __align__(8) AttnBars {
+  uint64_t qk_full, v_full, s_full, p_full, o_full;
+  uint32_t tmem_base;
+  volatile int abort;
+  uint32_t valid[4];     // key-validity bits of this CTA's 128 keys
+  float row_max[AT_BQ];  // per query row: running maximum (log2 domain) and sum of this key block
+  float row_sum[AT_BQ];
+};
+
+__device__ __forceinline__ bool at_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitLimitCycles) return false;
+  }
+  return true;
+}
+
+// MN-major shared-memory operand with the 128-byte swizzle: 64-element (128-byte) runs along
+// N, 8 K-rows per 1024-byte group; [16,30) leading byte offset >> 4 = distance between 64-wide
+// N chunks, [32,46) stride byte offset >> 4 = distance between 8-row K groups.
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t smem_addr, uint32_t lbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>(lbo_bytes >> 4) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+__global__ void __launch_bounds__(AT_THREADS, 1)
+attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ AttnBars bars;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sq = smem;
+  uint8_t* sk = smem + AT_TILE;
+  uint8_t* sv = smem + 2 * AT_TILE;
+
+  const int sp = blockIdx.x;  // key block == rank in the cluster
+  const int n_qt = (p.L + AT_BQ - 1) / AT_BQ;
+  const int h = blockIdx.y / n_qt, qt = blockIdx.y % n_qt;
+  const int b = blockIdx.z;
+  const int g = h / (p.H / p.G);
+  const int key0 = sp * AT_BK;
+
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+    mbar_init(&bars.qk_full, 1);
+    mbar_init(&bars.v_full, 1);
+    mbar_init(&bars.s_full, 1);
+    mbar_init(&bars.p_full, 4);
+    mbar_init(&bars.o_full, 1);
+    bars.abort = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars.tmem_base, 512);
+    tmem_relinquish();
+  }
+  if (warp == 2) {  // validity bits of this block's keys
+    uint32_t bits = 0;
+    for (int w = 0; w < 4; ++w) {
+      const int j = key0 + w * 32 + lane;
+      bool ok = j < p.Lk;
+      if (ok && p.key_valid) {
+        if (p.pdl) pdl_wait();
+        ok = p.key_valid[static_cast<long long>(b) * p.Lk + j] != 0;
+      }
+      bits = __ballot_sync(0xffffffffu, ok);
+      if (lane == 0) bars.valid[w] = bits;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars.tmem_base;
+  const uint32_t t_s = tmem, t_p = tmem + 128, t_o = tmem + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      if (p.pdl) pdl_wait();
+      const int qrow = b * p.L + qt * AT_BQ;
+      const int krow = (b * p.G + g) * p.Lcap + key0;
+      mbar_arrive_expect_tx(&bars.qk_full, 2 * AT_TILE);
+      for (int c = 0; c < 4; ++c) tma_load_2d(sq + c * AT_CHUNK, &tm_q, &bars.qk_full, h * AT_D + c * 64, qrow);
+      for (int c = 0; c < 4; ++c) tma_load_2d(sk + c * AT_CHUNK, &tm_k, &bars.qk_full, c * 64, krow);
+      mbar_arrive_expect_tx(&bars.v_full, AT_TILE);
+      for (int c = 0; c < 4; ++c) tma_load_2d(sv + c * AT_CHUNK, &tm_v, &bars.v_full, c * 64, krow);
+      if (p.pdl) pdl_launch_dependents();
+    }
+  } else if (warp == 1) {
+    const bool leader = elect_one();
+    const uint64_t dk = smem_desc_sw128(0);
+    bool ok = __all_sync(0xffffffffu, at_wait(&bars.qk_full, 0, &bars.abort));
+    if (ok) {
+      tc_fence_after();
+      const uint32_t idesc_s = idesc_bf16_f32(AT_BQ, AT_BK);
+      const uint32_t q16 = (smem_u32(sq) & 0x3FFFFu) >> 4, k16 = (smem_u32(sk) & 0x3FFFFu) >> 4;
+#pragma unroll
+      for (int ks = 0; ks < 16; ++ks) {  // D = 256 in steps of 16: chunk ks/4, 32 bytes per step
+        const uint32_t off = (ks >> 2) * (AT_CHUNK >> 4) + (ks & 3) * 2;
+        if (leader) umma_ss_bf16(t_s, dk | (q16 + off), dk | (k16 + off), idesc_s, ks > 0 ? 1u : 0u);
+      }
+      if (leader) tc_commit(&bars.s_full);
+      __syncwarp();
+      ok = __all_sync(0xffffffffu, at_wait(&bars.v_full, 0, &bars.abort) && at_wait(&bars.p_full, 0, &bars.abort));
+    }
+    if (ok) {
+      tc_fence_after();
+      // O[128 x 256] = P[128 x 128 keys] . V[keys x 256]: B operand N = D (MN-major), K = keys.
+      const uint32_t idesc_o = idesc_bf16_f32(AT_BQ, AT_D) | (1u << 16);
+      const uint32_t v_addr = smem_u32(sv);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {  // 16 keys per step: 16 rows x 128 bytes inside every chunk
+        const uint64_t bd = smem_desc_sw128_mn(v_addr + ks * 2048, AT_CHUNK);
+        if (leader) umma_ts_bf16(t_o, t_p + ks * 8, bd, idesc_o, ks > 0 ? 1u : 0u);
+      }
+      if (leader) tc_commit(&bars.o_full);
+      __syncwarp();
+    } else if (lane == 0) {
+      bars.abort = 1;
+      if (p.status) atomicCAS(p.status, 0, TYBOK_DEV_TIMEOUT_MMA);
+    }
+  } else {
+    // ------------------------------------------------------------ softmax, one thread per row
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    bool ok = __all_sync(0xffffffffu, at_wait(&bars.s_full, 0, &bars.abort));
+    if (ok) {
+      tc_fence_after();
+      float mx = -1e30f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(t_s + lane_addr + c * 32, v);
+        tc_wait_ld();
+        const uint32_t bits = bars.valid[c];
+#pragma unroll
+        for (int e = 0; e < 32; ++e)
+          if ((bits >> e) & 1u) mx = fmaxf(mx, __uint_as_float(v[e]));
+      }
+      const float m2 = mx * p.scale_log2e;  // scale > 0, so the maximum commutes with the scaling
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(t_s + lane_addr + c * 32, v);
+        tc_wait_ld();
+        const uint32_t bits = bars.valid[c];
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          const float p0 = ((bits >> e) & 1u) ? exp2f(__uint_as_float(v[e]) * p.scale_log2e - m2) : 0.f;
+          const float p1 = ((bits >> (e + 1)) & 1u) ? exp2f(__uint_as_float(v[e + 1]) * p.scale_log2e - m2) : 0.f;
+          sum += p0 + p1;
+          const __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
+          pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&pp);
+        }
+        tmem_st16(t_p + lane_addr + c * 16, pk);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      bars.row_max[row] = m2;
+      bars.row_sum[row] = sum;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars.p_full);
+      // -------------------------------------------------------- stage O (un-normalised) as [col][row] fp32
+      ok = __all_sync(0xffffffffu, at_wait(&bars.o_full, 0, &bars.abort));
+      if (ok) {
+        tc_fence_after();
+        float* stage = reinterpret_cast<float*>(smem);  // 128 KB: the Q and K tiles are no longer needed
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+          uint32_t v[32];
+          tmem_ld32(t_o + lane_addr + c * 32, v);
+          tc_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) stage[(c * 32 + e) * AT_BQ + row] = __uint_as_float(v[e]);
+        }
+      }
+    }
+    if (!ok && lane == 0) {
+      bars.abort = 1;
+      if (p.status) atomicCAS(p.status, 0, TYBOK_DEV_TIMEOUT_EPILOGUE);
+    }
+  }
+
+  // ------------------------------------------------------------ meet: every key block staged
+  tc_fence_before();
+  if (p.nsplit > 1) {
+    __syncwarp();
+    cluster_sync_all();
+  } else {
+    __syncthreads();
+  }
+
+  if (warp >= 2 && !bars.abort) {
+    // Merge: this CTA owns query rows [r0, r1) of the tile; thread = (row, 64-column group).
+    const int et = tid - 64;
+    const int rl = et & 31, cg = et >> 5;
+    const int rpr = (AT_BQ + p.nsplit - 1) / p.nsplit;
+    const int r0 = sp * rpr, r1 = min(AT_BQ, r0 + rpr);
+    const uint32_t stage_addr = smem_u32(smem);
+    const uint32_t max_addr = smem_u32(&bars.row_max[0]), sum_addr = smem_u32(&bars.row_sum[0]);
+    const long long hd = static_cast<long long>(p.H) * AT_D;
+    const long long plane = static_cast<long long>(p.B) * p.L * hd;
+    for (int r = r0 + rl; r < r1; r += 32) {
+      const int t = qt * AT_BQ + r;
+      if (t >= p.L) continue;
+      float w[AT_MAX_SPLITS];
+      float mx = -1e30f;
+      for (int s = 0; s < p.nsplit; ++s) {
+        float v;
+        const uint32_t a = p.nsplit > 1 ? dsmem_addr(max_addr + r * 4, s) : max_addr + r * 4;
+        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(a));
+        w[s] = v;
+        mx = fmaxf(mx, v);
+      }
+      float denom = 0.f;
+      for (int s = 0; s < p.nsplit; ++s) {
+        float l;
+        const uint32_t a = p.nsplit > 1 ? dsmem_addr(sum_addr + r * 4, s) : sum_addr + r * 4;
+        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(l) : "r"(a));
+        w[s] = exp2f(w[s] - mx);  // weight of key block s (0 for a block without valid keys)
+        denom += w[s] * l;
+      }
+      const float inv = denom > 0.f ? 1.0f / denom : 0.f;
+      const long long orow = (static_cast<long long>(b) * p.L + t) * hd + static_cast<long long>(h) * AT_D + cg * 64;
+#pragma unroll 1
+      for (int c8 = 0; c8 < 8; ++c8) {  // 8 columns at a time
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int s = 0; s < p.nsplit; ++s) {  // block order: bit-reproducible
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const uint32_t local = stage_addr + (((cg * 64 + c8 * 8 + e) * AT_BQ) + r) * 4;
+            const uint32_t a = p.nsplit > 1 ? dsmem_addr(local, s) : local;
+            float v;
+            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(a));
+            acc[e] += w[s] * v;
+          }
+        }
+        __nv_bfloat162 o2[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(acc[2 * e] * inv, acc[2 * e + 1] * inv);
+        if (p.out) *reinterpret_cast<uint4*>(p.out + orow + c8 * 8) = *reinterpret_cast<const uint4*>(o2);
+        if (p.out_planes) {
+          const float lo[4] = {__bfloat162float(o2[0].x) * p.plane_scale, __bfloat162float(o2[0].y) * p.plane_scale,
+                               __bfloat162float(o2[1].x) * p.plane_scale, __bfloat162float(o2[1].y) * p.plane_scale};
+          const float hi[4] = {__bfloat162float(o2[2].x) * p.plane_scale, __bfloat162float(o2[2].y) * p.plane_scale,
+                               __bfloat162float(o2[3].x) * p.plane_scale, __bfloat162float(o2[3].y) * p.plane_scale};
+          uint2 w1, w2, w3;
+          split3_quad(lo, w1.x, w2.x, w3.x);
+          split3_quad(hi, w1.y, w2.y, w3.y);
+          uint8_t* dst = p.out_planes + orow + c8 * 8;
+          *reinterpret_cast<uint2*>(dst) = w1;
+          *reinterpret_cast<uint2*>(dst + plane) = w2;
+          *reinterpret_cast<uint2*>(dst + 2 * plane) = w3;
+        }
+      }
+    }
+  }
+
+  if (p.nsplit > 1) {
+    __syncwarp();
+    cluster_sync_all();
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+}  // namespace tb
+
+extern "C" {
+
+int tybok_rope_store(const void* qkv, int64_t ldq, const int* pos, const void* cos_table, const void* sin_table,
+                     void* q_out, void* k_cache, void* v_cache, int B, int L, int H, int G, int D, int Lcap,
+                     int key_off, void* stream) {
+  using namespace tb;
+  if (!qkv || !pos || !cos_table || !sin_table || !q_out || !k_cache || !v_cache)
+    return host::fail(TYBOK_ERR_ARG, "rope_store: null pointer argument");
+  if (B <= 0 || L <= 0 || H <= 0 || G <= 0 || D % 16 != 0 || H % G != 0 || key_off < 0 || key_off + L > Lcap)
+    return host::fail(TYBOK_ERR_ARG, "rope_store: bad shape (D % 16 == 0, H % G == 0, key_off + L <= Lcap)");
+  if (ldq % 8 != 0 || ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
+                        reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
+                        reinterpret_cast<uintptr_t>(cos_table) | reinterpret_cast<uintptr_t>(sin_table)) & 15))
+    return host::fail(TYBOK_ERR_ARG, "rope_store: tensors must be 16-byte aligned, ldq % 8 == 0");
+  if (int rc = host::require_sm100()) return rc;
+  RopeParams p{static_cast<const __nv_bfloat16*>(qkv), ldq, pos, static_cast<const __nv_bfloat16*>(cos_table),
+               static_cast<const __nv_bfloat16*>(sin_table), static_cast<__nv_bfloat16*>(q_out),
+               static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), B, L, H, G, D, Lcap, key_off,
+               host::pdl_enabled() ? 1 : 0};
+  const long long total = static_cast<long long>(B) * L * (H + 2 * G) * (D / 16);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(std::min<long long>((total + 255) / 256, 8 * host::sm_count())));
+  cfg.blockDim = dim3(256);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = p.pdl;
+  if (cudaLaunchKernelEx(&cfg, rope_store_kernel, p) != cudaSuccess) return host::fail_cuda("launch rope_store_kernel");
+  host::count_launch();
+  return TYBOK_OK;
+}
+
+int tybok_attention(const void* q, const void* k_cache, const void* v_cache, const void* key_valid, void* out,
+                    void* out_planes, int out_shift, int B, int L, int H, int G, int D, int Lk, int Lcap, float scale,
+                    int* status_word, void* stream) {
+  using namespace tb;
+  if (!q || !k_cache || !v_cache || (!out && !out_planes)) return host::fail(TYBOK_ERR_ARG, "attention: null pointer argument");
+  if (D != AT_D) return host::fail(TYBOK_ERR_ARG, "attention: this kernel is built for head_dim 256");
+  if (B <= 0 || L <= 0 || H <= 0 || G <= 0 || H % G != 0 || Lk <= 0 || Lk > Lcap)
+    return host::fail(TYBOK_ERR_ARG, "attention: bad shape (H % G == 0, 0 < Lk <= Lcap)");
+  const int nsplit = (Lk + AT_BK - 1) / AT_BK;
+  if (nsplit > AT_MAX_SPLITS) return host::fail(TYBOK_ERR_ARG, "attention: at most 1024 keys (8 blocks of 128 per cluster)");
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
+       reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(out_planes)) & 15)
+    return host::fail(TYBOK_ERR_ARG, "attention: tensors must be 16-byte aligned");
+  if (out_shift < -60 || out_shift > 60) return host::fail(TYBOK_ERR_ARG, "attention: exponent shift out of range");
+  if (int rc = host::require_sm100()) return rc;
+
+  CUtensorMap tm_q, tm_k, tm_v;
+  const uint64_t hd = static_cast<uint64_t>(H) * D;
+  if (int rc = host::tensor_map_2d(&tm_q, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, hd, static_cast<uint64_t>(B) * L, hd * 2, 64, AT_BQ))
+    return rc;
+  const uint64_t krows = static_cast<uint64_t>(B) * G * Lcap;
+  if (int rc = host::tensor_map_2d(&tm_k, k_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, krows, D * 2, 64, AT_BK)) return rc;
+  if (int rc = host::tensor_map_2d(&tm_v, v_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, krows, D * 2, 64, AT_BK)) return rc;
+
+  AttnParams p{};
+  p.B = B; p.L = L; p.H = H; p.G = G; p.Lk = Lk; p.Lcap = Lcap; p.nsplit = nsplit;
+  p.scale_log2e = scale * 1.4426950408889634f;
+  p.key_valid = static_cast<const uint8_t*>(key_valid);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.out_planes = static_cast<uint8_t*>(out_planes);
+  p.plane_scale = ldexpf(1.0f, out_shift);
+  p.status = status_word;
+  p.pdl = host::pdl_enabled() ? 1 : 0;
+
+  static bool attr_set[64] = {};
+  const int dev = host::current_device();
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM) != cudaSuccess)
+      return host::fail_cuda("cudaFuncSetAttribute(attention_kernel)");
+    attr_set[dev] = true;
+  }
+  const int n_qt = (L + AT_BQ - 1) / AT_BQ;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(nsplit, H * n_qt, B);
+  cfg.blockDim = dim3(AT_THREADS);
+  cfg.dynamicSmemBytes = AT_SMEM;
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (p.pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (nsplit > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = nsplit;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  if (cudaLaunchKernelEx(&cfg, attention_kernel, tm_q, tm_k, tm_v, p) != cudaSuccess)
+    return host::fail_cuda("launch attention_kernel");
+  host::count_launch();
+  return TYBOK_OK;
+}
+
+}  // extern "C"

@@ -34,6 +34,11 @@ _L.define(
 _L.define("rmsnorm(Tensor x, Tensor? weight, Tensor? mod, int rows_per_group, float eps, bool out_bf16, "
           "bool out_planes, int out_shift) -> (Tensor, Tensor)")
 
+_L.define("rope_store(Tensor qkv, Tensor pos, Tensor cos, Tensor sin, Tensor(a!) k_cache, Tensor(b!) v_cache, int heads, "
+          "int key_off) -> Tensor")
+_L.define("attention(Tensor q, Tensor k_cache, Tensor v_cache, Tensor? key_valid, int tokens, int keys, float scale, "
+          "bool out_bf16, bool out_planes, int out_shift) -> (Tensor, Tensor)")
+
 _status: dict[int, torch.Tensor] = {}
 
 
@@ -178,6 +183,47 @@ def _rmsnorm_cuda(x, weight, mod, rows_per_group, eps, out_bf16, out_planes, out
     return y, yp
 
 
+def _rope_store_cuda(qkv, pos, cos, sin, k_cache, v_cache, heads, key_off):
+    lib = _lib.load()
+    b, g, lcap, d = k_cache.shape
+    if qkv.dtype != torch.bfloat16 or qkv.dim() != 2 or qkv.stride(1) != 1 or qkv.shape[1] != (heads + 2 * g) * d:
+        raise TypeError("rope_store: qkv must be bf16 [B*L, (H+2G)*D]")
+    if pos.dtype != torch.int32 or pos.numel() != qkv.shape[0] or not pos.is_contiguous():
+        raise TypeError("rope_store: pos must be contiguous int32 [B*L]")
+    for t in (k_cache, v_cache, cos, sin):
+        if t.dtype != torch.bfloat16 or not t.is_contiguous():
+            raise TypeError("rope_store: caches and cos/sin tables must be contiguous bf16")
+    if v_cache.shape != k_cache.shape or cos.shape[-1] != d:
+        raise ValueError("rope_store: cache / table shapes disagree")
+    l = qkv.shape[0] // b
+    q = torch.empty((qkv.shape[0], heads * d), dtype=torch.bfloat16, device=qkv.device)
+    rc = lib.tybok_rope_store(qkv.data_ptr(), qkv.stride(0), pos.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                              q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), b, l, heads, g, d, lcap,
+                              int(key_off), _stream(qkv))
+    _lib.check(rc, "tybok_rope_store")
+    return q
+
+
+def _attention_cuda(q, k_cache, v_cache, key_valid, tokens, keys, scale, out_bf16, out_planes, out_shift):
+    lib = _lib.load()
+    b, g, lcap, d = k_cache.shape
+    if q.dtype != torch.bfloat16 or q.dim() != 2 or not q.is_contiguous() or q.shape[0] != b * tokens:
+        raise TypeError("attention: q must be contiguous bf16 [B*L, H*D]")
+    h = q.shape[1] // d
+    if key_valid is not None and (key_valid.dtype != torch.uint8 or key_valid.shape != (b, keys)
+                                  or not key_valid.is_contiguous()):
+        raise TypeError("attention: key_valid must be contiguous uint8 [B, Lk]")
+    y, yp = _outputs(b * tokens, h * d, q.device, out_bf16, out_planes)
+    rc = lib.tybok_attention(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _ptr(key_valid),
+                             y.data_ptr() if out_bf16 else None, yp.data_ptr() if out_planes else None, int(out_shift),
+                             b, int(tokens), h, g, d, int(keys), lcap, float(scale), status_word(q.device).data_ptr(),
+                             _stream(q))
+    _lib.check(rc, "tybok_attention")
+    return y, yp
+
+
+_L.impl("rope_store", _rope_store_cuda, "CUDA")
+_L.impl("attention", _attention_cuda, "CUDA")
 _L.impl("rmsnorm", _rmsnorm_cuda, "CUDA")
 _L.impl("split3", _split3_cuda, "CUDA")
 _L.impl("w8x3_linear", _w8x3_linear_cuda, "CUDA")
@@ -224,6 +270,20 @@ def rmsnorm(x, weight=None, mod=None, *, rows_per_group=1, eps=1e-6, out_bf16=Fa
     """Gemma RMSNorm (``weight``) or AdaRMS norm (``mod`` = precomputed ``dense(cond)``); returns
     ``(y_bf16, y_planes)``; see ``tybok_rmsnorm``."""
     return torch.ops.tybok_b200.rmsnorm(x, weight, mod, rows_per_group, eps, out_bf16, out_planes, out_shift)
+
+
+def rope_store(qkv, pos, cos, sin, k_cache, v_cache, *, heads, key_off):
+    """RoPE on the packed projection rows; rotated q is returned ``[B*L, H*D]``, rotated k and v are
+    written into the caches ``[B, G, Lcap, D]`` at ``key_off``; see ``tybok_rope_store``."""
+    return torch.ops.tybok_b200.rope_store(qkv, pos, cos, sin, k_cache, v_cache, heads, key_off)
+
+
+def attention(q, k_cache, v_cache, key_valid=None, *, tokens, keys, scale, out_bf16=True, out_planes=False,
+              out_shift=DEFAULT_SHIFT):
+    """GQA attention over the first ``keys`` cache rows; returns ``(out_bf16, out_planes)``; see
+    ``tybok_attention``."""
+    return torch.ops.tybok_b200.attention(q, k_cache, v_cache, key_valid, tokens, keys, scale, out_bf16, out_planes,
+                                          out_shift)
 
 
 def launch_count() -> int:
