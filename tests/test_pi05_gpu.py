@@ -14,7 +14,7 @@ sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
 from make_golden import tiny_inputs  # noqa: E402
 
 from oracle import pi05_ref, w8_ref  # noqa: E402
-from tybok_b200.shapes import PI05_TINY  # noqa: E402
+from tybok_b200.shapes import PI05_SMALL, PI05_TINY  # noqa: E402
 from tybok_b200.weights import quantize_hot_linears, random_pi05_params  # noqa: E402
 
 pytestmark = pytest.mark.gpu
@@ -46,11 +46,28 @@ def test_rmsnorm_planes_and_bf16(m, w, ada):
     assert torch.equal(got[inside], want[inside])
 
 
-def _tiny_model():
+def _tiny_model(shape=PI05_TINY):
     from tybok_b200.pi05 import PI05Model
 
-    params = quantize_hot_linears(random_pi05_params(PI05_TINY, seed=0), PI05_TINY)
-    return params, PI05Model(params, PI05_TINY, device="cuda", vision_dtype=torch.float32)
+    params = quantize_hot_linears(random_pi05_params(shape, seed=0), shape)
+    return params, PI05Model(params, shape, device="cuda", vision_dtype=torch.float32)
+
+
+@pytest.mark.parametrize("batch", [1, 3])
+def test_small_policy_with_attention_kernel_matches_oracle(batch):
+    """head_dim 256 / MQA: the tcgen05 attention + RoPE/KV-store kernels run inside the model."""
+    from tybok_b200 import ops
+
+    params, model = _tiny_model(PI05_SMALL)
+    assert model.fused_attention
+    images, img_masks, tokens, masks, noise = tiny_inputs(PI05_SMALL, seed=7, batch=batch)
+    noise = torch.randn(noise.shape, generator=torch.Generator().manual_seed(1))
+    ref = pi05_ref.sample_actions(params, PI05_SMALL, images, img_masks, tokens, masks, noise)
+    out = model.sample_actions([t.cuda() for t in images], [t.cuda() for t in img_masks], tokens.cuda(), masks.cuda(),
+                               noise.cuda())
+    ops.check_status()
+    assert float((out.cpu() - ref).abs().max()) <= 2e-2
+    assert w8_ref.rel_l2(out.cpu(), ref) <= 1e-2
 
 
 def test_tiny_policy_chunk_matches_oracle():

@@ -122,6 +122,10 @@ class PI05Model:
         self.time_in = (f32("time_mlp_in.weight"), f32("time_mlp_in.bias"))
         self.time_out = (f32("time_mlp_out.weight"), f32("time_mlp_out.bias"))
         self.cos, self.sin = _rope_table(shape.vlm.head_dim, shape.prefix_len + shape.chunk + 8, dev)
+        # The tcgen05 attention kernel is built for head_dim 256 (both Gemma stacks of pi0.5);
+        # other head sizes use torch SDPA on the same caches.
+        self.fused_attention = shape.vlm.head_dim == 256 and shape.expert.head_dim == 256
+        self._cache_by_batch: dict[int, list] = {}
         self._precompute_step_constants()
 
     # ------------------------------------------------------------------ constants
@@ -194,7 +198,8 @@ class PI05Model:
     def _attention(self, spec: GemmaSpec, qkv: torch.Tensor, b: int, l: int, pos, mask, prefix_kv):
         """Packed qkv ``[B*L, (H+2Hkv)*D]`` -> attention output ``[B*L, H*D]`` and this layer's
         post-RoPE ``(K, V)`` ``[B, Hkv, L, D]``.  GQA over ``[prefix ; own]`` keys with a boolean
-        mask (layers.py:145-191).  torch SDPA for now (library call)."""
+        mask (layers.py:145-191).  torch SDPA: only used when the head size is not the 256 the
+        attention kernel of this package is built for."""
         h, g, d = spec.num_heads, spec.num_kv_heads, spec.head_dim
         qkv = qkv.view(b, l, h + 2 * g, d)
         q = self._rope(qkv[:, :, :h], pos).transpose(1, 2)
@@ -207,9 +212,23 @@ class PI05Model:
         a = F.scaled_dot_product_attention(q, kk, vv, attn_mask=mask, scale=d**-0.5, enable_gqa=(g != h))
         return a.transpose(1, 2).reshape(b * l, h * d), k, v
 
-    def _layer(self, spec, lay: _Layer, x, b, l, pos, mask, prefix_kv, mods):
+    def _caches(self, b: int):
+        """Per-layer K/V caches ``[B, G, prefix_len + chunk, D]`` (zero-initialised once per batch
+        size): the prefill writes keys [0, Lp), every expert layer-step rewrites [Lp, Lp + L)."""
+        c = self._cache_by_batch.get(b)
+        if c is None:
+            s = self.shape
+            lcap = s.prefix_len + s.chunk
+            mk = lambda: torch.zeros(b, s.vlm.num_kv_heads, lcap, s.vlm.head_dim, dtype=torch.bfloat16,  # noqa: E731
+                                     device=self.device)
+            c = [(mk(), mk()) for _ in range(s.vlm.depth)]
+            self._cache_by_batch[b] = c
+        return c
+
+    def _layer(self, spec, lay: _Layer, x, b, l, pos, mask, cache, key_off, key_valid, mods):
         """One decoder layer on ``x [B*L, W]`` bf16 (layers.py:268-308). ``mods`` is None for the
-        VLM (plain norms) or ``(mod_in, mod_post)`` ``[1, 3W]`` AdaRMS modulations."""
+        VLM (plain norms) or ``(mod_in, mod_post)`` ``[1, 3W]`` AdaRMS modulations.  ``cache`` is
+        this layer's ``(K, V)`` cache; the layer appends its keys at ``key_off``."""
         w = spec.width
         m = x.shape[0]
         if mods is None:
@@ -219,8 +238,16 @@ class PI05Model:
             _, xp = ops.rmsnorm(x, mod=mods[0], rows_per_group=m, out_shift=SHIFT_NORMED)
             gate_in, gate_post = mods[0][:, 2 * w :], mods[1][:, 2 * w :]
         qkv, _ = ops.w8x3_linear(xp, SHIFT_NORMED, *lay.qkv)
-        a, k, v = self._attention(spec, qkv, b, l, pos, mask, prefix_kv)
-        ap = ops.split3(a, SHIFT_ATTN)
+        if self.fused_attention:
+            q = ops.rope_store(qkv, pos, self.cos, self.sin, cache[0], cache[1], heads=spec.num_heads, key_off=key_off)
+            _, ap = ops.attention(q, cache[0], cache[1], key_valid, tokens=l, keys=key_off + l,
+                                  scale=spec.head_dim**-0.5, out_bf16=False, out_planes=True, out_shift=SHIFT_ATTN)
+        else:
+            prefix_kv = (cache[0][:, :, :key_off], cache[1][:, :, :key_off]) if key_off else None
+            a, k, v = self._attention(spec, qkv, b, l, pos.view(b, l).long(), mask, prefix_kv)
+            cache[0][:, :, key_off : key_off + l] = k
+            cache[1][:, :, key_off : key_off + l] = v
+            ap = ops.split3(a, SHIFT_ATTN)
         x, _ = ops.w8x3_linear(ap, SHIFT_ATTN, *lay.o, epilogue=ops.EPI_RESIDUAL, residual=x, gate=gate_in,
                                rows_per_gate=m)
         if mods is None:
@@ -231,34 +258,38 @@ class PI05Model:
                                out_shift=SHIFT_FFN)
         x, _ = ops.w8x3_linear(hp, SHIFT_FFN, *lay.down, epilogue=ops.EPI_RESIDUAL, residual=x, gate=gate_post,
                                rows_per_gate=m)
-        return x, k, v
+        return x
 
     # ------------------------------------------------------------------ prefix + denoise
     def prefill(self, prefix_embs: torch.Tensor, pad: torch.Tensor):
-        """VLM prefix pass collecting per-layer post-RoPE (K, V) (gemma.py:61-125, use_cache)."""
+        """VLM prefix pass filling the per-layer post-RoPE (K, V) caches (gemma.py:61-125,
+        use_cache); returns views ``[B, G, Lp, D]`` of the prefix part of every layer's cache."""
         spec = self.shape.vlm
         b, l, w = prefix_embs.shape
-        mask = _additive(pad[:, None, :, None] & pad[:, None, None, :])  # [B,1,L,L]: all-zero att masks
-        pos = torch.cumsum(pad, dim=1) - 1
-        pos = pos.clamp_min(0)
+        caches = self._caches(b)
+        mask = None if self.fused_attention else _additive(pad[:, None, :, None] & pad[:, None, None, :])
+        pos = (torch.cumsum(pad, dim=1) - 1).clamp_min(0).to(torch.int32).reshape(-1)
+        key_valid = pad.to(torch.uint8).contiguous()
         x = prefix_embs.reshape(b * l, w)
-        kv = []
-        for lay in self.vlm_layers:
-            x, k, v = self._layer(spec, lay, x, b, l, pos, mask, None, None)
-            kv.append((k, v))
-        return kv
+        for lay, cache in zip(self.vlm_layers, caches):
+            x = self._layer(spec, lay, x, b, l, pos, mask, cache, 0, key_valid, None)
+        return [(kc[:, :, :l], vc[:, :, :l]) for kc, vc in caches]
 
-    def denoise_step(self, step: int, x_t: torch.Tensor, pad: torch.Tensor, kv) -> torch.Tensor:
-        """One expert pass -> velocity ``[B, chunk, A]`` fp32 (flow_matching.py:505-556)."""
+    def denoise_step(self, step: int, x_t: torch.Tensor, pad: torch.Tensor, kv=None) -> torch.Tensor:
+        """One expert pass over the prefix caches -> velocity ``[B, chunk, A]`` fp32
+        (flow_matching.py:505-556)."""
         s = self.shape
         spec = s.expert
         b, l = x_t.shape[0], x_t.shape[1]
+        lp = pad.shape[1]
+        caches = self._caches(b)
         x = F.linear(x_t, *self.action_in).to(torch.bfloat16).reshape(b * l, spec.width)
-        mask = _additive(torch.cat([pad[:, None, None, :].expand(b, 1, l, pad.shape[1]),
-                                    torch.ones(b, 1, l, l, dtype=torch.bool, device=x.device)], dim=3))
-        pos = pad.sum(dim=-1, keepdim=True) + torch.arange(l, device=x.device)[None, :]
+        allowed = torch.cat([pad, torch.ones(b, l, dtype=torch.bool, device=x.device)], dim=1)  # [B, Lp+L]
+        mask = None if self.fused_attention else _additive(allowed[:, None, None, :].expand(b, 1, l, lp + l))
+        key_valid = allowed.to(torch.uint8).contiguous()
+        pos = (pad.sum(dim=-1, keepdim=True) + torch.arange(l, device=x.device)[None, :]).to(torch.int32).reshape(-1)
         for i, lay in enumerate(self.exp_layers):
-            x, _, _ = self._layer(spec, lay, x, b, l, pos, mask, kv[i], self.mods[step][i])
+            x = self._layer(spec, lay, x, b, l, pos, mask, caches[i], lp, key_valid, self.mods[step][i])
         y, _ = ops.rmsnorm(x, mod=self.final_mods[step], rows_per_group=b * l, out_bf16=True, out_planes=False)
         y = y.view(b, l, spec.width)[:, -s.chunk :].float()
         return F.linear(y, *self.action_out)

@@ -84,6 +84,19 @@ PI05_TINY = PI05Shape(
     steps=3,
 )
 
+#: A small policy with the real head geometry (MQA, head_dim 256), so GPU parity tests run the
+#: attention kernel inside the model; 130-token prefix = two key blocks.
+PI05_SMALL = PI05Shape(
+    vlm=GemmaSpec(256, 2, 512, 2, 1, 256),
+    expert=GemmaSpec(128, 2, 256, 2, 1, 256),
+    vision=SiglipSpec(hidden=128, heads=4, layers=2, mlp_dim=256, image=70, patch=14),
+    n_cams=2,
+    lang_len=80,
+    vocab=512,
+    chunk=10,
+    steps=3,
+)
+
 #: The W8 linear sweep of BASELINE config 1: (N, K) pairs and token counts M.
 W8_SWEEP_NK = ((16384, 2048), (2048, 16384), (2560, 2048), (4096, 1024), (1024, 4096))
 W8_SWEEP_M = (1, 50, 256, 800)
