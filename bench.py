@@ -83,47 +83,85 @@ def _synthetic_frame(engine, seed: int):
 
 
 def _gemm_roofline(engine, peaks, peaks_kind) -> dict:
-    """One extra eager chunk with every W8 GEMM launch bracketed by CUDA events on the launching
-    stream: achieved = sum of algorithmic bytes (N*K + 4N + 2MK + 2MN per launch; gated form two
-    weight matrices) / sum of launch durations."""
+    """Roofline of the dominant kernel (``w8_gemm_kernel``), measured live: every GEMM call
+    signature of one chunk is replayed as a CUDA graph of back-to-back launches over rotating
+    weight copies (> 3x L2, so weights stream from HBM as they do inside the chunk) and timed
+    with CUDA events on the launching stream.  Algorithmic bytes per launch =
+    nw*(N*K + 4N) + 2*M*K + 2*M*N (nw = 2 for the gated form), flops = 2*nw*M*N*K.
+    ``achieved`` aggregates the action-expert launches (M = 50*batch, HBM-bound, 720 of the 792
+    launches of a chunk); the prefix launches (M = 544*batch, tensor-bound) are reported beside."""
     from tybok_b200 import ops
 
-    lib = ops._lib.load()
-    lib.tybok_set_pdl(0)  # serialise launches so an event pair brackets exactly one kernel
-    rec = []
-    orig_lin, orig_geglu = ops.w8x3_linear, ops.w8x3_geglu
+    s = engine.config.shape
+    dev = engine.device
+    b = engine.batch_size
 
-    def timed(fn, nw):
-        def wrapper(planes, shift, w8, *a, **kw):
+    def shapes(spec, m, layers, reps):
+        hd, kvd = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim
+        return [("qkv", m, hd + 2 * kvd, spec.width, 1, layers * reps), ("o", m, spec.width, hd, 1, layers * reps),
+                ("geglu", m, spec.mlp_dim, spec.width, 2, layers * reps),
+                ("down", m, spec.width, spec.mlp_dim, 1, layers * reps)]
+
+    groups = {"expert": shapes(s.expert, b * s.chunk, s.expert.depth, s.steps),
+              "prefix": shapes(s.vlm, b * s.prefix_len, s.vlm.depth, 1)}
+    out = {}
+    for gname, lst in groups.items():
+        rows = []
+        for name, m, n, k, nw, count in lst:
+            nbuf = min(48, max(4, int(400e6 // (nw * n * k)) + 1))
+            ws = [[torch.randint(0, 120, (n, k), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+                   for _ in range(nw)] for _ in range(nbuf)]
+            sc = torch.rand(n, device=dev)
+            xp = ops.split3(torch.randn(m, k, device=dev).to(torch.bfloat16), 4)
+            res = torch.randn(m, n, device=dev).to(torch.bfloat16)
+
+            def call(i):
+                w = ws[i % nbuf]
+                if nw == 2:
+                    return ops.w8x3_geglu(xp, 4, w[0], sc, w[1], sc, out_bf16=False, out_planes=True)
+                if name == "qkv":
+                    return ops.w8x3_linear(xp, 4, w[0], sc)
+                return ops.w8x3_linear(xp, 4, w[0], sc, epilogue=ops.EPI_RESIDUAL, residual=res)
+
+            for i in range(3):
+                call(i)
+            torch.cuda.synchronize()
+            iters = 2 * nbuf
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for i in range(iters):
+                    call(i)
+            graph.replay()
+            torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            out = fn(planes, shift, w8, *a, **kw)
-            e1.record()
-            m, k, n = planes.shape[1], planes.shape[2], w8.shape[0]
-            rec.append((e0, e1, nw * (n * k + 4 * n) + 2 * m * k + 2 * m * n, 2.0 * nw * m * n * k))
-            return out
-        return wrapper
+            best = float("inf")
+            for _ in range(3):
+                e0.record()
+                graph.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                best = min(best, e0.elapsed_time(e1) / iters * 1e3)
+            byts = nw * (n * k + 4 * n) + 2 * m * k + 2 * m * n
+            rows.append({"gemm": name, "M": m, "N": n, "K": k, "nw": nw, "us": round(best, 2), "count": count,
+                         "GBps": round(byts / best / 1e3, 1), "TFps": round(2.0 * nw * m * n * k / best / 1e6, 1),
+                         "bytes": byts, "flops": 2.0 * nw * m * n * k})
+            del ws, graph
+        out[gname] = rows
+    torch.cuda.empty_cache()
 
-    import tybok_b200.pi05 as P
+    def agg(rows, key):
+        return sum(r["count"] * r[key] for r in rows) / sum(r["count"] * r["us"] for r in rows)
 
-    P.ops.w8x3_linear, P.ops.w8x3_geglu = timed(orig_lin, 1), timed(orig_geglu, 2)
-    try:
-        engine.model.sample_actions(*engine._dummy_inputs(engine.batch_size))
-        torch.cuda.synchronize()
-        rec.clear()
-        engine.model.sample_actions(*engine._dummy_inputs(engine.batch_size))
-        torch.cuda.synchronize()
-    finally:
-        P.ops.w8x3_linear, P.ops.w8x3_geglu = orig_lin, orig_geglu
-        lib.tybok_set_pdl(1)
-    ms = sum(a.elapsed_time(b) for a, b, _, _ in rec)
-    byts = sum(r[2] for r in rec)
-    flops = sum(r[3] for r in rec)
-    achieved = byts / (ms * 1e-3) / 1e9
-    return {"bound": "hbm", "kernel": "w8_gemm_kernel", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
-            "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None, "peak_source": peaks_kind,
-            "launches": len(rec), "gemm_ms_per_chunk": round(ms, 3), "algorithmic_bytes": byts,
-            "tensor_tflops": round(flops / (ms * 1e-3) / 1e12, 1)}
+    hbm = agg(out["expert"], "bytes") / 1e3  # bytes/us -> GB/s
+    tc = agg(out["prefix"], "flops") / 1e6  # flops/us -> TFLOP/s
+    strip = lambda rows: [{k: v for k, v in r.items() if k not in ("bytes", "flops")} for r in rows]  # noqa: E731
+    return {
+        "bound": "hbm", "kernel": "w8_gemm_kernel (action-expert launches, M=%d)" % (b * s.chunk),
+        "achieved": round(hbm, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(hbm / peaks["hbm_gbs"], 4),
+        "traffic": None, "peak_source": peaks_kind, "per_shape": strip(out["expert"]),
+        "prefix": {"bound": "tensor", "achieved": round(tc, 1), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                   "frac": round(tc / peaks["bf16_tflops"], 4), "per_shape": strip(out["prefix"])},
+    }
 
 
 def _cpu_chunk_times(reps: int, seed: int = 0) -> tuple[list[float], dict]:
