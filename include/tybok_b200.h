@@ -86,6 +86,25 @@ int tybok_w8a16_geglu(const void* x, const void* w8_gate, const float* scale_gat
                       const float* scale_up, void* h, int M, int I, int K, int64_t ldx, int64_t ldh, int token_tile,
                       int splits, void* workspace, size_t workspace_bytes, int* status_word, void* stream);
 
+/* tybok_w8a16_linear for callers that cannot allocate device memory and so cannot supply a
+ * workspace (a plugin inside a process whose GPU memory pool belongs to another runtime, a
+ * control loop that bans allocator calls once it is running, a binding without a device
+ * allocator).  It has no counterpart in the reference.  The activation planes live in a fixed
+ * 1.5 MiB device array inside the library (TYBOK_STATIC_PLANES_BYTES; held by every GPU that
+ * loads the library until exit), so 3*M*K must not exceed that size -- e.g. M = 128 tokens at
+ * K = 4096 -- and larger problems are refused with TYBOK_ERR_WORKSPACE.  It calls no
+ * cudaMalloc/cudaFree and no allocating library routine.  The first call on each device looks
+ * the array's address up (cudaGetSymbolAddress); make that first call before any stream
+ * capture.  All calls share the one array, which keeps whatever the previous call left in it
+ * (nothing needs clearing: each call overwrites every byte it later reads); two calls that can
+ * overlap on the GPU (different streams, or graph branches) race on it -- serialise them.
+ * Arguments as tybok_w8a16_linear, minus the workspace, token_tile and splits. */
+#define TYBOK_STATIC_PLANES_BYTES (3u * 128u * 4096u)
+int tybok_w8a16_linear_noalloc(const void* x, const void* w8, const float* scale, const void* bias, void* y, int M,
+                               int N, int K, int64_t ldx, int64_t ldy, int epilogue, const void* residual,
+                               int64_t ldres, const void* gate, int64_t ldgate, int rows_per_gate, int gate_is_bf16,
+                               int* status_word, void* stream);
+
 /* The same two operations on activation planes (one launch each).  Either output may be NULL:
  *   y / h        bf16 result, row stride ldy / ldh
  *   y_planes / h_planes  [3][M][N] planes of result * 2^out_shift, ready for the next GEMM

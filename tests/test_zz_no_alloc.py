@@ -1,0 +1,56 @@
+"""The allocation-free W8A16 entry point against the workspace-taking one.
+
+``tybok_w8a16_linear_noalloc`` is for hosts that cannot give the library a workspace (no device
+allocator of their own, or a rule against allocating once running): its scratch is a fixed
+array inside the library.  It must produce exactly what ``tybok_w8a16_linear`` produces, also on
+a second call that reuses the array with a different problem, and refuse problems that do not
+fit.  Collected last so that a first-failure stop has already run every other test."""
+
+import pytest
+import torch
+
+from oracle import w8_ref
+
+pytestmark = pytest.mark.gpu
+
+
+def _problem(seed, m, n, k):
+    g = torch.Generator().manual_seed(seed)
+    w8, scale = w8_ref.quantize_w8(torch.empty(n, k).normal_(0, 0.02, generator=g))
+    x = torch.empty(m, k).normal_(0, 1, generator=g).to(torch.bfloat16)
+    res = torch.empty(m, n).normal_(0, 1, generator=g).to(torch.bfloat16)
+    return x.cuda(), w8.cuda(), scale.cuda(), res.cuda(), (x, w8, scale, res)
+
+
+def test_noalloc_matches_workspace_entry_point_twice():
+    from tybok_b200 import _lib
+
+    lib = _lib.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    for seed, (m, n, k) in enumerate([(50, 1024, 2048), (128, 256, 4096)]):  # second call reuses the array
+        x, w8, scale, res, cpu = _problem(seed, m, n, k)
+        y_ws = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+        y_na = torch.empty_like(y_ws)
+        need = lib.tybok_w8a16_workspace_bytes(m, n, k, 0)
+        ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+        rc = lib.tybok_w8a16_linear(x.data_ptr(), w8.data_ptr(), scale.data_ptr(), None, y_ws.data_ptr(), m, n, k, k, n,
+                                    2, res.data_ptr(), n, None, 0, 1, 0, 0, 0, ws.data_ptr(), need, None, stream)
+        assert rc == 0, lib.tybok_last_error()
+        rc = lib.tybok_w8a16_linear_noalloc(x.data_ptr(), w8.data_ptr(), scale.data_ptr(), None, y_na.data_ptr(), m, n,
+                                            k, k, n, 2, res.data_ptr(), n, None, 0, 1, 0, None, stream)
+        assert rc == 0, lib.tybok_last_error()
+        torch.cuda.synchronize()
+        ref = cpu[3] + w8_ref.w8_linear(cpu[0], cpu[1], cpu[2])
+        assert w8_ref.rel_l2(y_na.cpu(), ref) <= 1e-2  # the tolerance of every W8 linear test
+        assert torch.equal(y_na, y_ws)  # same kernels, same planes: identical bits
+
+
+def test_noalloc_refuses_what_does_not_fit():
+    from tybok_b200 import _lib
+
+    lib = _lib.load()
+    x, w8, scale, _, _ = _problem(5, 16, 128, 128)
+    y = torch.empty(16, 128, dtype=torch.bfloat16, device="cuda")
+    rc = lib.tybok_w8a16_linear_noalloc(x.data_ptr(), w8.data_ptr(), scale.data_ptr(), None, y.data_ptr(), 129, 128,
+                                        4096, 4096, 128, 0, None, 0, None, 0, 1, 0, None, None)
+    assert rc == 3 and b"TYBOK_STATIC_PLANES_BYTES" in lib.tybok_last_error()

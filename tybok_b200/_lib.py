@@ -44,6 +44,11 @@ SIGNATURES = {
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_i64, c_i64, c_int, c_void_p, c_i64,
          c_void_p, c_i64, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p],
     ),
+    "tybok_w8a16_linear_noalloc": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_i64, c_i64, c_int, c_void_p, c_i64,
+         c_void_p, c_i64, c_int, c_int, c_void_p, c_void_p],
+    ),
     "tybok_w8a16_geglu": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_i64, c_i64, c_int, c_int,

@@ -665,6 +665,57 @@ int tybok_w8a16_linear(const void* x, const void* w8, const float* scale, const 
                            gate, ldgate, rows_per_gate, gate_is_bf16, token_tile, splits, status_word, stream);
 }
 
+// ---- W8A16 linear for callers that may not allocate ------------------------------------------
+// Some hosts of this library cannot hand it a workspace: a plugin running inside a serving
+// process whose memory pool is owned (and fully reserved) by another runtime, a real-time
+// control loop that forbids allocator calls after start-up, or a foreign-language binding that
+// has no device allocator at all.  For them the activation planes of tybok_w8a16_linear live in
+// this fixed device array instead of a caller-provided buffer.  Every GPU that loads the
+// library holds the array until the process exits.
+static __device__ __align__(256) uint8_t g_static_planes[TYBOK_STATIC_PLANES_BYTES];
+
+// Host code must not pass `g_static_planes` itself to a kernel or a tensor map: on the host
+// that name is only a stand-in for the symbol.  Its device address is looked up once per
+// device, with that device current.
+static void* static_planes_ptr(int* rc) {
+  static void* ptr[64] = {};
+  *rc = TYBOK_OK;
+  const int dev = tb::host::current_device();
+  if (dev < 0 || dev >= 64) {
+    *rc = tb::host::fail(TYBOK_ERR_CUDA, "w8a16_linear_noalloc: no current CUDA device");
+    return nullptr;
+  }
+  if (!ptr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_planes) != cudaSuccess || !p) {
+      *rc = tb::host::fail_cuda("w8a16_linear_noalloc: cudaGetSymbolAddress(g_static_planes)");
+      return nullptr;
+    }
+    ptr[dev] = p;
+  }
+  return ptr[dev];
+}
+
+int tybok_w8a16_linear_noalloc(const void* x, const void* w8, const float* scale, const void* bias, void* y, int M,
+                               int N, int K, int64_t ldx, int64_t ldy, int epilogue, const void* residual,
+                               int64_t ldres, const void* gate, int64_t ldgate, int rows_per_gate, int gate_is_bf16,
+                               int* status_word, void* stream) {
+  if (M <= 0 || K <= 0) return tb::host::fail(TYBOK_ERR_ARG, "w8a16_linear_noalloc: M and K must be positive");
+  const size_t need = static_cast<size_t>(3) * static_cast<size_t>(M) * static_cast<size_t>(K);
+  if (need > TYBOK_STATIC_PLANES_BYTES)
+    return tb::host::fail(TYBOK_ERR_WORKSPACE,
+                          "w8a16_linear_noalloc: 3*M*K exceeds TYBOK_STATIC_PLANES_BYTES (1.5 MiB); use "
+                          "tybok_w8a16_linear with a caller-owned workspace for larger problems");
+  int rc = TYBOK_OK;
+  void* planes = static_planes_ptr(&rc);
+  if (!planes) return rc;
+  // Nothing in the array has to start at zero: split3 overwrites all 3*M*K bytes the GEMM reads.
+  const int shift = TYBOK_DEFAULT_X_SHIFT;
+  if (int r = tybok_split3(x, ldx, planes, M, K, shift, stream)) return r;
+  return tybok_w8x3_linear(planes, shift, w8, scale, bias, y, ldy, nullptr, 0, M, N, K, epilogue, residual, ldres,
+                           gate, ldgate, rows_per_gate, gate_is_bf16, 0, 0, status_word, stream);
+}
+
 int tybok_w8a16_geglu(const void* x, const void* w8_gate, const float* scale_gate, const void* w8_up,
                       const float* scale_up, void* h, int M, int I, int K, int64_t ldx, int64_t ldh, int token_tile,
                       int splits, void* workspace, size_t workspace_bytes, int* status_word, void* stream) {
