@@ -58,6 +58,7 @@ __device__ __forceinline__ float rope1(float x, float rot, float c, float s) {
 }
 
 __global__ void rope_store_kernel(const RopeParams p) {
+  if (p.pdl) pdl_launch_dependents();  // the next kernel may start its preamble now
   if (p.pdl) pdl_wait();
   const int vec_per_head = p.D / 16;  // each thread: 8 elements of the first half + their partners
   const int slots = p.H + 2 * p.G;
@@ -105,7 +106,6 @@ __global__ void rope_store_kernel(const RopeParams p) {
     *reinterpret_cast<uint4*>(dst + c * 8) = lo;
     *reinterpret_cast<uint4*>(dst + half + c * 8) = hi;
   }
-  if (p.pdl) pdl_launch_dependents();
 }
 
 struct AttnParams {
@@ -127,6 +127,7 @@ struct __align__(8) AttnBars {
   uint32_t valid[4];     // key-validity bits of this CTA's 128 keys
   float row_max[AT_BQ];  // per query row: running maximum (log2 domain) and sum of this key block
   float row_sum[AT_BQ];
+  float wn[AT_MAX_SPLITS][AT_BQ];  // merge weights of the rows this CTA owns: exp2(m_s - m) / denominator
 };
 
 __device__ __forceinline__ bool at_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
@@ -207,6 +208,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
   if (warp == 0) {
     if (lane == 0) {
+      if (p.pdl) pdl_launch_dependents();  // the o-projection GEMM may start prefetching its weights
       if (p.pdl) pdl_wait();
       const int qrow = b * p.L + qt * AT_BQ;
       const int krow = (b * p.G + g) * p.Lcap + key0;
@@ -215,7 +217,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       for (int c = 0; c < 4; ++c) tma_load_2d(sk + c * AT_CHUNK, &tm_k, &bars.qk_full, c * 64, krow);
       mbar_arrive_expect_tx(&bars.v_full, AT_TILE);
       for (int c = 0; c < 4; ++c) tma_load_2d(sv + c * AT_CHUNK, &tm_v, &bars.v_full, c * 64, krow);
-      if (p.pdl) pdl_launch_dependents();
     }
   } else if (warp == 1) {
     const bool leader = elect_one();
@@ -298,14 +299,19 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       ok = __all_sync(0xffffffffu, at_wait(&bars.o_full, 0, &bars.abort));
       if (ok) {
         tc_fence_after();
-        float* stage = reinterpret_cast<float*>(smem);  // 128 KB: the Q and K tiles are no longer needed
+        // 128 KB staging tile over the (no longer needed) Q and K tiles: [row][64 float4], the
+        // float4 index XORed with (row & 7) so that a warp's 16-byte stores spread over all banks.
+        float4* stage = reinterpret_cast<float4*>(smem);
 #pragma unroll 1
         for (int c = 0; c < 8; ++c) {
           uint32_t v[32];
           tmem_ld32(t_o + lane_addr + c * 32, v);
           tc_wait_ld();
 #pragma unroll
-          for (int e = 0; e < 32; ++e) stage[(c * 32 + e) * AT_BQ + row] = __uint_as_float(v[e]);
+          for (int j = 0; j < 8; ++j)
+            stage[row * 64 + ((c * 8 + j) ^ (row & 7))] =
+                make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
+                            __uint_as_float(v[4 * j + 3]));
         }
       }
     }
@@ -325,67 +331,76 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   }
 
   if (warp >= 2 && !bars.abort) {
-    // Merge: this CTA owns query rows [r0, r1) of the tile; thread = (row, 64-column group).
+    // Merge: this CTA owns query rows [r0, r1) of the tile; thread = (4 output columns, row parity).
     const int et = tid - 64;
-    const int rl = et & 31, cg = et >> 5;
-    const int rpr = (AT_BQ + p.nsplit - 1) / p.nsplit;
-    const int r0 = sp * rpr, r1 = min(AT_BQ, r0 + rpr);
+    const int c4 = et & 63, rsub = et >> 6;
+    // Only the tile's real query rows are merged, split evenly over the key-block CTAs.
+    const int nvalid = min(AT_BQ, p.L - qt * AT_BQ);
+    const int rpr = (nvalid + p.nsplit - 1) / p.nsplit;
+    const int r0 = sp * rpr, r1 = min(nvalid, r0 + rpr);
     const uint32_t stage_addr = smem_u32(smem);
     const uint32_t max_addr = smem_u32(&bars.row_max[0]), sum_addr = smem_u32(&bars.row_sum[0]);
     const long long hd = static_cast<long long>(p.H) * AT_D;
     const long long plane = static_cast<long long>(p.B) * p.L * hd;
-    for (int r = r0 + rl; r < r1; r += 32) {
-      const int t = qt * AT_BQ + r;
-      if (t >= p.L) continue;
-      float w[AT_MAX_SPLITS];
+    if (r0 + et < r1) {  // one thread per owned row: normalised weight of every key block
+      const int r = r0 + et;
+      float w[AT_MAX_SPLITS], l[AT_MAX_SPLITS];
       float mx = -1e30f;
-      for (int s = 0; s < p.nsplit; ++s) {
-        float v;
-        const uint32_t a = p.nsplit > 1 ? dsmem_addr(max_addr + r * 4, s) : max_addr + r * 4;
-        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(a));
-        w[s] = v;
-        mx = fmaxf(mx, v);
+#pragma unroll
+      for (int s = 0; s < AT_MAX_SPLITS; ++s) {
+        w[s] = -1e30f;
+        l[s] = 0.f;
+        if (s < p.nsplit) {
+          const uint32_t am = p.nsplit > 1 ? dsmem_addr(max_addr + r * 4, s) : max_addr + r * 4;
+          const uint32_t al = p.nsplit > 1 ? dsmem_addr(sum_addr + r * 4, s) : sum_addr + r * 4;
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(w[s]) : "r"(am));
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(l[s]) : "r"(al));
+        }
+        mx = fmaxf(mx, w[s]);
       }
       float denom = 0.f;
-      for (int s = 0; s < p.nsplit; ++s) {
-        float l;
-        const uint32_t a = p.nsplit > 1 ? dsmem_addr(sum_addr + r * 4, s) : sum_addr + r * 4;
-        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(l) : "r"(a));
-        w[s] = exp2f(w[s] - mx);  // weight of key block s (0 for a block without valid keys)
-        denom += w[s] * l;
+#pragma unroll
+      for (int s = 0; s < AT_MAX_SPLITS; ++s) {
+        w[s] = s < p.nsplit ? exp2f(w[s] - mx) : 0.f;  // 0 for a block without valid keys
+        denom += w[s] * l[s];
       }
       const float inv = denom > 0.f ? 1.0f / denom : 0.f;
-      const long long orow = (static_cast<long long>(b) * p.L + t) * hd + static_cast<long long>(h) * AT_D + cg * 64;
-#pragma unroll 1
-      for (int c8 = 0; c8 < 8; ++c8) {  // 8 columns at a time
-        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int s = 0; s < p.nsplit; ++s) {  // block order: bit-reproducible
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const uint32_t local = stage_addr + (((cg * 64 + c8 * 8 + e) * AT_BQ) + r) * 4;
-            const uint32_t a = p.nsplit > 1 ? dsmem_addr(local, s) : local;
-            float v;
-            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(a));
-            acc[e] += w[s] * v;
-          }
-        }
-        __nv_bfloat162 o2[4];
+      for (int s = 0; s < AT_MAX_SPLITS; ++s) bars.wn[s][et] = w[s] * inv;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps, unconditionally
+#pragma unroll 4
+    for (int r = r0 + rsub; r < r1; r += 2) {
+      const int t = qt * AT_BQ + r;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      const uint32_t local = stage_addr + (r * 64 + (c4 ^ (r & 7))) * 16;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(acc[2 * e] * inv, acc[2 * e + 1] * inv);
-        if (p.out) *reinterpret_cast<uint4*>(p.out + orow + c8 * 8) = *reinterpret_cast<const uint4*>(o2);
-        if (p.out_planes) {
-          const float lo[4] = {__bfloat162float(o2[0].x) * p.plane_scale, __bfloat162float(o2[0].y) * p.plane_scale,
-                               __bfloat162float(o2[1].x) * p.plane_scale, __bfloat162float(o2[1].y) * p.plane_scale};
-          const float hi[4] = {__bfloat162float(o2[2].x) * p.plane_scale, __bfloat162float(o2[2].y) * p.plane_scale,
-                               __bfloat162float(o2[3].x) * p.plane_scale, __bfloat162float(o2[3].y) * p.plane_scale};
-          uint2 w1, w2, w3;
-          split3_quad(lo, w1.x, w2.x, w3.x);
-          split3_quad(hi, w1.y, w2.y, w3.y);
-          uint8_t* dst = p.out_planes + orow + c8 * 8;
-          *reinterpret_cast<uint2*>(dst) = w1;
-          *reinterpret_cast<uint2*>(dst + plane) = w2;
-          *reinterpret_cast<uint2*>(dst + 2 * plane) = w3;
+      for (int s = 0; s < AT_MAX_SPLITS; ++s) {  // block order: bit-reproducible
+        if (s < p.nsplit) {
+          const float ws = bars.wn[s][r - r0];
+          const float4 v = ld_dsmem_f4(p.nsplit > 1 ? dsmem_addr(local, s) : local);
+          acc.x += ws * v.x; acc.y += ws * v.y; acc.z += ws * v.z; acc.w += ws * v.w;
         }
+      }
+      const float inv = 1.0f;
+      const __nv_bfloat162 o01 = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+      const __nv_bfloat162 o23 = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+      const long long off = (static_cast<long long>(b) * p.L + t) * hd + static_cast<long long>(h) * AT_D + c4 * 4;
+      if (p.out) {
+        uint2 st;
+        st.x = *reinterpret_cast<const uint32_t*>(&o01);
+        st.y = *reinterpret_cast<const uint32_t*>(&o23);
+        *reinterpret_cast<uint2*>(p.out + off) = st;
+      }
+      if (p.out_planes) {
+        const float xs[4] = {__bfloat162float(o01.x) * p.plane_scale, __bfloat162float(o01.y) * p.plane_scale,
+                             __bfloat162float(o23.x) * p.plane_scale, __bfloat162float(o23.y) * p.plane_scale};
+        uint32_t w1, w2, w3;
+        split3_quad(xs, w1, w2, w3);
+        uint8_t* dst = p.out_planes + off;
+        *reinterpret_cast<uint32_t*>(dst) = w1;
+        *reinterpret_cast<uint32_t*>(dst + plane) = w2;
+        *reinterpret_cast<uint32_t*>(dst + 2 * plane) = w3;
       }
     }
   }

@@ -35,17 +35,21 @@ struct NormParams {
   int pdl;
 };
 
+template <int VEC>
 __global__ void __launch_bounds__(128) rmsnorm_kernel(const NormParams p) {
+  // Let the next kernel in the stream start its preamble (weight prefetch) right away; it still
+  // waits for this grid to finish before it reads what is written here.
+  if (p.pdl) pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m = blockIdx.x * 4 + warp;
   if (p.pdl) pdl_wait();
   if (m < p.M) {
     const int nvec = p.W / 8;  // 8-element vectors per row
     const __nv_bfloat16* row = p.x + m * p.ldx;
-    float v[NORM_MAX_VEC][8];
+    float v[VEC][8];
     float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < NORM_MAX_VEC; ++i) {
+    for (int i = 0; i < VEC; ++i) {
       const int c = lane + 32 * i;
       if (c < nvec) {
         const uint4 raw = *reinterpret_cast<const uint4*>(row + c * 8);
@@ -64,17 +68,25 @@ __global__ void __launch_bounds__(128) rmsnorm_kernel(const NormParams p) {
     const float* mod = p.mod ? p.mod + static_cast<long long>(m / p.rows_per_group) * p.ldmod : nullptr;
     const long long plane = static_cast<long long>(p.M) * p.W;
 #pragma unroll
-    for (int i = 0; i < NORM_MAX_VEC; ++i) {
+    for (int i = 0; i < VEC; ++i) {
       const int c = lane + 32 * i;
       if (c < nvec) {
         float o[8];
+        // x * rstd is formed in fp32 (the bf16 x promotes), as in the reference's _norm
+        float sc[8], sh[8];
+        {
+          const float* a = mod ? mod + c * 8 : p.weight + c * 8;
+          const float4 a0 = *reinterpret_cast<const float4*>(a), a1 = *reinterpret_cast<const float4*>(a + 4);
+          sc[0] = a0.x; sc[1] = a0.y; sc[2] = a0.z; sc[3] = a0.w; sc[4] = a1.x; sc[5] = a1.y; sc[6] = a1.z; sc[7] = a1.w;
+          if (mod) {
+            const float4 b0 = *reinterpret_cast<const float4*>(a + p.W), b1 = *reinterpret_cast<const float4*>(a + p.W + 4);
+            sh[0] = b0.x; sh[1] = b0.y; sh[2] = b0.z; sh[3] = b0.w; sh[4] = b1.x; sh[5] = b1.y; sh[6] = b1.z; sh[7] = b1.w;
+          }
+        }
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          const int k = c * 8 + e;
-          // x * rstd is formed in fp32 (the bf16 x promotes), as in the reference's _norm
-          float t = v[i][e] * rstd;
-          if (mod) t = t * (1.0f + mod[k]) + mod[p.W + k];
-          else if (p.weight) t = t * (1.0f + p.weight[k]);
+          float t = v[i][e] * rstd * (1.0f + sc[e]);
+          if (mod) t = v[i][e] * rstd * (1.0f + sc[e]) + sh[e];
           o[e] = t;
         }
         __nv_bfloat162 b[4];
@@ -97,7 +109,6 @@ __global__ void __launch_bounds__(128) rmsnorm_kernel(const NormParams p) {
       }
     }
   }
-  if (p.pdl) pdl_launch_dependents();
 }
 
 }  // namespace tb
@@ -106,11 +117,12 @@ extern "C" int tybok_rmsnorm(const void* x, int64_t ldx, const float* weight, co
                              int rows_per_group, int M, int W, float eps, void* y, int64_t ldy, void* y_planes,
                              int out_shift, void* stream) {
   using namespace tb;
-  if (!x || (!y && !y_planes)) return host::fail(TYBOK_ERR_ARG, "rmsnorm: null pointer argument");
+  if (!x || (!y && !y_planes) || (!weight && !mod)) return host::fail(TYBOK_ERR_ARG, "rmsnorm: null pointer argument");
   if (M <= 0 || W <= 0 || W % 8 != 0 || W > NORM_MAX_VEC * 256)
     return host::fail(TYBOK_ERR_ARG, "rmsnorm: W must be a multiple of 8 and <= 4096");
   if (ldx % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (y && ((reinterpret_cast<uintptr_t>(y) & 15) || ldy % 8 != 0)) ||
-      (y_planes && (reinterpret_cast<uintptr_t>(y_planes) & 7)))
+      (y_planes && (reinterpret_cast<uintptr_t>(y_planes) & 7)) ||
+      ((reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(mod)) & 15) || (mod && ldmod % 4 != 0))
     return host::fail(TYBOK_ERR_ARG, "rmsnorm: rows must be 16-byte aligned (ld % 8 == 0)");
   if (mod && rows_per_group <= 0) return host::fail(TYBOK_ERR_ARG, "rmsnorm: rows_per_group must be positive");
   if (out_shift < -60 || out_shift > 60) return host::fail(TYBOK_ERR_ARG, "rmsnorm: exponent shift out of range");
@@ -129,7 +141,14 @@ extern "C" int tybok_rmsnorm(const void* x, int64_t ldx, const float* weight, co
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = p.pdl;
-  if (cudaLaunchKernelEx(&cfg, rmsnorm_kernel, p) != cudaSuccess) return host::fail_cuda("launch rmsnorm_kernel");
+  const int per_lane = (W / 8 + 31) / 32;
+  cudaError_t e;
+  if (per_lane <= 1) e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<1>, p);
+  else if (per_lane <= 2) e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<2>, p);
+  else if (per_lane <= 4) e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<4>, p);
+  else if (per_lane <= 8) e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<8>, p);
+  else e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<NORM_MAX_VEC>, p);
+  if (e != cudaSuccess) return host::fail_cuda("launch rmsnorm_kernel");
   host::count_launch();
   return TYBOK_OK;
 }

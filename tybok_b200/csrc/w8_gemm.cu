@@ -47,7 +47,6 @@ constexpr int BK = 128;  // K per pipeline stage (one 128-byte swizzle row of 8-
 constexpr int W_TILE_BYTES = BN * BK;
 constexpr int MAX_STAGES = 8;
 constexpr int EPI_WARPS = 8;
-constexpr int EPI_THREADS = EPI_WARPS * 32;
 constexpr int THREADS = 32 * (2 + EPI_WARPS);
 constexpr int DYN_SMEM_MAX = 226 * 1024;  // 227 KB per CTA minus 1 KB left for static shared memory
 constexpr int MAX_SPLITS = 8;             // portable cluster size
@@ -150,6 +149,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
   const uint32_t tmem = bars.tmem_base;
   // Per-thread epilogue constants (4 consecutive channels), fetched while the main loop runs.
   float s0[4] = {0, 0, 0, 0}, s1[4] = {0, 0, 0, 0}, b0[4] = {0, 0, 0, 0};
+  uint2 res_pf[4] = {};  // residual of this thread's first four token rows, fetched early
   long long* tr = p.trace ? p.trace + 16ll * ((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) : nullptr;
   if (tr && tid == 0) { tr[0] = t_start; tr[1] = clock64(); }
 
@@ -158,6 +158,9 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     if (lane == 0) {
       int issued = 0;
       bool ok = true;
+      // Dependents may start their own preamble (their weight prefetch) as soon as every CTA of
+      // this grid is running; they still wait for this grid to complete before touching its output.
+      if (p.pdl) pdl_launch_dependents();
       // Weights do not depend on the previous kernel in the stream: request them before waiting
       // for it; the activation planes are requested once the dependency has resolved.
       const int pre = min(ns, nkb);
@@ -187,7 +190,6 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
         tma_load_3d(st + x_off, &tm_x, &bars.full[s], k0, t_tile * p.bt, 0);
         issued = i + 1;
       }
-      if (p.pdl) pdl_launch_dependents();
       if (!ok || bars.abort) {
         // Unwinding: do not leave the CTA while its own bulk copies may still land in its
         // shared memory. Wait (bounded) for the newest copy of every stage.
@@ -268,6 +270,21 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
         if (p.bias0) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) b0[e] = __bfloat162float(p.bias0[n + e]);
+        }
+        if (p.epi == EPI_RESIDUAL) {
+          // The residual was written by an earlier kernel: wait for it once, then fetch the rows
+          // this thread will finish first, long before the accumulator is ready.
+          if (p.pdl) pdl_wait();
+          const int rank = p.splits > 1 ? static_cast<int>(cluster_ctarank()) : 0;
+          const int rpr = (p.bt + p.splits - 1) / p.splits;
+          const int r1 = min(p.bt, rank * rpr + rpr);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int t = rank * rpr + ((tid - 64) >> 5) + 8 * u;
+            const int m = t_tile * p.bt + t;
+            if (t < r1 && m < p.M)
+              res_pf[u] = *reinterpret_cast<const uint2*>(p.res + static_cast<long long>(m) * p.ldres + n);
+          }
         }
       }
     }
@@ -391,7 +408,8 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
 #pragma unroll
           for (int e = 0; e < 4; ++e) o[e] = bf16_round(o[e] * gv[e]);
         }
-        const uint2 rr = *reinterpret_cast<const uint2*>(p.res + static_cast<long long>(m) * p.ldres + n);
+        const uint2 rr = (tb == r0 + rgrp) ? res_pf[u]
+                                           : *reinterpret_cast<const uint2*>(p.res + static_cast<long long>(m) * p.ldres + n);
         const __nv_bfloat162 r01 = *reinterpret_cast<const __nv_bfloat162*>(&rr.x);
         const __nv_bfloat162 r23 = *reinterpret_cast<const __nv_bfloat162*>(&rr.y);
         o[0] += __bfloat162float(r01.x); o[1] += __bfloat162float(r01.y);
@@ -437,6 +455,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
 // x[M,K] (bf16, row stride ldx) -> three e5m2 planes [3][M][K] holding x * 2^shift.
 __global__ void split3_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ planes, int M,
                               int K, float mult, int pdl) {
+  if (pdl) pdl_launch_dependents();  // the next kernel may start its preamble now
   if (pdl) pdl_wait();
   const long long plane = static_cast<long long>(M) * K;
   const int kv = K / 8;  // 8 elements per thread
@@ -458,7 +477,6 @@ __global__ void split3_kernel(const __nv_bfloat16* __restrict__ x, long long ldx
     *reinterpret_cast<uint2*>(dst + plane) = w2;
     *reinterpret_cast<uint2*>(dst + 2 * plane) = w3;
   }
-  if (pdl) pdl_launch_dependents();
 }
 
 // ------------------------------------------------------------------------------------ host
