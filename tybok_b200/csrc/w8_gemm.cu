@@ -62,6 +62,8 @@ struct GemmParams {
   int kb_per_split;
   int nstages;
   int tmem_cols;
+  int stage_off;  // byte offset of the epilogue staging tile: 0 (over the idle ring) without split-K,
+                  // behind the ring with split-K, because peers write into it while this CTA still streams
   int merge;     // 1: the three planes are one UMMA of N = 3*bt whose column groups the epilogue adds
   int epi;
   int pdl;
@@ -138,6 +140,16 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     mbar_init(&bars.tmem_full, 1);
     bars.abort = 0;
     fence_barrier_init();
+    // Weights depend on nothing that runs before this kernel: request the first stages now,
+    // before the rest of the CTA has even finished its set-up.
+    const int pre = min(ns, nkb);
+    for (int i = 0; i < pre; ++i) {
+      uint8_t* st = smem + i * stage_bytes;
+      mbar_arrive_expect_tx(&bars.full[i], stage_bytes);
+      const int k0 = (kb0 + i) * BK;
+      tma_load_2d(st, &tm_w0, &bars.full[i], k0, n_tile * BN);
+      if (p.nw == 2) tma_load_2d(st + W_TILE_BYTES, &tm_w1, &bars.full[i], k0, n_tile * BN);
+    }
   }
   if (warp == 1) {
     tmem_alloc(&bars.tmem_base, p.tmem_cols);
@@ -150,6 +162,12 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
   // Per-thread epilogue constants (4 consecutive channels), fetched while the main loop runs.
   float s0[4] = {0, 0, 0, 0}, s1[4] = {0, 0, 0, 0}, b0[4] = {0, 0, 0, 0};
   uint2 res_pf[4] = {};  // residual of this thread's first four token rows, fetched early
+  // Split-K ownership: the tile's real token rows are divided evenly over the cluster ranks.
+  const int m_base = t_tile * p.bt;
+  const int nvalid = min(p.bt, p.M - m_base);
+  const int rpr = (nvalid + p.splits - 1) / p.splits;
+  const int rank = p.splits > 1 ? static_cast<int>(cluster_ctarank()) : 0;
+  const int own_rows = max(0, min(nvalid, rank * rpr + rpr) - rank * rpr);
   long long* tr = p.trace ? p.trace + 16ll * ((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) : nullptr;
   if (tr && tid == 0) { tr[0] = t_start; tr[1] = clock64(); }
 
@@ -161,16 +179,9 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
       // Dependents may start their own preamble (their weight prefetch) as soon as every CTA of
       // this grid is running; they still wait for this grid to complete before touching its output.
       if (p.pdl) pdl_launch_dependents();
-      // Weights do not depend on the previous kernel in the stream: request them before waiting
-      // for it; the activation planes are requested once the dependency has resolved.
+      // The weight tiles of the first stages were requested during set-up; the activation planes
+      // are requested once the programmatic dependency has resolved.
       const int pre = min(ns, nkb);
-      for (int i = 0; i < pre; ++i) {
-        uint8_t* st = smem + i * stage_bytes;
-        mbar_arrive_expect_tx(&bars.full[i], stage_bytes);
-        const int k0 = (kb0 + i) * BK;
-        tma_load_2d(st, &tm_w0, &bars.full[i], k0, n_tile * BN);
-        if (p.nw == 2) tma_load_2d(st + W_TILE_BYTES, &tm_w1, &bars.full[i], k0, n_tile * BN);
-      }
       if (p.pdl) pdl_wait();
       for (int i = 0; i < pre; ++i)
         tma_load_3d(smem + i * stage_bytes + x_off, &tm_x, &bars.full[i], (kb0 + i) * BK, t_tile * p.bt, 0);
@@ -275,15 +286,12 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
           // The residual was written by an earlier kernel: wait for it once, then fetch the rows
           // this thread will finish first, long before the accumulator is ready.
           if (p.pdl) pdl_wait();
-          const int rank = p.splits > 1 ? static_cast<int>(cluster_ctarank()) : 0;
-          const int rpr = (p.bt + p.splits - 1) / p.splits;
-          const int r1 = min(p.bt, rank * rpr + rpr);
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
-            const int t = rank * rpr + ((tid - 64) >> 5) + 8 * u;
-            const int m = t_tile * p.bt + t;
-            if (t < r1 && m < p.M)
-              res_pf[u] = *reinterpret_cast<const uint2*>(p.res + static_cast<long long>(m) * p.ldres + n);
+            const int rl = ((tid - 64) >> 5) + 8 * u;
+            if (rl < own_rows)
+              res_pf[u] = *reinterpret_cast<const uint2*>(
+                  p.res + static_cast<long long>(m_base + rank * rpr + rl) * p.ldres + n);
           }
         }
       }
@@ -293,8 +301,12 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     if (tr && ew == 0 && lane == 0) tr[4] = clock64();
     if (ok) {
       tc_fence_after();
-      float* stage = reinterpret_cast<float*>(smem);
-      const int ngroups = p.bt / 16;
+      // Every token row is written straight into the staging tile of the CTA that owns it
+      // (slot [split][w][row within owner][128 channels], through distributed shared memory when
+      // the owner is another rank), so that after the meeting point each owner only reads its
+      // own shared memory.
+      const uint32_t stage_addr = smem_u32(smem + p.stage_off);
+      const int ngroups = (nvalid + 15) / 16;
       const int acc_cols = p.merge ? 3 * p.bt : p.bt;
       for (int w = 0; w < p.nw; ++w) {
         for (int g = half; g < ngroups; g += 2) {
@@ -312,8 +324,30 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
           } else {
             tc_wait_ld();
           }
+          if (p.splits == 1) {
+            // Own tile, row = token: up to 16 stores at fixed 512-byte steps.
+            float* dst = reinterpret_cast<float*>(smem + p.stage_off) + (w * rpr + g * 16) * BN + row;
 #pragma unroll
-          for (int e = 0; e < 16; ++e) stage[(w * p.bt + g * 16 + e) * BN + row] = __uint_as_float(v[e]);
+            for (int e = 0; e < 16; ++e)
+              if (g * 16 + e < nvalid) dst[e * BN] = __uint_as_float(v[e]);
+          } else {
+            // Up to three owners per group of 16 tokens; an owner's window is linear, so one
+            // address translation per owner and 512-byte steps inside it.
+            const int t0 = g * 16;
+            int owner = t0 / rpr, rl = t0 - owner * rpr;
+            const uint32_t slot = stage_addr + (((split * p.nw + w) * rpr) * BN + row) * 4;
+            uint32_t base = dsmem_addr(slot, owner);
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              if (t0 + e < nvalid)
+                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(base + rl * (BN * 4)), "f"(__uint_as_float(v[e])));
+              if (++rl == rpr) {
+                rl = 0;
+                ++owner;
+                if (owner < p.splits) base = dsmem_addr(slot, owner);
+              }
+            }
+          }
         }
       }
     }
@@ -335,50 +369,29 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     // 4 consecutive channels per thread, 8 token rows per pass; with split-K, rank r owns token
     // rows [r*R, (r+1)*R) and sums them over all ranks in rank order.
     if (p.pdl) pdl_wait();  // outputs / residual may still be in use by the previous kernel
+    if (tr && tid == 64) tr[9] = clock64();
     const int et = tid - 64;
     const int v4 = et & 31;
     const int rgrp = et >> 5;
     const int n = n_tile * BN + v4 * 4;
     const bool n_ok = n < p.N;  // N % 4 == 0, so all four channels are valid together
-    const int rank = p.splits > 1 ? static_cast<int>(cluster_ctarank()) : 0;
-    const int rpr = (p.bt + p.splits - 1) / p.splits;
-    const int r0 = rank * rpr, r1 = min(p.bt, r0 + rpr);
-    const int m_base = t_tile * p.bt;
-    const float* stage = reinterpret_cast<const float*>(smem);
-    const uint32_t stage_addr = smem_u32(smem);
+    const float* stage = reinterpret_cast<const float*>(smem + p.stage_off);
     const long long plane = static_cast<long long>(p.M) * p.N;
-    // Rows are handled in batches of four (t, t+8, t+16, t+24): all staging loads of a batch are
-    // issued before any arithmetic, so their latencies overlap.
-    for (int tb = r0 + rgrp; tb < r1; tb += 32) {
-      float4 a0b[4], a1b[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int t = tb + 8 * u;
-        a0b[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-        a1b[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (t >= r1 || m_base + t >= p.M || !n_ok) continue;
-        if (p.splits == 1) {
-          a0b[u] = *reinterpret_cast<const float4*>(stage + t * BN + v4 * 4);
-          if (p.nw == 2) a1b[u] = *reinterpret_cast<const float4*>(stage + (p.bt + t) * BN + v4 * 4);
-        } else {
-          const uint32_t off0 = stage_addr + (t * BN + v4 * 4) * 4;
-          const uint32_t off1 = stage_addr + ((p.bt + t) * BN + v4 * 4) * 4;
-          for (int sp = 0; sp < p.splits; ++sp) {  // rank order: bit-reproducible
-            const float4 f = ld_dsmem_f4(dsmem_addr(off0, sp));
-            a0b[u].x += f.x; a0b[u].y += f.y; a0b[u].z += f.z; a0b[u].w += f.w;
-            if (p.nw == 2) {
-              const float4 g = ld_dsmem_f4(dsmem_addr(off1, sp));
-              a1b[u].x += g.x; a1b[u].y += g.y; a1b[u].z += g.z; a1b[u].w += g.w;
-            }
-          }
+    if (tr && tid == 64) tr[10] = clock64();
+#pragma unroll 1
+    for (int rl = rgrp; rl < own_rows && n_ok; rl += 8) {
+      const int m = m_base + rank * rpr + rl;
+      float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+      for (int sp = 0; sp < p.splits; ++sp) {  // split order: bit-reproducible
+        const float4 f = *reinterpret_cast<const float4*>(stage + ((sp * p.nw) * rpr + rl) * BN + v4 * 4);
+        a0.x += f.x; a0.y += f.y; a0.z += f.z; a0.w += f.w;
+        if (p.nw == 2) {
+          const float4 g = *reinterpret_cast<const float4*>(stage + ((sp * p.nw + 1) * rpr + rl) * BN + v4 * 4);
+          a1.x += g.x; a1.y += g.y; a1.z += g.z; a1.w += g.w;
         }
       }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-      const int t = tb + 8 * u;
-      const int m = m_base + t;
-      if (t >= r1 || !n_ok || m >= p.M) continue;
-      const float4 a0 = a0b[u], a1 = a1b[u];
+      {
       // Every rounding point is the one the reference's bf16 torch modules have: linear output,
       // GELU output, product, gated value, residual sum.
       float o[4] = {bf16_round(a0.x * s0[0] + b0[0]), bf16_round(a0.y * s0[1] + b0[1]),
@@ -408,8 +421,9 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
 #pragma unroll
           for (int e = 0; e < 4; ++e) o[e] = bf16_round(o[e] * gv[e]);
         }
-        const uint2 rr = (tb == r0 + rgrp) ? res_pf[u]
-                                           : *reinterpret_cast<const uint2*>(p.res + static_cast<long long>(m) * p.ldres + n);
+        const int u = (rl - rgrp) >> 3;
+        const uint2 rr = u < 4 ? res_pf[u < 4 ? u : 0]
+                               : *reinterpret_cast<const uint2*>(p.res + static_cast<long long>(m) * p.ldres + n);
         const __nv_bfloat162 r01 = *reinterpret_cast<const __nv_bfloat162*>(&rr.x);
         const __nv_bfloat162 r23 = *reinterpret_cast<const __nv_bfloat162*>(&rr.y);
         o[0] += __bfloat162float(r01.x); o[1] += __bfloat162float(r01.y);
@@ -439,11 +453,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
   }
 
   if (tr && tid == 64) tr[7] = clock64();
-  // Peers may still be reading this CTA's staging tile: leave together.
-  if (p.splits > 1) {
-    __syncwarp();
-    cluster_sync_all();
-  }
+  // After the meeting point nobody touches another CTA's shared memory: CTAs leave on their own.
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
@@ -481,7 +491,7 @@ __global__ void split3_kernel(const __nv_bfloat16* __restrict__ x, long long ldx
 
 // ------------------------------------------------------------------------------------ host
 struct Plan {
-  int bt, t_tiles, n_tiles, splits, kb_total, kb_per_split, nstages, smem_bytes, tmem_cols, merge;
+  int bt, t_tiles, n_tiles, splits, kb_total, kb_per_split, nstages, smem_bytes, tmem_cols, merge, stage_off;
 };
 
 static int round_up(int a, int b) { return (a + b - 1) / b * b; }
@@ -492,7 +502,9 @@ static bool make_plan(int M, int N, int K, int nw, int force_bt, int force_split
   if (force_bt > 0) {
     bt = force_bt;
   } else {
-    const int cap = 128;
+    // Token tiles of at most 80 keep 3*bt <= 256, so the three planes are one UMMA per K slice
+    // (measured on 544 x 2048 x 16384: 733 vs 447 TFLOP/s against 112-token tiles).
+    const int cap = 80;
     const int tiles = (M + cap - 1) / cap;
     bt = round_up((M + tiles - 1) / tiles, 16);
   }
@@ -509,13 +521,22 @@ static bool make_plan(int M, int N, int K, int nw, int force_bt, int force_split
     if (tiles * 2 <= sms) splits = std::min(sms / tiles, std::max(1, pl.kb_total / 2));  // >= 2 K blocks per split
   }
   splits = std::max(1, std::min(std::min(splits, MAX_SPLITS), pl.kb_total));
-  pl.kb_per_split = (pl.kb_total + splits - 1) / splits;
-  pl.splits = (pl.kb_total + pl.kb_per_split - 1) / pl.kb_per_split;  // no empty split
   const int stage_bytes = nw * W_TILE_BYTES + 3 * bt * 128;
-  pl.nstages = std::min(MAX_STAGES, (DYN_SMEM_MAX - 1024) / stage_bytes);  // 1 KB of alignment slack
-  pl.nstages = std::min(pl.nstages, std::max(2, pl.kb_per_split));
-  if (pl.nstages < 2) return false;
-  pl.smem_bytes = pl.nstages * stage_bytes + 1024;
+  for (;; --splits) {  // fewer splits if the split-K staging tile does not fit beside the ring
+    pl.kb_per_split = (pl.kb_total + splits - 1) / splits;
+    pl.splits = (pl.kb_total + pl.kb_per_split - 1) / pl.kb_per_split;  // no empty split
+    // Staging tile of the epilogue: [splits][nw][rows per rank][128] fp32.
+    const int rpr = (bt + pl.splits - 1) / pl.splits;
+    const int staging = round_up(pl.splits * nw * rpr * BN * 4, 1024);
+    const int extra = pl.splits > 1 ? staging : 0;
+    pl.nstages = std::min(MAX_STAGES, (DYN_SMEM_MAX - 1024 - extra) / stage_bytes);  // 1 KB of alignment slack
+    pl.nstages = std::min(pl.nstages, std::max(2, pl.kb_per_split));
+    while (pl.splits == 1 && pl.nstages * stage_bytes < staging) ++pl.nstages;  // the ring doubles as the tile
+    pl.stage_off = pl.splits > 1 ? pl.nstages * stage_bytes : 0;
+    pl.smem_bytes = pl.nstages * stage_bytes + extra + 1024;
+    if (pl.nstages >= 2 && pl.nstages <= MAX_STAGES && pl.smem_bytes <= DYN_SMEM_MAX) break;
+    if (splits == 1) return false;
+  }
   pl.merge = (3 * bt <= 256 && nw * 3 * bt <= 512) ? 1 : 0;
   pl.tmem_cols = 32;
   while (pl.tmem_cols < nw * bt * (pl.merge ? 3 : 1)) pl.tmem_cols *= 2;
@@ -564,7 +585,7 @@ static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, co
   GemmParams p{};
   p.M = M; p.N = N; p.K = K;
   p.bt = pl.bt; p.nw = nw; p.splits = pl.splits; p.kb_total = pl.kb_total; p.kb_per_split = pl.kb_per_split;
-  p.nstages = pl.nstages; p.tmem_cols = pl.tmem_cols; p.merge = pl.merge; p.epi = epi; p.pdl = host::pdl_enabled() ? 1 : 0;
+  p.nstages = pl.nstages; p.tmem_cols = pl.tmem_cols; p.merge = pl.merge; p.stage_off = pl.stage_off; p.epi = epi; p.pdl = host::pdl_enabled() ? 1 : 0;
   p.out_scale = ldexpf(1.0f, -x_shift);
   p.plane_scale = ldexpf(1.0f, out_shift);
   p.scale0 = s0; p.scale1 = s1; p.bias0 = static_cast<const __nv_bfloat16*>(bias);
