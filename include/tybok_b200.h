@@ -131,6 +131,13 @@ int tybok_rmsnorm(const void* x, int64_t ldx, const float* weight, const float* 
                   int rows_per_group, int M, int W, float eps, void* y, int64_t ldy, void* y_planes,
                   int out_shift, void* stream);
 
+/* LayerNorm (no affine, fp32 statistics) followed by the DiT modulation x * (1 + scale) + shift
+ * with bf16 shift/scale [W] broadcast over rows and every step rounded to bf16, as
+ * modulate(apply_norm2(x), shift, scale) of tybok/policies/fastwam/models/dit_block.py:67-69,
+ * 392-397 and wan_base.py:131-148.  Outputs as tybok_rmsnorm. */
+int tybok_layernorm_modulate(const void* x, int64_t ldx, const void* shift, const void* scale, int M, int W, float eps,
+                             void* y, int64_t ldy, void* y_planes, int out_shift, void* stream);
+
 /* RoPE + KV store.  qkv is the packed projection output [B*L, (H+2G)*D] (row stride ldq); q and
  * k are rotated (rotate-half form, bf16 cos/sin tables [max_pos, D], bf16 arithmetic with the
  * reference's rounding points) at positions pos[B*L]; q goes to q_out [B*L, H*D], k and v to the

@@ -69,6 +69,16 @@ def dit_ffn(x, up, down) -> torch.Tensor:
     return w8_linear(gelu_tanh(w8_linear(x, *up)), *down)
 
 
+def dit_ffn_tail(x, shift, scale, gate, up, down, eps: float = 1e-6) -> torch.Tensor:
+    """FFN tail of a DiT block: ``x + gate * ffn(modulate(LN(x), shift, scale))``
+    (tybok/policies/fastwam/models/dit_block.py:67-69,392-397; wan_base.py:131-148): LayerNorm
+    without affine in fp32 cast back to bf16, every modulation op in bf16.  ``up``/``down`` are
+    ``(w8, scale, bias)`` triples; ``shift``/``scale``/``gate`` broadcast over tokens."""
+    n = F.layer_norm(x.float(), (x.shape[-1],), None, None, eps).type_as(x)
+    h = n * (1 + scale) + shift
+    return x + gate * dit_ffn(h, up, down)
+
+
 def rms_norm(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
     """``x * rsqrt(mean(x^2) + eps)`` with fp32 statistics
     (tybok/policies/pi05/models/layers.py:51-53). The product promotes to fp32."""

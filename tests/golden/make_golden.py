@@ -56,6 +56,17 @@ def linear_case(seed, m, n, k):
     return w, x
 
 
+def dit_case(seed=4, m=70, h=256, f=512):
+    """Seeded inputs of the DiT FFN-tail fixture: x [1,m,h] bf16, (shift, scale, gate) [1,1,h] bf16,
+    and fp32 master weights/bf16 biases of the two FFN linears."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.empty(1, m, h).normal_(0, 1, generator=g).to(torch.bfloat16)
+    mods = tuple(torch.empty(1, 1, h).normal_(0, 0.5, generator=g).to(torch.bfloat16) for _ in range(3))
+    ws = [(torch.empty(f, h).normal_(0, 0.02, generator=g), torch.empty(f).normal_(0, 0.1, generator=g).to(torch.bfloat16)),
+          (torch.empty(h, f).normal_(0, 0.02, generator=g), torch.empty(h).normal_(0, 0.1, generator=g).to(torch.bfloat16))]
+    return x, mods, ws
+
+
 def main() -> None:
     from tybok.policies.fastwam.models.fp8_linear import FP8Linear
     from tybok.policies.fastwam.models.policy import _dequant_fp8_weight
@@ -92,6 +103,26 @@ def main() -> None:
         ws[name] = w
     with torch.no_grad():
         out["mlp"] = {"in_sum": checksum(x, *ws.values()), "y": mlp(x)}
+
+    # ---- a6: DiT FFN tail on dequantised weights ---------------------------------------
+    from tybok.policies.fastwam.models.dit_block import FastWAMAttentionBlock, modulate
+
+    x, mods, ws = dit_case()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        blk = FastWAMAttentionBlock(256, 128, 2, 512)
+    finally:
+        torch.set_default_dtype(torch.float32)
+    for idx, (w, b) in zip((0, 2), ws):
+        src = nn.Linear(w.shape[1], w.shape[0], bias=False)
+        src.weight.data.copy_(w)
+        q = FP8Linear.from_linear(src)
+        blk.ffn[idx].weight.data.copy_(_dequant_fp8_weight(q.weight.data, q.weight_scale.data))
+        blk.ffn[idx].bias.data.copy_(b)
+    shift, scale, gate = mods
+    with torch.no_grad():
+        y = x + gate * blk.ffn(modulate(blk.apply_norm2(x), shift, scale))
+    out["dit_ffn"] = {"in_sum": checksum(x, *mods, *[t for pair in ws for t in pair]), "y": y}
 
     # ---- whole tiny policy -------------------------------------------------------------
     shape = PI05_TINY

@@ -9,7 +9,7 @@ import torch
 
 sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
 
-from make_golden import checksum, linear_case, tiny_inputs  # noqa: E402
+from make_golden import checksum, dit_case, linear_case, tiny_inputs  # noqa: E402
 
 from oracle import pi05_ref, w8_ref  # noqa: E402
 from tybok_b200.shapes import PI05_TINY  # noqa: E402
@@ -54,6 +54,13 @@ def test_gated_mlp_matches_reference(golden):
     assert checksum(x, *ws) == golden["mlp"]["in_sum"]
     gate, up, down = (w8_ref.quantize_w8(w) for w in ws)
     assert torch.equal(w8_ref.gemma_mlp(x, gate, up, down), golden["mlp"]["y"])
+
+
+def test_dit_ffn_tail_matches_reference(golden):
+    x, mods, ws = dit_case()
+    assert checksum(x, *mods, *[t for pair in ws for t in pair]) == golden["dit_ffn"]["in_sum"]
+    up, down = ((*w8_ref.quantize_w8(w), b) for w, b in ws)
+    assert torch.equal(w8_ref.dit_ffn_tail(x, *mods, up, down), golden["dit_ffn"]["y"])
 
 
 def _tiny_params():

@@ -24,6 +24,8 @@ struct NormParams {
   long long ldx;
   const float* weight;  // [W] or NULL
   const float* mod;     // [groups, ldmod] or NULL; scale at [0,W), shift at [W,2W)
+  const __nv_bfloat16* ln_scale;  // [W] bf16: LayerNorm + modulate form when set
+  const __nv_bfloat16* ln_shift;  // [W] bf16
   long long ldmod;
   int rows_per_group;
   int M, W;
@@ -62,6 +64,29 @@ __global__ void __launch_bounds__(128) rmsnorm_kernel(const NormParams p) {
         }
       }
     }
+    float mean = 0.f;
+    if (p.ln_scale) {  // LayerNorm: centre first, then the variance of the centred values
+      float sm = 0.f;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i)
+        if (lane + 32 * i < nvec) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) sm += v[i][e];
+        }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sm += __shfl_xor_sync(0xffffffffu, sm, o);
+      mean = sm / static_cast<float>(p.W);
+      ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i)
+        if (lane + 32 * i < nvec) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            v[i][e] -= mean;
+            ss += v[i][e] * v[i][e];
+          }
+        }
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     const float rstd = rsqrtf(ss / static_cast<float>(p.W) + p.eps);
@@ -72,6 +97,20 @@ __global__ void __launch_bounds__(128) rmsnorm_kernel(const NormParams p) {
       const int c = lane + 32 * i;
       if (c < nvec) {
         float o[8];
+        if (p.ln_scale) {
+          // modulate(LN(x)) with every step rounded to bf16, as the reference's bf16 tensor ops
+          // do: n = bf16(LN), t = bf16(1 + scale), out = bf16(bf16(n * t) + shift).
+          const uint4 rs = *reinterpret_cast<const uint4*>(p.ln_scale + c * 8);
+          const uint4 rh = *reinterpret_cast<const uint4*>(p.ln_shift + c * 8);
+          const __nv_bfloat16* ps = reinterpret_cast<const __nv_bfloat16*>(&rs);
+          const __nv_bfloat16* ph = reinterpret_cast<const __nv_bfloat16*>(&rh);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float nrm = bf16_round(v[i][e] * rstd);
+            const float t = bf16_round(1.0f + __bfloat162float(ps[e]));
+            o[e] = bf16_round(nrm * t) + __bfloat162float(ph[e]);
+          }
+        } else {
         // x * rstd is formed in fp32 (the bf16 x promotes), as in the reference's _norm
         float sc[8], sh[8];
         {
@@ -88,6 +127,7 @@ __global__ void __launch_bounds__(128) rmsnorm_kernel(const NormParams p) {
           float t = v[i][e] * rstd * (1.0f + sc[e]);
           if (mod) t = v[i][e] * rstd * (1.0f + sc[e]) + sh[e];
           o[e] = t;
+        }
         }
         __nv_bfloat162 b[4];
 #pragma unroll
@@ -113,11 +153,11 @@ __global__ void __launch_bounds__(128) rmsnorm_kernel(const NormParams p) {
 
 }  // namespace tb
 
-extern "C" int tybok_rmsnorm(const void* x, int64_t ldx, const float* weight, const float* mod, int64_t ldmod,
-                             int rows_per_group, int M, int W, float eps, void* y, int64_t ldy, void* y_planes,
-                             int out_shift, void* stream) {
-  using namespace tb;
-  if (!x || (!y && !y_planes) || (!weight && !mod)) return host::fail(TYBOK_ERR_ARG, "rmsnorm: null pointer argument");
+namespace tb {
+static int launch_norm(const void* x, int64_t ldx, const float* weight, const float* mod, int64_t ldmod,
+                       int rows_per_group, const void* ln_scale, const void* ln_shift, int M, int W, float eps, void* y,
+                       int64_t ldy, void* y_planes, int out_shift, void* stream) {
+  if (!x || (!y && !y_planes) || (!weight && !mod && !ln_scale)) return host::fail(TYBOK_ERR_ARG, "rmsnorm: null pointer argument");
   if (M <= 0 || W <= 0 || W % 8 != 0 || W > NORM_MAX_VEC * 256)
     return host::fail(TYBOK_ERR_ARG, "rmsnorm: W must be a multiple of 8 and <= 4096");
   if (ldx % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (y && ((reinterpret_cast<uintptr_t>(y) & 15) || ldy % 8 != 0)) ||
@@ -129,6 +169,7 @@ extern "C" int tybok_rmsnorm(const void* x, int64_t ldx, const float* weight, co
   if (int rc = host::require_sm100()) return rc;
   NormParams p{};
   p.x = static_cast<const __nv_bfloat16*>(x); p.ldx = ldx; p.weight = weight; p.mod = mod; p.ldmod = ldmod;
+  p.ln_scale = static_cast<const __nv_bfloat16*>(ln_scale); p.ln_shift = static_cast<const __nv_bfloat16*>(ln_shift);
   p.rows_per_group = rows_per_group > 0 ? rows_per_group : 1; p.M = M; p.W = W; p.eps = eps;
   p.plane_scale = ldexpf(1.0f, out_shift); p.planes = static_cast<uint8_t*>(y_planes);
   p.y = static_cast<__nv_bfloat16*>(y); p.ldy = ldy; p.pdl = host::pdl_enabled() ? 1 : 0;
@@ -152,3 +193,22 @@ extern "C" int tybok_rmsnorm(const void* x, int64_t ldx, const float* weight, co
   host::count_launch();
   return TYBOK_OK;
 }
+}  // namespace tb
+
+extern "C" {
+
+int tybok_rmsnorm(const void* x, int64_t ldx, const float* weight, const float* mod, int64_t ldmod, int rows_per_group,
+                  int M, int W, float eps, void* y, int64_t ldy, void* y_planes, int out_shift, void* stream) {
+  return tb::launch_norm(x, ldx, weight, mod, ldmod, rows_per_group, nullptr, nullptr, M, W, eps, y, ldy, y_planes,
+                         out_shift, stream);
+}
+
+int tybok_layernorm_modulate(const void* x, int64_t ldx, const void* shift, const void* scale, int M, int W, float eps,
+                             void* y, int64_t ldy, void* y_planes, int out_shift, void* stream) {
+  if (!shift || !scale) return tb::host::fail(TYBOK_ERR_ARG, "layernorm_modulate: null shift/scale");
+  if ((reinterpret_cast<uintptr_t>(shift) | reinterpret_cast<uintptr_t>(scale)) & 15)
+    return tb::host::fail(TYBOK_ERR_ARG, "layernorm_modulate: shift/scale must be 16-byte aligned");
+  return tb::launch_norm(x, ldx, nullptr, nullptr, 0, 1, scale, shift, M, W, eps, y, ldy, y_planes, out_shift, stream);
+}
+
+}  // extern "C"

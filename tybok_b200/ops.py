@@ -39,6 +39,9 @@ _L.define("rope_store(Tensor qkv, Tensor pos, Tensor cos, Tensor sin, Tensor(a!)
 _L.define("attention(Tensor q, Tensor k_cache, Tensor v_cache, Tensor? key_valid, int tokens, int keys, float scale, "
           "bool out_bf16, bool out_planes, int out_shift) -> (Tensor, Tensor)")
 
+_L.define("layernorm_modulate(Tensor x, Tensor shift, Tensor scale, float eps, bool out_bf16, bool out_planes, "
+          "int out_shift) -> (Tensor, Tensor)")
+
 _status: dict[int, torch.Tensor] = {}
 
 
@@ -222,6 +225,24 @@ def _attention_cuda(q, k_cache, v_cache, key_valid, tokens, keys, scale, out_bf1
     return y, yp
 
 
+def _layernorm_modulate_cuda(x, shift, scale, eps, out_bf16, out_planes, out_shift):
+    lib = _lib.load()
+    if x.dtype != torch.bfloat16:
+        raise TypeError(f"layernorm_modulate: x must be bf16, got {x.dtype}")
+    x2 = _rows(x)
+    m, w = x2.shape
+    for t in (shift, scale):
+        if t.dtype != torch.bfloat16 or t.numel() != w or not t.is_contiguous():
+            raise TypeError("layernorm_modulate: shift/scale must be contiguous bf16 with W elements")
+    y, yp = _outputs(m, w, x.device, out_bf16, out_planes)
+    rc = lib.tybok_layernorm_modulate(x2.data_ptr(), x2.stride(0), shift.data_ptr(), scale.data_ptr(), m, w, float(eps),
+                                      y.data_ptr() if out_bf16 else None, w, yp.data_ptr() if out_planes else None,
+                                      int(out_shift), _stream(x))
+    _lib.check(rc, "tybok_layernorm_modulate")
+    return y, yp
+
+
+_L.impl("layernorm_modulate", _layernorm_modulate_cuda, "CUDA")
 _L.impl("rope_store", _rope_store_cuda, "CUDA")
 _L.impl("attention", _attention_cuda, "CUDA")
 _L.impl("rmsnorm", _rmsnorm_cuda, "CUDA")
@@ -284,6 +305,12 @@ def attention(q, k_cache, v_cache, key_valid=None, *, tokens, keys, scale, out_b
     ``tybok_attention``."""
     return torch.ops.tybok_b200.attention(q, k_cache, v_cache, key_valid, tokens, keys, scale, out_bf16, out_planes,
                                           out_shift)
+
+
+def layernorm_modulate(x, shift, scale, *, eps=1e-6, out_bf16=False, out_planes=True, out_shift=DEFAULT_SHIFT):
+    """``modulate(LayerNorm(x), shift, scale)`` of a DiT block; returns ``(y_bf16, y_planes)``; see
+    ``tybok_layernorm_modulate``."""
+    return torch.ops.tybok_b200.layernorm_modulate(x, shift, scale, eps, out_bf16, out_planes, out_shift)
 
 
 def launch_count() -> int:
