@@ -317,6 +317,68 @@ def run_ours(args, rank: int, world: int) -> None:
         dist.destroy_process_group()
 
 
+def run_dit_ffn(args, rank: int, world: int) -> None:
+    """Secondary workload (BASELINE config 3): the FFN tail of one fastWAM-class DiT block
+    (hidden 3072, ffn 14336, 4096+50 tokens), tensor-parallel over N GPUs with one NCCL
+    all-reduce per call (strong scaling: the work is fixed, the weights are sharded)."""
+    import torch.distributed as dist
+
+    from tybok_b200 import ops
+    from tybok_b200.dit import DiTFFN
+    from tybok_b200.shapes import DIT_FULL as S
+
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    peaks, peaks_kind = _peaks()
+    g = torch.Generator(device="cuda").manual_seed(0)  # same weights on every rank
+    rn = lambda *sh, std=1.0: torch.empty(*sh, device="cuda").normal_(0, std, generator=g)  # noqa: E731
+    nblk = 6  # rotating blocks: 6 x 88 MB of e4m3 weights > L2
+    blocks = [DiTFFN(rn(S.ffn, S.hidden, std=0.02), rn(S.ffn, std=0.1), rn(S.hidden, S.ffn, std=0.02),
+                     rn(S.hidden, std=0.1), device=f"cuda:{local}", rank=rank, world=world) for _ in range(nblk)]
+    x = rn(S.seq, S.hidden).to(torch.bfloat16)
+    shift, scale, gate = (rn(S.hidden, std=0.5).to(torch.bfloat16) for _ in range(3))
+    for i in range(max(3, args.warmup)):
+        blocks[i % nblk](x, shift, scale, gate)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        y = blocks[i % nblk](x, shift, scale, gate)
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    ops.check_status()
+    flops = 4.0 * S.seq * S.hidden * S.ffn
+    if rank == 0:
+        print(json.dumps({
+            "metric": "dit_ffn_tail_ms_per_block", "value": round(ms, 4), "unit": "ms", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": round(ms, 4), "higher_is_better": False,
+            "scaling": "strong", "vs_baseline": None, "dtype": "e4m3 weights x bf16 activations, fp32 accumulate",
+            "data": "synthetic", "config": {"workload": "dit_ffn: hidden 3072, ffn 14336, 4146 tokens, TP over N GPUs",
+                                            "l2": "6 rotating blocks (528 MB of weights) exceed L2"},
+            "clocks": clocks, "gpu_launches": 3 * args.steps,
+            "roofline": {"bound": "tensor", "achieved": round(flops / ms / 1e9, 1), "peak": peaks["bf16_tflops"] * world,
+                         "unit": "TFLOP/s", "frac": round(flops / ms / 1e9 / (peaks["bf16_tflops"] * world), 4),
+                         "traffic": None, "peak_source": peaks_kind},
+            "finite": bool(torch.isfinite(y.float()).all()),
+        }), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -325,6 +387,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="pi05_chunk", choices=["pi05_chunk", "dit_ffn"])
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -334,6 +397,9 @@ def main() -> None:
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device -- the product path has no CPU fallback (use --impl reference "
                          "for the CPU oracle timing)")
+    if args.workload == "dit_ffn":
+        run_dit_ffn(args, rank, world)
+        return
     run_ours(args, rank, world)
 
 
