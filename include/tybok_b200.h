@@ -138,6 +138,17 @@ int tybok_rmsnorm(const void* x, int64_t ldx, const float* weight, const float* 
 int tybok_layernorm_modulate(const void* x, int64_t ldx, const void* shift, const void* scale, int M, int W, float eps,
                              void* y, int64_t ldy, void* y_planes, int out_shift, void* stream);
 
+/* Per-step tail of the action-expert loop, one launch: final AdaRMS norm (scale/shift from
+ * mod[g, 0:2W]) -> fp32 out-projection [A=32, W] -> x_t += dt * v (fp32, in place) -> next
+ * step's suffix embedding h = bf16(W_in . x_t + b_in) with W_in fp32 [W, 32].  x == NULL skips
+ * everything but the embedding (first step); h == NULL skips the embedding (last step).
+ * Replaces expert.norm + action_out_proj + the Euler update + action_in_proj of
+ * tybok/policies/pi05/models/flow_matching.py:193-254,464-502,545-556 and its fused
+ * final-norm/out-projection kernel (flow_matching.py:41-150). */
+int tybok_action_tail(const void* x, int64_t ldx, const float* mod, int64_t ldmod, int rows_per_group, float eps,
+                      const float* w_out, const float* b_out, float* x_t, float dt, const float* w_in,
+                      const float* b_in, void* h, int M, int W, int A, void* stream);
+
 /* RoPE + KV store.  qkv is the packed projection output [B*L, (H+2G)*D] (row stride ldq); q and
  * k are rotated (rotate-half form, bf16 cos/sin tables [max_pos, D], bf16 arithmetic with the
  * reference's rounding points) at positions pos[B*L]; q goes to q_out [B*L, H*D], k and v to the

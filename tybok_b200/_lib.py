@@ -36,6 +36,8 @@ SIGNATURES = {
                               c_void_p, c_i64, c_void_p, c_int, c_void_p]),
     "tybok_layernorm_modulate": (c_int, [c_void_p, c_i64, c_void_p, c_void_p, c_int, c_int, ctypes.c_float, c_void_p,
                                          c_i64, c_void_p, c_int, c_void_p]),
+    "tybok_action_tail": (c_int, [c_void_p, c_i64, c_void_p, c_i64, c_int, ctypes.c_float, c_void_p, c_void_p, c_void_p,
+                                  ctypes.c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "tybok_rope_store": (c_int, [c_void_p, c_i64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                  c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "tybok_attention": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,

@@ -118,6 +118,7 @@ struct AttnParams {
   float plane_scale;
   int* status;
   int pdl;
+  long long* trace;  // tuning aid: [CTA][16] SM-clock samples, NULL in production
 };
 
 struct __align__(8) AttnBars {
@@ -158,6 +159,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                  const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ AttnBars bars;
+  const long long t_start = clock64();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sq = smem;
@@ -205,6 +207,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   tc_fence_after();
   const uint32_t tmem = bars.tmem_base;
   const uint32_t t_s = tmem, t_p = tmem + 128, t_o = tmem + 256;
+  long long* tr = p.trace ? p.trace + 16ll * ((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) : nullptr;
+  if (tr && tid == 0) { tr[0] = t_start; tr[1] = clock64(); }
 
   if (warp == 0) {
     if (lane == 0) {
@@ -257,6 +261,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int row = q * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     bool ok = __all_sync(0xffffffffu, at_wait(&bars.s_full, 0, &bars.abort));
+    if (tr && tid == 64) tr[2] = clock64();
     if (ok) {
       tc_fence_after();
       float mx = -1e30f;
@@ -295,8 +300,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       bars.row_sum[row] = sum;
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars.p_full);
+      if (tr && tid == 64) tr[3] = clock64();
       // -------------------------------------------------------- stage O (un-normalised) as [col][row] fp32
       ok = __all_sync(0xffffffffu, at_wait(&bars.o_full, 0, &bars.abort));
+      if (tr && tid == 64) tr[4] = clock64();
       if (ok) {
         tc_fence_after();
         // 128 KB staging tile over the (no longer needed) Q and K tiles: [row][64 float4], the
@@ -322,6 +329,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   }
 
   // ------------------------------------------------------------ meet: every key block staged
+  if (tr && tid == 64) tr[5] = clock64();
   tc_fence_before();
   if (p.nsplit > 1) {
     __syncwarp();
@@ -330,6 +338,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     __syncthreads();
   }
 
+  if (tr && tid == 64) tr[6] = clock64();
   if (warp >= 2 && !bars.abort) {
     // Merge: this CTA owns query rows [r0, r1) of the tile; thread = (4 output columns, row parity).
     const int et = tid - 64;
@@ -369,6 +378,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       for (int s = 0; s < AT_MAX_SPLITS; ++s) bars.wn[s][et] = w[s] * inv;
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps, unconditionally
+    if (tr && tid == 64) tr[7] = clock64();
 #pragma unroll 4
     for (int r = r0 + rsub; r < r1; r += 2) {
       const int t = qt * AT_BQ + r;
@@ -405,6 +415,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
   }
 
+  if (tr && tid == 64) tr[8] = clock64();
   if (p.nsplit > 1) {
     __syncwarp();
     cluster_sync_all();
@@ -485,6 +496,7 @@ int tybok_attention(const void* q, const void* k_cache, const void* v_cache, con
   p.plane_scale = ldexpf(1.0f, out_shift);
   p.status = status_word;
   p.pdl = host::pdl_enabled() ? 1 : 0;
+  p.trace = host::trace_buffer();
 
   static bool attr_set[64] = {};
   const int dev = host::current_device();

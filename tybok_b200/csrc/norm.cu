@@ -37,7 +37,9 @@ struct NormParams {
   int pdl;
 };
 
-template <int VEC>
+// VEC = 8-element vectors per lane; FULL = every lane owns exactly VEC vectors (W == 256 * VEC),
+// which removes the bounds predicates so that the loads can be hoisted and overlapped.
+template <int VEC, bool FULL>
 __global__ void __launch_bounds__(128) rmsnorm_kernel(const NormParams p) {
   // Let the next kernel in the stream start its preamble (weight prefetch) right away; it still
   // waits for this grid to finish before it reads what is written here.
@@ -53,7 +55,7 @@ __global__ void __launch_bounds__(128) rmsnorm_kernel(const NormParams p) {
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
       const int c = lane + 32 * i;
-      if (c < nvec) {
+      if (FULL || c < nvec) {
         const uint4 raw = *reinterpret_cast<const uint4*>(row + c * 8);
         const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
@@ -69,7 +71,7 @@ __global__ void __launch_bounds__(128) rmsnorm_kernel(const NormParams p) {
       float sm = 0.f;
 #pragma unroll
       for (int i = 0; i < VEC; ++i)
-        if (lane + 32 * i < nvec) {
+        if (FULL || lane + 32 * i < nvec) {
 #pragma unroll
           for (int e = 0; e < 8; ++e) sm += v[i][e];
         }
@@ -79,7 +81,7 @@ __global__ void __launch_bounds__(128) rmsnorm_kernel(const NormParams p) {
       ss = 0.f;
 #pragma unroll
       for (int i = 0; i < VEC; ++i)
-        if (lane + 32 * i < nvec) {
+        if (FULL || lane + 32 * i < nvec) {
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             v[i][e] -= mean;
@@ -95,7 +97,7 @@ __global__ void __launch_bounds__(128) rmsnorm_kernel(const NormParams p) {
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
       const int c = lane + 32 * i;
-      if (c < nvec) {
+      if (FULL || c < nvec) {
         float o[8];
         if (p.ln_scale) {
           // modulate(LN(x)) with every step rounded to bf16, as the reference's bf16 tensor ops
@@ -183,12 +185,17 @@ static int launch_norm(const void* x, int64_t ldx, const float* weight, const fl
   cfg.attrs = attr;
   cfg.numAttrs = p.pdl;
   const int per_lane = (W / 8 + 31) / 32;
+  const bool full = W % 256 == 0 && W / 256 == per_lane && (per_lane & (per_lane - 1)) == 0;
   cudaError_t e;
-  if (per_lane <= 1) e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<1>, p);
-  else if (per_lane <= 2) e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<2>, p);
-  else if (per_lane <= 4) e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<4>, p);
-  else if (per_lane <= 8) e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<8>, p);
-  else e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<NORM_MAX_VEC>, p);
+  if (full && per_lane == 4) e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<4, true>, p);
+  else if (full && per_lane == 8) e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<8, true>, p);
+  else if (full && per_lane == 1) e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<1, true>, p);
+  else if (full && per_lane == 2) e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<2, true>, p);
+  else if (per_lane <= 1) e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<1, false>, p);
+  else if (per_lane <= 2) e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<2, false>, p);
+  else if (per_lane <= 4) e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<4, false>, p);
+  else if (per_lane <= 8) e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<8, false>, p);
+  else e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<NORM_MAX_VEC, false>, p);
   if (e != cudaSuccess) return host::fail_cuda("launch rmsnorm_kernel");
   host::count_launch();
   return TYBOK_OK;

@@ -42,6 +42,9 @@ _L.define("attention(Tensor q, Tensor k_cache, Tensor v_cache, Tensor? key_valid
 _L.define("layernorm_modulate(Tensor x, Tensor shift, Tensor scale, float eps, bool out_bf16, bool out_planes, "
           "int out_shift) -> (Tensor, Tensor)")
 
+_L.define("action_tail(Tensor? x, Tensor? mod, int rows_per_group, float eps, Tensor? w_out, Tensor? b_out, "
+          "Tensor(a!) x_t, float dt, Tensor? w_in, Tensor? b_in, bool embed) -> Tensor")
+
 _status: dict[int, torch.Tensor] = {}
 
 
@@ -243,6 +246,32 @@ def _layernorm_modulate_cuda(x, shift, scale, eps, out_bf16, out_planes, out_shi
 
 
 _L.impl("layernorm_modulate", _layernorm_modulate_cuda, "CUDA")
+def _action_tail_cuda(x, mod, rows_per_group, eps, w_out, b_out, x_t, dt, w_in, b_in, embed):
+    lib = _lib.load()
+    if x_t.dtype != torch.float32 or not x_t.is_contiguous():
+        raise TypeError("action_tail: x_t must be contiguous fp32 [M, A]")
+    a = x_t.shape[-1]
+    m = x_t.numel() // a
+    for t in (mod, w_out, b_out, w_in, b_in):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+            raise TypeError("action_tail: modulation and projection tensors must be contiguous fp32")
+    if x is not None:
+        x = _rows(x)
+        if x.dtype != torch.bfloat16 or x.shape[0] != m:
+            raise TypeError("action_tail: x must be bf16 [M, W]")
+        w = x.shape[1]
+    else:
+        w = w_in.shape[0]
+    h = torch.empty((m, w) if embed else (0,), dtype=torch.bfloat16, device=x_t.device)
+    rc = lib.tybok_action_tail(_ptr(x), x.stride(0) if x is not None else 0, _ptr(mod),
+                               mod.shape[-1] if mod is not None else 0, int(rows_per_group), float(eps), _ptr(w_out),
+                               _ptr(b_out), x_t.data_ptr(), float(dt), _ptr(w_in) if embed else None,
+                               _ptr(b_in) if embed else None, h.data_ptr() if embed else None, m, w, a, _stream(x_t))
+    _lib.check(rc, "tybok_action_tail")
+    return h
+
+
+_L.impl("action_tail", _action_tail_cuda, "CUDA")
 _L.impl("rope_store", _rope_store_cuda, "CUDA")
 _L.impl("attention", _attention_cuda, "CUDA")
 _L.impl("rmsnorm", _rmsnorm_cuda, "CUDA")
@@ -311,6 +340,12 @@ def layernorm_modulate(x, shift, scale, *, eps=1e-6, out_bf16=False, out_planes=
     """``modulate(LayerNorm(x), shift, scale)`` of a DiT block; returns ``(y_bf16, y_planes)``; see
     ``tybok_layernorm_modulate``."""
     return torch.ops.tybok_b200.layernorm_modulate(x, shift, scale, eps, out_bf16, out_planes, out_shift)
+
+
+def action_tail(x, mod, w_out, b_out, x_t, dt, w_in, b_in, *, rows_per_group=1, eps=1e-6, embed=True):
+    """Final norm + fp32 out-projection + Euler update of ``x_t`` (in place) + next suffix
+    embedding (returned, bf16); ``x=None`` computes only the embedding; see ``tybok_action_tail``."""
+    return torch.ops.tybok_b200.action_tail(x, mod, rows_per_group, eps, w_out, b_out, x_t, dt, w_in, b_in, embed)
 
 
 def launch_count() -> int:

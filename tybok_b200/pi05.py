@@ -294,13 +294,39 @@ class PI05Model:
         y = y.view(b, l, spec.width)[:, -s.chunk :].float()
         return F.linear(y, *self.action_out)
 
+    def _expert_layers(self, step: int, h: torch.Tensor, b: int, l: int, pad: torch.Tensor, key_valid, pos, mask):
+        """All expert layers of one denoise step on the suffix embedding ``h [B*L, W]``."""
+        caches = self._caches(b)
+        lp = pad.shape[1]
+        x = h
+        for i, lay in enumerate(self.exp_layers):
+            x = self._layer(self.shape.expert, lay, x, b, l, pos, mask, caches[i], lp, key_valid, self.mods[step][i])
+        return x
+
     @torch.no_grad()
     def sample_actions(self, images, img_masks, tokens, masks, noise: torch.Tensor) -> torch.Tensor:
         """Prefix prefill + ``steps`` forward-Euler updates from ``noise`` (flow_matching.py:761-838)."""
+        s = self.shape
         embs, pad = self.embed_prefix(images, img_masks, tokens, masks)
-        kv = self.prefill(embs, pad)
-        dt = -1.0 / self.shape.steps
-        x_t = noise
-        for step in range(self.shape.steps):
-            x_t = x_t + dt * self.denoise_step(step, x_t, pad, kv)
+        self.prefill(embs, pad)
+        dt = -1.0 / s.steps
+        b, l = noise.shape[0], noise.shape[1]
+        if not (s.max_action_dim == 32 and l == s.chunk and s.expert.width in (128, 256, 512, 1024, 2048)):
+            x_t = noise
+            for step in range(s.steps):
+                x_t = x_t + dt * self.denoise_step(step, x_t, pad)
+            return x_t
+        # Fused tail: one launch per step does final norm + out-projection + Euler update + the
+        # next step's suffix embedding; masks and positions are built once per chunk.
+        lp = pad.shape[1]
+        allowed = torch.cat([pad, torch.ones(b, l, dtype=torch.bool, device=pad.device)], dim=1)
+        mask = None if self.fused_attention else _additive(allowed[:, None, None, :].expand(b, 1, l, lp + l))
+        key_valid = allowed.to(torch.uint8).contiguous()
+        pos = (pad.sum(dim=-1, keepdim=True) + torch.arange(l, device=pad.device)[None, :]).to(torch.int32).reshape(-1)
+        x_t = noise.float().contiguous().clone()
+        h = ops.action_tail(None, None, None, None, x_t, dt, *self.action_in)
+        for step in range(s.steps):
+            x = self._expert_layers(step, h, b, l, pad, key_valid, pos, mask)
+            h = ops.action_tail(x, self.final_mods[step], *self.action_out, x_t, dt, *self.action_in,
+                                rows_per_group=b * l, embed=step + 1 < s.steps)
         return x_t
