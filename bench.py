@@ -109,16 +109,17 @@ def _gemm_roofline(engine, peaks, peaks_kind) -> dict:
         rows = []
         for name, m, n, k, nw, count in lst:
             nbuf = min(48, max(4, int(400e6 // (nw * n * k)) + 1))
-            ws = [[torch.randint(0, 120, (n, k), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
-                   for _ in range(nw)] for _ in range(nbuf)]
-            sc = torch.rand(n, device=dev)
+            # the gated form streams gate and up as one interleaved [2N, K] matrix
+            ws = [[torch.randint(0, 120, (nw * n, k), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)]
+                  for _ in range(nbuf)]
+            sc = torch.rand(nw * n, device=dev)
             xp = ops.split3(torch.randn(m, k, device=dev).to(torch.bfloat16), 4)
             res = torch.randn(m, n, device=dev).to(torch.bfloat16)
 
             def call(i):
                 w = ws[i % nbuf]
                 if nw == 2:
-                    return ops.w8x3_geglu(xp, 4, w[0], sc, w[1], sc, out_bf16=False, out_planes=True)
+                    return ops.w8x3_geglu_packed(xp, 4, w[0], sc, out_bf16=False, out_planes=True)
                 if name == "qkv":
                     return ops.w8x3_linear(xp, 4, w[0], sc)
                 return ops.w8x3_linear(xp, 4, w[0], sc, epilogue=ops.EPI_RESIDUAL, residual=res)

@@ -169,6 +169,15 @@ int tybok_attention(const void* q, const void* k_cache, const void* v_cache, con
                     void* out_planes, int out_shift, int B, int L, int H, int G, int D, int Lk, int Lcap, float scale,
                     int* status_word, void* stream);
 
+/* tybok_w8x3_geglu on ONE packed weight matrix [2*I, K]: every block of 128 rows holds the 64
+ * gate rows of channels 64j..64j+63 followed by their 64 up rows (scale_packed [2*I] likewise),
+ * so a CTA streams a single weight tile per K block and its accumulator holds gate and up of
+ * the same channels (the role of the interleaved q/k rows in the reference's fused kernels,
+ * tybok/policies/pi05/models/triton_expert_fused_qkv_rope_attn.py:103-251).  I % 64 == 0. */
+int tybok_w8x3_geglu_packed(const void* x_planes, int x_shift, const void* w8_packed, const float* scale_packed, void* h,
+                            int64_t ldh, void* h_planes, int out_shift, int M, int I, int K, int token_tile, int splits,
+                            int* status_word, void* stream);
+
 /* Enable (1) / disable (0) programmatic dependent launch for every kernel of this library
  * (process-wide; default 1).  With it, a kernel's weight prefetch overlaps the tail of the
  * previous kernel in the stream. */

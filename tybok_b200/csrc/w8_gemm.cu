@@ -49,12 +49,16 @@ constexpr int MAX_STAGES = 8;
 constexpr int EPI_WARPS = 8;
 constexpr int THREADS = 32 * (2 + EPI_WARPS);
 constexpr int DYN_SMEM_MAX = 226 * 1024;  // 227 KB per CTA minus 1 KB left for static shared memory
+constexpr int CORESIDENT_SMEM = 112 * 1024;  // dynamic shared memory of a CTA when two share an SM (228 KB)
 constexpr int MAX_SPLITS = 8;             // portable cluster size
 
-enum : int { EPI_NONE = 0, EPI_GELU = 1, EPI_RESIDUAL = 2, EPI_GEGLU = 3 };
+// EPI_GEGLU_PACKED: one weight matrix whose 128-row tiles hold 64 gate rows followed by the 64
+// up rows of the same channels; the tile yields 64 output channels gelu(gate) * up.
+enum : int { EPI_NONE = 0, EPI_GELU = 1, EPI_RESIDUAL = 2, EPI_GEGLU = 3, EPI_GEGLU_PACKED = 4 };
 
 struct GemmParams {
   int M, N, K;
+  int n_out;     // width of the output rows: N, or N / 2 for EPI_GEGLU_PACKED
   int bt;        // token tile (UMMA N), multiple of 16, <= 256 (<= 128 when nw == 2)
   int nw;        // weight matrices per CTA: 1, or 2 for the gated form
   int splits;    // split-K factor == cluster size along z
@@ -270,12 +274,16 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     const int row = q * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     {
-      const int n = n_tile * BN + ((tid - 64) & 31) * 4;
-      if (n < p.N) {  // weights-side data: independent of the previous kernel in the stream
-        const float4 t = *reinterpret_cast<const float4*>(p.scale0 + n);
+      const bool packed = p.epi == EPI_GEGLU_PACKED;
+      const int v4p = (tid - 64) & 31;
+      const int col0 = packed ? (v4p & 15) * 4 : v4p * 4;
+      const int n = packed ? n_tile * (BN / 2) + col0 : n_tile * BN + col0;  // first output channel of this thread
+      if (n < p.n_out) {  // weights-side data: independent of the previous kernel in the stream
+        const float4 t = *reinterpret_cast<const float4*>(p.scale0 + n_tile * BN + col0);
         s0[0] = t.x * p.out_scale; s0[1] = t.y * p.out_scale; s0[2] = t.z * p.out_scale; s0[3] = t.w * p.out_scale;
-        if (p.nw == 2) {
-          const float4 u = *reinterpret_cast<const float4*>(p.scale1 + n);
+        if (p.nw == 2 || packed) {
+          const float4 u = packed ? *reinterpret_cast<const float4*>(p.scale0 + n_tile * BN + BN / 2 + col0)
+                                  : *reinterpret_cast<const float4*>(p.scale1 + n);
           s1[0] = u.x * p.out_scale; s1[1] = u.y * p.out_scale; s1[2] = u.z * p.out_scale; s1[3] = u.w * p.out_scale;
         }
         if (p.bias0) {
@@ -373,21 +381,29 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     const int et = tid - 64;
     const int v4 = et & 31;
     const int rgrp = et >> 5;
-    const int n = n_tile * BN + v4 * 4;
-    const bool n_ok = n < p.N;  // N % 4 == 0, so all four channels are valid together
+    // Packed gated form: 16 lanes cover the 64 output channels of a row, so a warp takes two
+    // rows per pass; otherwise 32 lanes cover the 128 channels of one row.
+    const bool packed = p.epi == EPI_GEGLU_PACKED;
+    const int col0 = packed ? (v4 & 15) * 4 : v4 * 4;
+    const int n = packed ? n_tile * (BN / 2) + col0 : n_tile * BN + col0;
+    const bool n_ok = n < p.n_out;  // n_out % 4 == 0, so all four channels are valid together
+    const int row0 = packed ? rgrp * 2 + (v4 >> 4) : rgrp;
+    const int rstep = packed ? 16 : 8;
     const float* stage = reinterpret_cast<const float*>(smem + p.stage_off);
-    const long long plane = static_cast<long long>(p.M) * p.N;
+    const long long plane = static_cast<long long>(p.M) * p.n_out;
     if (tr && tid == 64) tr[10] = clock64();
 #pragma unroll 1
-    for (int rl = rgrp; rl < own_rows && n_ok; rl += 8) {
+    for (int rl = row0; rl < own_rows && n_ok; rl += rstep) {
       const int m = m_base + rank * rpr + rl;
       float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 1
       for (int sp = 0; sp < p.splits; ++sp) {  // split order: bit-reproducible
-        const float4 f = *reinterpret_cast<const float4*>(stage + ((sp * p.nw) * rpr + rl) * BN + v4 * 4);
+        const float* r0p = stage + ((sp * p.nw) * rpr + rl) * BN;
+        const float4 f = *reinterpret_cast<const float4*>(r0p + col0);
         a0.x += f.x; a0.y += f.y; a0.z += f.z; a0.w += f.w;
-        if (p.nw == 2) {
-          const float4 g = *reinterpret_cast<const float4*>(stage + ((sp * p.nw + 1) * rpr + rl) * BN + v4 * 4);
+        if (p.nw == 2 || packed) {
+          const float4 g = packed ? *reinterpret_cast<const float4*>(r0p + BN / 2 + col0)
+                                  : *reinterpret_cast<const float4*>(stage + ((sp * p.nw + 1) * rpr + rl) * BN + col0);
           a1.x += g.x; a1.y += g.y; a1.z += g.z; a1.w += g.w;
         }
       }
@@ -399,7 +415,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
       if (p.epi == EPI_GELU) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[e] = gelu_tanh_fast(o[e]);
-      } else if (p.epi == EPI_GEGLU) {
+      } else if (p.epi == EPI_GEGLU || p.epi == EPI_GEGLU_PACKED) {
         const float u[4] = {bf16_round(a1.x * s1[0]), bf16_round(a1.y * s1[1]), bf16_round(a1.z * s1[2]),
                             bf16_round(a1.w * s1[3])};
 #pragma unroll
@@ -443,7 +459,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
                              __bfloat162float(o23.x) * p.plane_scale, __bfloat162float(o23.y) * p.plane_scale};
         uint32_t w1, w2, w3;
         split3_quad(xs, w1, w2, w3);
-        uint8_t* dst = p.y_planes + static_cast<long long>(m) * p.N + n;
+        uint8_t* dst = p.y_planes + static_cast<long long>(m) * p.n_out + n;
         *reinterpret_cast<uint32_t*>(dst) = w1;
         *reinterpret_cast<uint32_t*>(dst + plane) = w2;
         *reinterpret_cast<uint32_t*>(dst + 2 * plane) = w3;
@@ -504,9 +520,21 @@ static bool make_plan(int M, int N, int K, int nw, int force_bt, int force_split
   } else {
     // Token tiles of at most 80 keep 3*bt <= 256, so the three planes are one UMMA per K slice
     // (measured on 544 x 2048 x 16384: 733 vs 447 TFLOP/s against 112-token tiles).
-    const int cap = 80;
-    const int tiles = (M + cap - 1) / cap;
-    bt = round_up((M + tiles - 1) / tiles, 16);
+    // Between caps of 80 and 64 tokens take the one with the cheaper wave count: a wave costs
+    // about bt + 24 token-columns of MMA time (544 x 2048 x 16384: 112 tiles of 80 -> 54 us,
+    // 144 tiles of 64 -> 51 us; 544 x 2560 x 2048: 140 tiles of 80 -> 13.5 us, 180 of 64 -> 23 us).
+    const int sms = host::sm_count();
+    const int n_tiles = (N + BN - 1) / BN;
+    long long best_cost = 0;
+    bt = 0;
+    for (int cap : {80, 64}) {
+      if (cap == 64 && M <= 80) break;  // one tile already: do not stream the weights twice
+      const int tiles = (M + cap - 1) / cap;
+      const int cand = round_up((M + tiles - 1) / tiles, 16);
+      const long long waves = (static_cast<long long>((M + cand - 1) / cand) * n_tiles + sms - 1) / sms;
+      const long long cost = waves * (cand + 24);
+      if (bt == 0 || cost < best_cost) { bt = cand; best_cost = cost; }
+    }
   }
   if (bt % 16 != 0 || bt < 16 || bt > max_bt) return false;
   pl.bt = bt;
@@ -531,6 +559,12 @@ static bool make_plan(int M, int N, int K, int nw, int force_bt, int force_split
     const int extra = pl.splits > 1 ? staging : 0;
     pl.nstages = std::min(MAX_STAGES, (DYN_SMEM_MAX - 1024 - extra) / stage_bytes);  // 1 KB of alignment slack
     pl.nstages = std::min(pl.nstages, std::max(2, pl.kb_per_split));
+    // Several waves of full-K tiles: a shallower ring lets two CTAs share an SM, so one tile's
+    // epilogue runs under the other's main loop (measured on 544 x 32768 x 2048: 117 vs 156 us).
+    if (pl.splits == 1 && pl.t_tiles * pl.n_tiles >= 2 * host::sm_count() && nw * 3 * bt <= 256) {
+      const int shared = (CORESIDENT_SMEM - 1024) / stage_bytes;
+      if (shared >= 2) pl.nstages = std::min(pl.nstages, shared);
+    }
     while (pl.splits == 1 && pl.nstages * stage_bytes < staging) ++pl.nstages;  // the ring doubles as the tile
     pl.stage_off = pl.splits > 1 ? pl.nstages * stage_bytes : 0;
     pl.smem_bytes = pl.nstages * stage_bytes + extra + 1024;
@@ -553,10 +587,12 @@ static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, co
   if (M <= 0 || N <= 0 || K <= 0) return host::fail(TYBOK_ERR_ARG, "w8 gemm: M, N, K must be positive");
   if (K % 16 != 0) return host::fail(TYBOK_ERR_ARG, "w8 gemm: K must be a multiple of 16 (TMA row pitch)");
   if (N % 4 != 0) return host::fail(TYBOK_ERR_ARG, "w8 gemm: N must be a multiple of 4 (vector epilogue)");
+  if (epi == EPI_GEGLU_PACKED && (N % BN != 0 || w1)) return host::fail(TYBOK_ERR_ARG, "w8 gemm: packed gate/up needs 2*I % 128 == 0");
+  const int n_out = epi == EPI_GEGLU_PACKED ? N / 2 : N;
   if ((reinterpret_cast<uintptr_t>(planes) | reinterpret_cast<uintptr_t>(w0) | reinterpret_cast<uintptr_t>(w1) |
        reinterpret_cast<uintptr_t>(s0) | reinterpret_cast<uintptr_t>(s1)) & 15)
     return host::fail(TYBOK_ERR_ARG, "w8 gemm: planes, w8 and scale must be 16-byte aligned");
-  if (y && ((reinterpret_cast<uintptr_t>(y) & 7) || ldy % 4 != 0 || ldy < N))
+  if (y && ((reinterpret_cast<uintptr_t>(y) & 7) || ldy % 4 != 0 || ldy < n_out))
     return host::fail(TYBOK_ERR_ARG, "w8 gemm: y must be 8-byte aligned with ldy >= N, ldy % 4 == 0");
   if (y_planes && (reinterpret_cast<uintptr_t>(y_planes) & 3))
     return host::fail(TYBOK_ERR_ARG, "w8 gemm: output planes must be 4-byte aligned");
@@ -583,7 +619,7 @@ static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, co
     return rc;
 
   GemmParams p{};
-  p.M = M; p.N = N; p.K = K;
+  p.M = M; p.N = N; p.K = K; p.n_out = n_out;
   p.bt = pl.bt; p.nw = nw; p.splits = pl.splits; p.kb_total = pl.kb_total; p.kb_per_split = pl.kb_per_split;
   p.nstages = pl.nstages; p.tmem_cols = pl.tmem_cols; p.merge = pl.merge; p.stage_off = pl.stage_off; p.epi = epi; p.pdl = host::pdl_enabled() ? 1 : 0;
   p.out_scale = ldexpf(1.0f, -x_shift);
@@ -690,6 +726,14 @@ int tybok_w8x3_geglu(const void* x_planes, int x_shift, const void* w8_gate, con
   return tb::launch_gemm(static_cast<const uint8_t*>(x_planes), w8_gate, w8_up, scale_gate, scale_up, nullptr, h,
                          h_planes, M, I, K, ldh, tb::EPI_GEGLU, nullptr, 0, nullptr, 0, 1, 0, x_shift, out_shift,
                          token_tile, splits, status_word, static_cast<cudaStream_t>(stream));
+}
+
+int tybok_w8x3_geglu_packed(const void* x_planes, int x_shift, const void* w8_packed, const float* scale_packed, void* h,
+                            int64_t ldh, void* h_planes, int out_shift, int M, int I, int K, int token_tile, int splits,
+                            int* status_word, void* stream) {
+  return tb::launch_gemm(static_cast<const uint8_t*>(x_planes), w8_packed, nullptr, scale_packed, nullptr, nullptr, h,
+                         h_planes, M, 2 * I, K, ldh, tb::EPI_GEGLU_PACKED, nullptr, 0, nullptr, 0, 1, 0, x_shift,
+                         out_shift, token_tile, splits, status_word, static_cast<cudaStream_t>(stream));
 }
 
 int tybok_w8a16_linear(const void* x, const void* w8, const float* scale, const void* bias, void* y, int M, int N,

@@ -45,6 +45,9 @@ _L.define("layernorm_modulate(Tensor x, Tensor shift, Tensor scale, float eps, b
 _L.define("action_tail(Tensor? x, Tensor? mod, int rows_per_group, float eps, Tensor? w_out, Tensor? b_out, "
           "Tensor(a!) x_t, float dt, Tensor? w_in, Tensor? b_in, bool embed) -> Tensor")
 
+_L.define("w8x3_geglu_packed(Tensor planes, int shift, Tensor w8_packed, Tensor scale_packed, bool out_bf16, "
+          "bool out_planes, int out_shift, int token_tile, int splits) -> (Tensor, Tensor)")
+
 _status: dict[int, torch.Tensor] = {}
 
 
@@ -275,6 +278,25 @@ _L.impl("action_tail", _action_tail_cuda, "CUDA")
 _L.impl("rope_store", _rope_store_cuda, "CUDA")
 _L.impl("attention", _attention_cuda, "CUDA")
 _L.impl("rmsnorm", _rmsnorm_cuda, "CUDA")
+def _w8x3_geglu_packed_cuda(planes, shift, w8_packed, scale_packed, out_bf16, out_planes, out_shift, token_tile, splits):
+    lib = _lib.load()
+    _check_w8(w8_packed, "w8x3_geglu_packed")
+    if planes.dtype != torch.uint8 or planes.dim() != 3 or planes.shape[0] != 3 or not planes.is_contiguous():
+        raise TypeError("w8x3_geglu_packed: planes must be a contiguous uint8 [3, M, K] tensor")
+    n2, k = w8_packed.shape
+    if n2 % 128 != 0 or planes.shape[2] != k or scale_packed.numel() != n2:
+        raise ValueError("w8x3_geglu_packed: packed weight must be [2*I, K] with I % 64 == 0 and a [2*I] scale")
+    i, m = n2 // 2, planes.shape[1]
+    h, hp = _outputs(m, i, planes.device, out_bf16, out_planes)
+    rc = lib.tybok_w8x3_geglu_packed(planes.data_ptr(), int(shift), w8_packed.data_ptr(), scale_packed.data_ptr(),
+                                     h.data_ptr() if out_bf16 else None, i, hp.data_ptr() if out_planes else None,
+                                     int(out_shift), m, i, k, int(token_tile), int(splits),
+                                     status_word(planes.device).data_ptr(), _stream(planes))
+    _lib.check(rc, "tybok_w8x3_geglu_packed")
+    return h, hp
+
+
+_L.impl("w8x3_geglu_packed", _w8x3_geglu_packed_cuda, "CUDA")
 _L.impl("split3", _split3_cuda, "CUDA")
 _L.impl("w8x3_linear", _w8x3_linear_cuda, "CUDA")
 _L.impl("w8x3_geglu", _w8x3_geglu_cuda, "CUDA")
@@ -298,6 +320,26 @@ def w8x3_geglu(planes, shift, w8_gate, scale_gate, w8_up, scale_up, *, out_bf16=
     """``gelu_tanh(x@Wg.T) * (x@Wu.T)`` on activation planes; see ``tybok_w8x3_geglu``."""
     return torch.ops.tybok_b200.w8x3_geglu(planes, shift, w8_gate, scale_gate, w8_up, scale_up, out_bf16, out_planes,
                                            out_shift, token_tile, splits)
+
+
+def pack_gate_up(w8_gate, scale_gate, w8_up, scale_up):
+    """Interleave gate and up rows in blocks of 64 -> ``([2I, K] e4m3, [2I] fp32)`` for
+    ``w8x3_geglu_packed`` (rows 128j..128j+63 = gate channels 64j.., rows +64.. = their up rows)."""
+    i, k = w8_gate.shape
+    if i % 64 != 0:
+        raise ValueError("pack_gate_up: the FFN width must be a multiple of 64")
+    g = w8_gate.view(torch.uint8).view(i // 64, 64, k)
+    u = w8_up.view(torch.uint8).view(i // 64, 64, k)
+    w = torch.stack((g, u), dim=1).reshape(2 * i, k).contiguous().view(torch.float8_e4m3fn)
+    s = torch.stack((scale_gate.view(i // 64, 64), scale_up.view(i // 64, 64)), dim=1).reshape(2 * i).contiguous()
+    return w, s
+
+
+def w8x3_geglu_packed(planes, shift, w8_packed, scale_packed, *, out_bf16=True, out_planes=False,
+                      out_shift=DEFAULT_SHIFT, token_tile=0, splits=0):
+    """Gated FFN front half on a ``pack_gate_up`` weight; see ``tybok_w8x3_geglu_packed``."""
+    return torch.ops.tybok_b200.w8x3_geglu_packed(planes, shift, w8_packed, scale_packed, out_bf16, out_planes,
+                                                  out_shift, token_tile, splits)
 
 
 def w8a16_linear(x, w8, scale, bias=None, *, epilogue=EPI_NONE, residual=None, gate=None, rows_per_gate=1,

@@ -37,7 +37,7 @@ SHIFT_FFN = 4  # gelu(gate) * up
 class _Layer:
     """Packed weights of one Gemma decoder layer."""
 
-    __slots__ = ("qkv", "o", "gate", "up", "down", "norm_in", "norm_post")
+    __slots__ = ("qkv", "o", "gate", "up", "gate_up", "down", "norm_in", "norm_post")
 
 
 def _q(params: dict, name: str, device) -> tuple[torch.Tensor, torch.Tensor]:
@@ -59,8 +59,12 @@ def _pack_decoder(params: dict, root: str, spec: GemmaSpec, adarms: bool, device
         lay.qkv = (torch.cat([q[0].view(torch.uint8), k[0].view(torch.uint8), v[0].view(torch.uint8)]).contiguous(),
                    torch.cat([q[1], k[1], v[1]]).contiguous())
         lay.o = _q(params, f"{base}.self_attn.o_proj", device)
-        lay.gate = _q(params, f"{base}.mlp.gate_proj", device)
-        lay.up = _q(params, f"{base}.mlp.up_proj", device)
+        gate = _q(params, f"{base}.mlp.gate_proj", device)
+        up = _q(params, f"{base}.mlp.up_proj", device)
+        if gate[0].shape[0] % 64 == 0:  # one interleaved matrix: a single weight tile per K block
+            lay.gate_up, lay.gate, lay.up = ops.pack_gate_up(*gate, *up), None, None
+        else:
+            lay.gate_up, lay.gate, lay.up = None, gate, up
         lay.down = _q(params, f"{base}.mlp.down_proj", device)
         if adarms:
             lay.norm_in = (params[f"{base}.input_layernorm.dense.weight"].to(device).float(),
@@ -254,8 +258,12 @@ class PI05Model:
             _, xp = ops.rmsnorm(x, weight=lay.norm_post, out_shift=SHIFT_NORMED)
         else:
             _, xp = ops.rmsnorm(x, mod=mods[1], rows_per_group=m, out_shift=SHIFT_NORMED)
-        _, hp = ops.w8x3_geglu(xp, SHIFT_NORMED, *lay.gate, *lay.up, out_bf16=False, out_planes=True,
-                               out_shift=SHIFT_FFN)
+        if lay.gate_up is not None:
+            _, hp = ops.w8x3_geglu_packed(xp, SHIFT_NORMED, *lay.gate_up, out_bf16=False, out_planes=True,
+                                          out_shift=SHIFT_FFN)
+        else:
+            _, hp = ops.w8x3_geglu(xp, SHIFT_NORMED, *lay.gate, *lay.up, out_bf16=False, out_planes=True,
+                                   out_shift=SHIFT_FFN)
         x, _ = ops.w8x3_linear(hp, SHIFT_FFN, *lay.down, epilogue=ops.EPI_RESIDUAL, residual=x, gate=gate_post,
                                rows_per_gate=m)
         return x
