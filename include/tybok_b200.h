@@ -158,6 +158,17 @@ int tybok_rope_store(const void* qkv, int64_t ldq, const int* pos, const void* c
                      void* q_out, void* k_cache, void* v_cache, int B, int L, int H, int G, int D, int Lcap,
                      int key_off, void* stream);
 
+/* The packed q/k/v projection with tybok_rope_store as its epilogue: q_out and the caches are
+ * written straight from the accumulator, no [B*L, (H+2G)*D] intermediate.  w8_paired is the
+ * packed qkv weight [(H+2G)*D, K] with the rows of every head slot reordered so that each block
+ * of 128 rows holds dimensions 64t..64t+63 followed by their rotate-half partners D/2+64t..
+ * (scale_paired likewise); D % 128 == 0.  Same role as the interleaved q/k rows of the
+ * reference's fused qkv+RoPE kernel (tybok/policies/pi05/models/triton_expert_fused_qkv_rope_attn.py:103-251). */
+int tybok_w8x3_qkv_rope(const void* x_planes, int x_shift, const void* w8_paired, const float* scale_paired,
+                        const int* pos, const void* cos_table, const void* sin_table, void* q_out, void* k_cache,
+                        void* v_cache, int B, int L, int H, int G, int D, int Lcap, int key_off, int K, int token_tile,
+                        int splits, int* status_word, void* stream);
+
 /* GQA/MQA attention of L query tokens per batch element over the first Lk keys of the caches
  * (head_dim 256, Lk <= 1024): softmax(q k^T * scale + mask) v with fp32 softmax, bf16 P.
  *   q          [B*L, H*D] bf16 (already rotated);  k_cache / v_cache  [B, G, Lcap, D] bf16, finite

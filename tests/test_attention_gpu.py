@@ -71,3 +71,35 @@ def test_attention_matches_oracle(b, l, lp, h, g):
     # bit-reproducible
     out2, _ = ops.attention(q, kc, vc, key_valid.cuda(), tokens=l, keys=lk, scale=D**-0.5)
     assert torch.equal(out2.cpu().view(b, l, h * D), out)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("b,l,h,g,k,key_off", [(1, 50, 8, 1, 1024, 544), (2, 10, 2, 1, 128, 130), (1, 130, 2, 2, 256, 0)])
+def test_qkv_rope_epilogue_matches_projection_then_rope_store(b, l, h, g, k, key_off):
+    """The projection with RoPE + KV store as its epilogue writes bit-for-bit what the plain
+    projection followed by the rope_store kernel writes (same split count)."""
+    from tybok_b200 import ops
+
+    d = 256
+    dev = torch.device("cuda")
+    gen = torch.Generator().manual_seed(5)
+    w = torch.empty((h + 2 * g) * d, k).normal_(0, 0.02, generator=gen)
+    w8, sc = w8_ref.quantize_w8(w)
+    w8, sc = w8.to(dev), sc.to(dev)
+    x = torch.empty(b * l, k).normal_(0, 1, generator=gen).to(torch.bfloat16).to(dev)
+    pos = (torch.arange(l, dtype=torch.int32)[None] + torch.tensor([[3], [11]], dtype=torch.int32)[:b]).reshape(-1).to(dev)
+    cos, sin = w8_ref.rope_cos_sin(torch.arange(1024)[None], d, torch.bfloat16)
+    cos, sin = cos[0].contiguous().to(dev), sin[0].contiguous().to(dev)
+    lcap = key_off + l + 3
+    caches = [torch.zeros(b, g, lcap, d, dtype=torch.bfloat16, device=dev) for _ in range(4)]
+    xp = ops.split3(x, 4)
+    qkv, _ = ops.w8x3_linear(xp, 4, w8, sc, splits=1)
+    q0 = ops.rope_store(qkv, pos, cos, sin, caches[0], caches[1], heads=h, key_off=key_off)
+    wp, sp = ops.pair_qkv_rows(w8, sc, d)
+    q1 = ops.w8x3_qkv_rope(xp, 4, wp, sp, pos, cos, sin, caches[2], caches[3], heads=h, key_off=key_off, splits=1)
+    q2 = ops.w8x3_qkv_rope(xp, 4, wp, sp, pos, cos, sin, caches[2].clone(), caches[3].clone(), heads=h, key_off=key_off)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert torch.equal(q0, q1)
+    assert torch.equal(caches[0], caches[2]) and torch.equal(caches[1], caches[3])
+    assert w8_ref.rel_l2(q2.float().cpu(), q0.float().cpu()) < 2e-3  # other split count: fp32 summation order only

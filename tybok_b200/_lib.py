@@ -47,6 +47,11 @@ SIGNATURES = {
         [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_i64, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
          c_void_p, c_void_p],
     ),
+    "tybok_w8x3_qkv_rope": (
+        c_int,
+        [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    ),
     "tybok_w8a16_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "tybok_w8a16_linear": (
         c_int,

@@ -51,12 +51,6 @@ struct RopeParams {
   int B, L, H, G, D, Lcap, key_off, pdl;
 };
 
-// bf16 arithmetic with the rounding points of the reference's torch ops (rope.py:67-75):
-// out = bf16(bf16(x*cos) + bf16(rot*sin)).
-__device__ __forceinline__ float rope1(float x, float rot, float c, float s) {
-  return bf16_round(bf16_round(x * c) + bf16_round(rot * s));
-}
-
 __global__ void rope_store_kernel(const RopeParams p) {
   if (p.pdl) pdl_launch_dependents();  // the next kernel may start its preamble now
   if (p.pdl) pdl_wait();

@@ -312,4 +312,10 @@ __device__ __forceinline__ float gelu_tanh_f(float x) {
 }
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
+// Rotate-half RoPE element in bf16 arithmetic with the rounding points of the reference's torch
+// ops (rope.py:67-75): out = bf16(bf16(x*cos) + bf16(rot*sin)).
+__device__ __forceinline__ float rope1(float x, float rot, float c, float s) {
+  return bf16_round(bf16_round(x * c) + bf16_round(rot * s));
+}
+
 }  // namespace tb

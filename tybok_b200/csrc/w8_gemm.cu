@@ -54,7 +54,19 @@ constexpr int MAX_SPLITS = 8;             // portable cluster size
 
 // EPI_GEGLU_PACKED: one weight matrix whose 128-row tiles hold 64 gate rows followed by the 64
 // up rows of the same channels; the tile yields 64 output channels gelu(gate) * up.
-enum : int { EPI_NONE = 0, EPI_GELU = 1, EPI_RESIDUAL = 2, EPI_GEGLU = 3, EPI_GEGLU_PACKED = 4 };
+// EPI_QKV_ROPE: packed q/k/v projection whose 128-row tiles hold 64 head dimensions followed by
+// their rotate-half partners (d, d + D/2); the tile is rotated and stored as q rows / cache rows.
+enum : int { EPI_NONE = 0, EPI_GELU = 1, EPI_RESIDUAL = 2, EPI_GEGLU = 3, EPI_GEGLU_PACKED = 4, EPI_QKV_ROPE = 5 };
+
+struct RopeEpi {
+  const int* pos;              // [M] position of every token row
+  const __nv_bfloat16* cos;    // [max_pos][D]
+  const __nv_bfloat16* sin;
+  __nv_bfloat16* q;            // [M][H*D]
+  __nv_bfloat16* kcache;       // [B][G][Lcap][D]
+  __nv_bfloat16* vcache;
+  int L, H, G, D, Lcap, key_off;
+};
 
 struct GemmParams {
   int M, N, K;
@@ -87,6 +99,7 @@ struct GemmParams {
   int gate_bf16;
   int* status;
   long long* trace;  // tuning aid: [CTA][16] SM-clock samples, NULL in production
+  RopeEpi rope;      // EPI_QKV_ROPE only
 };
 
 struct __align__(8) Barriers {
@@ -274,10 +287,10 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     const int row = q * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     {
-      const bool packed = p.epi == EPI_GEGLU_PACKED;
+      const bool packed = p.epi == EPI_GEGLU_PACKED || p.epi == EPI_QKV_ROPE;  // paired half tiles
       const int v4p = (tid - 64) & 31;
       const int col0 = packed ? (v4p & 15) * 4 : v4p * 4;
-      const int n = packed ? n_tile * (BN / 2) + col0 : n_tile * BN + col0;  // first output channel of this thread
+      const int n = p.epi == EPI_GEGLU_PACKED ? n_tile * (BN / 2) + col0 : n_tile * BN + col0;  // first output channel
       if (n < p.n_out) {  // weights-side data: independent of the previous kernel in the stream
         const float4 t = *reinterpret_cast<const float4*>(p.scale0 + n_tile * BN + col0);
         s0[0] = t.x * p.out_scale; s0[1] = t.y * p.out_scale; s0[2] = t.z * p.out_scale; s0[3] = t.w * p.out_scale;
@@ -383,9 +396,9 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     const int rgrp = et >> 5;
     // Packed gated form: 16 lanes cover the 64 output channels of a row, so a warp takes two
     // rows per pass; otherwise 32 lanes cover the 128 channels of one row.
-    const bool packed = p.epi == EPI_GEGLU_PACKED;
+    const bool packed = p.epi == EPI_GEGLU_PACKED || p.epi == EPI_QKV_ROPE;
     const int col0 = packed ? (v4 & 15) * 4 : v4 * 4;
-    const int n = packed ? n_tile * (BN / 2) + col0 : n_tile * BN + col0;
+    const int n = p.epi == EPI_GEGLU_PACKED ? n_tile * (BN / 2) + col0 : n_tile * BN + col0;
     const bool n_ok = n < p.n_out;  // n_out % 4 == 0, so all four channels are valid together
     const int row0 = packed ? rgrp * 2 + (v4 >> 4) : rgrp;
     const int rstep = packed ? 16 : 8;
@@ -420,6 +433,48 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
                             bf16_round(a1.w * s1[3])};
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[e] = bf16_round(gelu_tanh_fast(o[e])) * u[e];
+      } else if (p.epi == EPI_QKV_ROPE) {
+        // o = dimensions d..d+3 of one head slot, u = their partners d + D/2; rotate q and k
+        // slots (bf16 rounding points of rope.py:67-75), pass v through, store both halves.
+        const RopeEpi& r = p.rope;
+        float u[4] = {bf16_round(a1.x * s1[0]), bf16_round(a1.y * s1[1]), bf16_round(a1.z * s1[2]),
+                      bf16_round(a1.w * s1[3])};
+        const int tps = r.D >> 7;  // 128-row tiles per head slot
+        const int slot = n_tile / tps;
+        const int d = (n_tile - slot * tps) * 64 + col0;
+        const int half = r.D >> 1;
+        if (slot < r.H + r.G) {
+          const long long tb = static_cast<long long>(r.pos[m]) * r.D + d;
+          const uint2 c0 = *reinterpret_cast<const uint2*>(r.cos + tb), c1 = *reinterpret_cast<const uint2*>(r.cos + tb + half);
+          const uint2 n0 = *reinterpret_cast<const uint2*>(r.sin + tb), n1 = *reinterpret_cast<const uint2*>(r.sin + tb + half);
+          const __nv_bfloat16* pc0 = reinterpret_cast<const __nv_bfloat16*>(&c0);
+          const __nv_bfloat16* pc1 = reinterpret_cast<const __nv_bfloat16*>(&c1);
+          const __nv_bfloat16* pn0 = reinterpret_cast<const __nv_bfloat16*>(&n0);
+          const __nv_bfloat16* pn1 = reinterpret_cast<const __nv_bfloat16*>(&n1);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float lo = o[e], hi = u[e];  // rotate_half(x) = (-x2, x1)
+            o[e] = rope1(lo, -hi, __bfloat162float(pc0[e]), __bfloat162float(pn0[e]));
+            u[e] = rope1(hi, lo, __bfloat162float(pc1[e]), __bfloat162float(pn1[e]));
+          }
+        }
+        __nv_bfloat16* dst;
+        if (slot < r.H) {
+          dst = r.q + (static_cast<long long>(m) * r.H + slot) * r.D;
+        } else {
+          const int g = (slot - r.H) % r.G;
+          const int b = m / r.L, t = m - b * r.L;
+          dst = (slot < r.H + r.G ? r.kcache : r.vcache) +
+                ((static_cast<long long>(b) * r.G + g) * r.Lcap + r.key_off + t) * r.D;
+        }
+        const __nv_bfloat162 l01 = __floats2bfloat162_rn(o[0], o[1]), l23 = __floats2bfloat162_rn(o[2], o[3]);
+        const __nv_bfloat162 h01 = __floats2bfloat162_rn(u[0], u[1]), h23 = __floats2bfloat162_rn(u[2], u[3]);
+        uint2 st;
+        st.x = *reinterpret_cast<const uint32_t*>(&l01); st.y = *reinterpret_cast<const uint32_t*>(&l23);
+        *reinterpret_cast<uint2*>(dst + d) = st;
+        st.x = *reinterpret_cast<const uint32_t*>(&h01); st.y = *reinterpret_cast<const uint32_t*>(&h23);
+        *reinterpret_cast<uint2*>(dst + half + d) = st;
+        continue;
       } else if (p.epi == EPI_RESIDUAL) {
         if (p.gate) {
           const long long gi = static_cast<long long>(m / p.rows_per_gate) * p.ldgate + n;
@@ -581,9 +636,9 @@ static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, co
                        const void* bias, void* y, void* y_planes, int M, int N, int K, long long ldy, int epi,
                        const void* res, long long ldres, const void* gate, long long ldgate, int rows_per_gate,
                        int gate_bf16, int x_shift, int out_shift, int force_bt, int force_splits, int* status,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, const RopeEpi* rope = nullptr) {
   const int nw = w1 ? 2 : 1;
-  if (!planes || !w0 || !s0 || (!y && !y_planes)) return host::fail(TYBOK_ERR_ARG, "w8 gemm: null pointer argument");
+  if (!planes || !w0 || !s0 || (!y && !y_planes && !rope)) return host::fail(TYBOK_ERR_ARG, "w8 gemm: null pointer argument");
   if (M <= 0 || N <= 0 || K <= 0) return host::fail(TYBOK_ERR_ARG, "w8 gemm: M, N, K must be positive");
   if (K % 16 != 0) return host::fail(TYBOK_ERR_ARG, "w8 gemm: K must be a multiple of 16 (TMA row pitch)");
   if (N % 4 != 0) return host::fail(TYBOK_ERR_ARG, "w8 gemm: N must be a multiple of 4 (vector epilogue)");
@@ -630,6 +685,7 @@ static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, co
   p.gate = gate; p.ldgate = ldgate; p.rows_per_gate = rows_per_gate > 0 ? rows_per_gate : 1; p.gate_bf16 = gate_bf16;
   p.status = status;
   p.trace = host::trace_buffer();
+  if (rope) p.rope = *rope;
 
   static bool attr_set[64] = {};
   const int dev = host::current_device();
@@ -734,6 +790,27 @@ int tybok_w8x3_geglu_packed(const void* x_planes, int x_shift, const void* w8_pa
   return tb::launch_gemm(static_cast<const uint8_t*>(x_planes), w8_packed, nullptr, scale_packed, nullptr, nullptr, h,
                          h_planes, M, 2 * I, K, ldh, tb::EPI_GEGLU_PACKED, nullptr, 0, nullptr, 0, 1, 0, x_shift,
                          out_shift, token_tile, splits, status_word, static_cast<cudaStream_t>(stream));
+}
+
+int tybok_w8x3_qkv_rope(const void* x_planes, int x_shift, const void* w8_paired, const float* scale_paired,
+                        const int* pos, const void* cos_table, const void* sin_table, void* q_out, void* k_cache,
+                        void* v_cache, int B, int L, int H, int G, int D, int Lcap, int key_off, int K, int token_tile,
+                        int splits, int* status_word, void* stream) {
+  if (!pos || !cos_table || !sin_table || !q_out || !k_cache || !v_cache)
+    return tb::host::fail(TYBOK_ERR_ARG, "qkv_rope: null pointer argument");
+  if (B <= 0 || L <= 0 || H <= 0 || G <= 0 || D <= 0 || D % 128 != 0 || key_off < 0 || key_off + L > Lcap)
+    return tb::host::fail(TYBOK_ERR_ARG, "qkv_rope: needs head_dim % 128 == 0 and key_off + L <= Lcap");
+  if ((reinterpret_cast<uintptr_t>(cos_table) | reinterpret_cast<uintptr_t>(sin_table) |
+       reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 7)
+    return tb::host::fail(TYBOK_ERR_ARG, "qkv_rope: tables, q and caches must be 8-byte aligned");
+  tb::RopeEpi r{};
+  r.pos = pos; r.cos = static_cast<const __nv_bfloat16*>(cos_table); r.sin = static_cast<const __nv_bfloat16*>(sin_table);
+  r.q = static_cast<__nv_bfloat16*>(q_out); r.kcache = static_cast<__nv_bfloat16*>(k_cache);
+  r.vcache = static_cast<__nv_bfloat16*>(v_cache);
+  r.L = L; r.H = H; r.G = G; r.D = D; r.Lcap = Lcap; r.key_off = key_off;
+  return tb::launch_gemm(static_cast<const uint8_t*>(x_planes), w8_paired, nullptr, scale_paired, nullptr, nullptr,
+                         nullptr, nullptr, B * L, (H + 2 * G) * D, K, 0, tb::EPI_QKV_ROPE, nullptr, 0, nullptr, 0, 1, 0,
+                         x_shift, 0, token_tile, splits, status_word, static_cast<cudaStream_t>(stream), &r);
 }
 
 int tybok_w8a16_linear(const void* x, const void* w8, const float* scale, const void* bias, void* y, int M, int N,

@@ -48,6 +48,10 @@ _L.define("action_tail(Tensor? x, Tensor? mod, int rows_per_group, float eps, Te
 _L.define("w8x3_geglu_packed(Tensor planes, int shift, Tensor w8_packed, Tensor scale_packed, bool out_bf16, "
           "bool out_planes, int out_shift, int token_tile, int splits) -> (Tensor, Tensor)")
 
+_L.define("w8x3_qkv_rope(Tensor planes, int shift, Tensor w8_paired, Tensor scale_paired, Tensor pos, Tensor cos, "
+          "Tensor sin, Tensor(a!) k_cache, Tensor(b!) v_cache, int heads, int key_off, int token_tile, int splits) "
+          "-> Tensor")
+
 _status: dict[int, torch.Tensor] = {}
 
 
@@ -275,6 +279,33 @@ def _action_tail_cuda(x, mod, rows_per_group, eps, w_out, b_out, x_t, dt, w_in, 
 
 
 _L.impl("action_tail", _action_tail_cuda, "CUDA")
+def _w8x3_qkv_rope_cuda(planes, shift, w8_paired, scale_paired, pos, cos, sin, k_cache, v_cache, heads, key_off,
+                        token_tile, splits):
+    lib = _lib.load()
+    _check_w8(w8_paired, "w8x3_qkv_rope")
+    b, g, lcap, d = k_cache.shape
+    if planes.dtype != torch.uint8 or planes.dim() != 3 or planes.shape[0] != 3 or not planes.is_contiguous():
+        raise TypeError("w8x3_qkv_rope: planes must be a contiguous uint8 [3, M, K] tensor")
+    m, k = planes.shape[1], planes.shape[2]
+    if w8_paired.shape != ((heads + 2 * g) * d, k) or scale_paired.numel() != w8_paired.shape[0] or d % 128 != 0:
+        raise ValueError("w8x3_qkv_rope: weight must be [(H+2G)*D, K] with head_dim % 128 == 0")
+    if pos.dtype != torch.int32 or pos.numel() != m or not pos.is_contiguous() or m % b != 0:
+        raise TypeError("w8x3_qkv_rope: pos must be contiguous int32 [B*L]")
+    for t in (k_cache, v_cache, cos, sin):
+        if t.dtype != torch.bfloat16 or not t.is_contiguous():
+            raise TypeError("w8x3_qkv_rope: caches and cos/sin tables must be contiguous bf16")
+    if v_cache.shape != k_cache.shape or cos.shape[-1] != d or sin.shape != cos.shape:
+        raise ValueError("w8x3_qkv_rope: cache / table shapes disagree")
+    q = torch.empty((m, heads * d), dtype=torch.bfloat16, device=planes.device)
+    rc = lib.tybok_w8x3_qkv_rope(planes.data_ptr(), int(shift), w8_paired.data_ptr(), scale_paired.data_ptr(),
+                                 pos.data_ptr(), cos.data_ptr(), sin.data_ptr(), q.data_ptr(), k_cache.data_ptr(),
+                                 v_cache.data_ptr(), b, m // b, heads, g, d, lcap, int(key_off), k, int(token_tile),
+                                 int(splits), status_word(planes.device).data_ptr(), _stream(planes))
+    _lib.check(rc, "tybok_w8x3_qkv_rope")
+    return q
+
+
+_L.impl("w8x3_qkv_rope", _w8x3_qkv_rope_cuda, "CUDA")
 _L.impl("rope_store", _rope_store_cuda, "CUDA")
 _L.impl("attention", _attention_cuda, "CUDA")
 _L.impl("rmsnorm", _rmsnorm_cuda, "CUDA")
@@ -333,6 +364,28 @@ def pack_gate_up(w8_gate, scale_gate, w8_up, scale_up):
     w = torch.stack((g, u), dim=1).reshape(2 * i, k).contiguous().view(torch.float8_e4m3fn)
     s = torch.stack((scale_gate.view(i // 64, 64), scale_up.view(i // 64, 64)), dim=1).reshape(2 * i).contiguous()
     return w, s
+
+
+def pair_qkv_rows(w8_qkv, scale_qkv, head_dim):
+    """Reorder the rows of a packed q/k/v weight for ``w8x3_qkv_rope``: inside every head slot,
+    blocks of 64 dimensions alternate with the block of their rotate-half partners."""
+    n, k = w8_qkv.shape
+    if head_dim % 128 != 0 or n % head_dim != 0:
+        raise ValueError("pair_qkv_rows: head_dim must be a multiple of 128")
+    half = head_dim // 2
+    d = torch.arange(half, device=w8_qkv.device).view(half // 64, 1, 64)
+    within = torch.cat((d, d + half), dim=1).reshape(-1)  # [D]: 64 dims, 64 partners, next 64 dims, ...
+    idx = (torch.arange(n // head_dim, device=w8_qkv.device)[:, None] * head_dim + within[None]).reshape(-1)
+    w = w8_qkv.view(torch.uint8)[idx].contiguous().view(torch.float8_e4m3fn)
+    return w, scale_qkv[idx].contiguous()
+
+
+def w8x3_qkv_rope(planes, shift, w8_paired, scale_paired, pos, cos, sin, k_cache, v_cache, *, heads, key_off,
+                  token_tile=0, splits=0):
+    """q/k/v projection + RoPE + KV store in one kernel; returns rotated q ``[B*L, H*D]``; see
+    ``tybok_w8x3_qkv_rope``."""
+    return torch.ops.tybok_b200.w8x3_qkv_rope(planes, shift, w8_paired, scale_paired, pos, cos, sin, k_cache, v_cache,
+                                              heads, key_off, token_tile, splits)
 
 
 def w8x3_geglu_packed(planes, shift, w8_packed, scale_packed, *, out_bf16=True, out_planes=False,

@@ -37,7 +37,7 @@ SHIFT_FFN = 4  # gelu(gate) * up
 class _Layer:
     """Packed weights of one Gemma decoder layer."""
 
-    __slots__ = ("qkv", "o", "gate", "up", "gate_up", "down", "norm_in", "norm_post")
+    __slots__ = ("qkv", "qkv_paired", "o", "gate", "up", "gate_up", "down", "norm_in", "norm_post")
 
 
 def _q(params: dict, name: str, device) -> tuple[torch.Tensor, torch.Tensor]:
@@ -50,7 +50,7 @@ def _q(params: dict, name: str, device) -> tuple[torch.Tensor, torch.Tensor]:
     return w8, s
 
 
-def _pack_decoder(params: dict, root: str, spec: GemmaSpec, adarms: bool, device) -> list[_Layer]:
+def _pack_decoder(params: dict, root: str, spec: GemmaSpec, adarms: bool, device, pair_rope: bool) -> list[_Layer]:
     layers = []
     for i in range(spec.depth):
         base = f"{root}.layers.{i}"
@@ -58,6 +58,11 @@ def _pack_decoder(params: dict, root: str, spec: GemmaSpec, adarms: bool, device
         q, k, v = (_q(params, f"{base}.self_attn.{n}_proj", device) for n in ("q", "k", "v"))
         lay.qkv = (torch.cat([q[0].view(torch.uint8), k[0].view(torch.uint8), v[0].view(torch.uint8)]).contiguous(),
                    torch.cat([q[1], k[1], v[1]]).contiguous())
+        # head sizes the attention kernel takes: RoPE runs in the projection's epilogue on paired rows
+        lay.qkv_paired = None
+        if pair_rope:
+            lay.qkv_paired = ops.pair_qkv_rows(lay.qkv[0].view(torch.float8_e4m3fn), lay.qkv[1], spec.head_dim)
+            lay.qkv = None
         lay.o = _q(params, f"{base}.self_attn.o_proj", device)
         gate = _q(params, f"{base}.mlp.gate_proj", device)
         up = _q(params, f"{base}.mlp.up_proj", device)
@@ -116,8 +121,9 @@ class PI05Model:
         self.proj_b = params[f"{PROJECTOR}.bias"].to(dev, vision_dtype)
         self.embed = params[f"{VLM}.embed_tokens.weight"].to(dev)
         self.embed_scale = torch.tensor(shape.vlm.width**0.5, dtype=self.embed.dtype, device=dev)
-        self.vlm_layers = _pack_decoder(params, VLM, shape.vlm, False, dev)
-        self.exp_layers = _pack_decoder(params, EXPERT, shape.expert, True, dev)
+        self.fused_attention = shape.vlm.head_dim == 256 and shape.expert.head_dim == 256
+        self.vlm_layers = _pack_decoder(params, VLM, shape.vlm, False, dev, self.fused_attention)
+        self.exp_layers = _pack_decoder(params, EXPERT, shape.expert, True, dev, self.fused_attention)
         self.final_norm = (params[f"{EXPERT}.norm.dense.weight"].to(dev).float(),
                            params[f"{EXPERT}.norm.dense.bias"].to(dev).float())
         f32 = lambda n: params[n].to(dev).float()  # noqa: E731
@@ -241,12 +247,13 @@ class PI05Model:
         else:
             _, xp = ops.rmsnorm(x, mod=mods[0], rows_per_group=m, out_shift=SHIFT_NORMED)
             gate_in, gate_post = mods[0][:, 2 * w :], mods[1][:, 2 * w :]
-        qkv, _ = ops.w8x3_linear(xp, SHIFT_NORMED, *lay.qkv)
         if self.fused_attention:
-            q = ops.rope_store(qkv, pos, self.cos, self.sin, cache[0], cache[1], heads=spec.num_heads, key_off=key_off)
+            q = ops.w8x3_qkv_rope(xp, SHIFT_NORMED, *lay.qkv_paired, pos, self.cos, self.sin, cache[0], cache[1],
+                                  heads=spec.num_heads, key_off=key_off)
             _, ap = ops.attention(q, cache[0], cache[1], key_valid, tokens=l, keys=key_off + l,
                                   scale=spec.head_dim**-0.5, out_bf16=False, out_planes=True, out_shift=SHIFT_ATTN)
         else:
+            qkv, _ = ops.w8x3_linear(xp, SHIFT_NORMED, *lay.qkv)
             prefix_kv = (cache[0][:, :, :key_off], cache[1][:, :, :key_off]) if key_off else None
             a, k, v = self._attention(spec, qkv, b, l, pos.view(b, l).long(), mask, prefix_kv)
             cache[0][:, :, key_off : key_off + l] = k
