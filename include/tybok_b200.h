@@ -48,7 +48,7 @@ long long tybok_launch_count(void);
 /* ---- activation planes -------------------------------------------------------------------
  * The GEMMs consume activations as three e5m2 byte planes [3][M][K] whose sum is
  * x * 2^x_shift; for bf16 x the sum is exact whenever |x * 2^x_shift| lies in [2^-7, 57344]
- * (below: absolute error <= 2^-17; above: the terms saturate).  Kernels of this library that
+ * (below: absolute error <= 2^-17 + 2^-25; above: the terms saturate).  Kernels of this library that
  * produce activations can write the planes directly; tybok_split3 converts a bf16 tensor. */
 #define TYBOK_DEFAULT_X_SHIFT 4
 int tybok_split3(const void* x, int64_t ldx, void* planes, int M, int K, int x_shift, void* stream);

@@ -137,7 +137,7 @@ def test_split3_planes_are_exact():
     want = x.float() * 16.0
     inside = want.abs() >= 2.0**-7
     assert torch.equal(total[inside], want[inside])
-    assert float((total - want).abs().max()) <= 2.0**-17
+    assert float((total - want).abs().max()) <= 2.0**-17 + 2.0**-24
 
 
 def test_planes_in_planes_out_chain():
@@ -158,7 +158,7 @@ def test_planes_in_planes_out_chain():
     # the planes hold exactly the bf16 intermediate
     got, want = hp.cpu().view(torch.float8_e5m2).float().sum(0), h.cpu().float() * 64.0
     inside = want.abs() >= 2.0**-7
-    assert torch.equal(got[inside], want[inside]) and float((got - want).abs().max()) <= 2.0**-17
+    assert torch.equal(got[inside], want[inside]) and float((got - want).abs().max()) <= 2.0**-17 + 2.0**-24
 
 
 def test_c_abi_bf16_entry_point_with_workspace():

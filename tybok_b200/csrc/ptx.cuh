@@ -173,7 +173,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
 __device__ __forceinline__ float gelu_tanh_fast(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
   const float y2 = 2.0f * k0 * (x + k1 * x * x * x);
-  return x * __frcp_rn(1.0f + __expf(-y2));
+  return __fdividef(x, 1.0f + __expf(-y2));  // approximate reciprocal: no special-value slow path
 }
 
 // ---------------------------------------------------------------- programmatic dependent launch

@@ -3,7 +3,7 @@
 // x * 2^shift = h1 + h2 + h3 with every term an e5m2 number: h1 = rn(x'), h2 = rn(x' - h1),
 // h3 = rn(x' - h1 - h2).  Three terms of 3 significant bits each carry the 8 significant bits
 // of a bf16 value, so the sum is exact whenever |x'| lies in [2^-7, 57344]; below that the
-// absolute error is at most 2^-17, above it the terms saturate.  A weight-stationary fp8
+// absolute error is at most 2^-17 + 2^-25, above it the terms saturate.  A weight-stationary fp8
 // tensor-core GEMM over the three planes therefore reproduces the bf16-activation product
 // exactly while the weights stay e4m3 in shared memory.
 #pragma once
@@ -14,23 +14,34 @@
 
 namespace tb {
 
-__device__ __forceinline__ float2 e5m2x2_to_float2(uint32_t pair) {
-  // e5m2 is the upper byte of an fp16: shift each byte into the high half of a 16-bit lane.
-  const uint32_t h = ((pair & 0xFFu) << 8) | ((pair & 0xFF00u) << 16);
-  return __half22float2(*reinterpret_cast<const __half2*>(&h));
+// The residuals are formed in packed fp16: a bf16 value inside the window is an fp16 number
+// (8 significant bits, exponent in range), each e5m2 term is the upper byte of an fp16, and
+// every difference x' - h1 (- h2) is again an fp16 number, so the arithmetic is exact there and
+// needs two conversions and two packed subtractions fewer per pair than an fp32 formulation.
+__device__ __forceinline__ uint32_t f16x2_from_floats(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ uint32_t e5m2x2_from_f16x2(uint32_t h2) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e5m2x2.f16x2 %0, %1;" : "=h"(r) : "r"(h2));
+  return r;
+}
+__device__ __forceinline__ uint32_t f16x2_sub(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
 }
 
 // Two values -> three byte pairs (low byte = first value).
 __device__ __forceinline__ void split3_pair(float x0, float x1, uint32_t& p1, uint32_t& p2, uint32_t& p3) {
-  p1 = __nv_cvt_float2_to_fp8x2(make_float2(x0, x1), __NV_SATFINITE, __NV_E5M2);
-  float2 f = e5m2x2_to_float2(p1);
-  x0 -= f.x;
-  x1 -= f.y;
-  p2 = __nv_cvt_float2_to_fp8x2(make_float2(x0, x1), __NV_SATFINITE, __NV_E5M2);
-  f = e5m2x2_to_float2(p2);
-  x0 -= f.x;
-  x1 -= f.y;
-  p3 = __nv_cvt_float2_to_fp8x2(make_float2(x0, x1), __NV_SATFINITE, __NV_E5M2);
+  uint32_t x = f16x2_from_floats(x0, x1);
+  p1 = e5m2x2_from_f16x2(x);
+  x = f16x2_sub(x, __byte_perm(p1, 0, 0x1404));  // e5m2 bytes -> the upper bytes of the two halves
+  p2 = e5m2x2_from_f16x2(x);
+  x = f16x2_sub(x, __byte_perm(p2, 0, 0x1404));
+  p3 = e5m2x2_from_f16x2(x);
 }
 
 // Four values -> one 32-bit word per plane (byte i = value i).

@@ -125,7 +125,9 @@ __device__ __forceinline__ void fail(Barriers* b, int* status, int code) {
   if (status) atomicCAS(status, 0, code);
 }
 
-__global__ void __launch_bounds__(THREADS, 1)
+// Bounded for two CTAs per SM: multi-wave full-K launches run with a shallow ring so that one
+// tile's epilogue overlaps the other's main loop (register budget 64K / 640 threads).
+__global__ void __launch_bounds__(THREADS, 2)
 w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1,
                const __grid_constant__ CUtensorMap tm_x, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -303,10 +305,27 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
 #pragma unroll
           for (int e = 0; e < 4; ++e) b0[e] = __bfloat162float(p.bias0[n + e]);
         }
+        if (p.epi == EPI_QKV_ROPE) {
+          // Positions and tables are constants: fetch the cos/sin of this thread's first row now.
+          const RopeEpi& r = p.rope;
+          const int tps = r.D >> 7;
+          const int rl = ((tid - 64) >> 5) * 2 + (v4p >> 4);
+          if (rl < own_rows && n_tile / tps < r.H + r.G) {
+            const long long tb = static_cast<long long>(r.pos[m_base + rank * rpr + rl]) * r.D + (n_tile % tps) * 64 + col0;
+            res_pf[0] = *reinterpret_cast<const uint2*>(r.cos + tb);
+            res_pf[1] = *reinterpret_cast<const uint2*>(r.cos + tb + (r.D >> 1));
+            res_pf[2] = *reinterpret_cast<const uint2*>(r.sin + tb);
+            res_pf[3] = *reinterpret_cast<const uint2*>(r.sin + tb + (r.D >> 1));
+          }
+        }
+      }
+      // These warps are idle until the accumulator is complete, so they wait for the previous
+      // kernel now, under the main loop, not between the accumulator and the stores.
+      if (p.pdl) pdl_wait();
+      if (n < p.n_out) {
         if (p.epi == EPI_RESIDUAL) {
-          // The residual was written by an earlier kernel: wait for it once, then fetch the rows
-          // this thread will finish first, long before the accumulator is ready.
-          if (p.pdl) pdl_wait();
+          // The residual was written by an earlier kernel: fetch the rows this thread will finish
+          // first, long before the accumulator is ready.
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int rl = ((tid - 64) >> 5) + 8 * u;
@@ -389,7 +408,6 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     // ---------------------------------------------------------- epilogue, phase B
     // 4 consecutive channels per thread, 8 token rows per pass; with split-K, rank r owns token
     // rows [r*R, (r+1)*R) and sums them over all ranks in rank order.
-    if (p.pdl) pdl_wait();  // outputs / residual may still be in use by the previous kernel
     if (tr && tid == 64) tr[9] = clock64();
     const int et = tid - 64;
     const int v4 = et & 31;
@@ -444,9 +462,12 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
         const int d = (n_tile - slot * tps) * 64 + col0;
         const int half = r.D >> 1;
         if (slot < r.H + r.G) {
-          const long long tb = static_cast<long long>(r.pos[m]) * r.D + d;
-          const uint2 c0 = *reinterpret_cast<const uint2*>(r.cos + tb), c1 = *reinterpret_cast<const uint2*>(r.cos + tb + half);
-          const uint2 n0 = *reinterpret_cast<const uint2*>(r.sin + tb), n1 = *reinterpret_cast<const uint2*>(r.sin + tb + half);
+          uint2 c0 = res_pf[0], c1 = res_pf[1], n0 = res_pf[2], n1 = res_pf[3];
+          if (rl != row0) {
+            const long long tb = static_cast<long long>(r.pos[m]) * r.D + d;
+            c0 = *reinterpret_cast<const uint2*>(r.cos + tb); c1 = *reinterpret_cast<const uint2*>(r.cos + tb + half);
+            n0 = *reinterpret_cast<const uint2*>(r.sin + tb); n1 = *reinterpret_cast<const uint2*>(r.sin + tb + half);
+          }
           const __nv_bfloat16* pc0 = reinterpret_cast<const __nv_bfloat16*>(&c0);
           const __nv_bfloat16* pc1 = reinterpret_cast<const __nv_bfloat16*>(&c1);
           const __nv_bfloat16* pn0 = reinterpret_cast<const __nv_bfloat16*>(&n0);
