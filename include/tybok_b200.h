@@ -174,11 +174,15 @@ int tybok_w8x3_qkv_rope(const void* x_planes, int x_shift, const void* w8_paired
  *   q          [B*L, H*D] bf16 (already rotated);  k_cache / v_cache  [B, G, Lcap, D] bf16, finite
  *   key_valid  NULL or uint8 [B, Lk]: 0 masks a key for every query of that batch element
  *   out        bf16 [B*L, H*D] and/or out_planes [3][B*L][H*D] planes of out * 2^out_shift
+ *   workspace  >= tybok_attention_workspace_bytes(B, L, H, Lk) bytes, 16-byte aligned (0 bytes, and
+ *              NULL allowed, when Lk <= 128): the key blocks of a query tile exchange their
+ *              partial outputs through it (L2), then merge in block order
  * Replaces GemmaAttention._forward_eager (tybok/policies/pi05/models/layers.py:166-191) and the
  * split-K flash kernels of tybok/policies/pi05/models/triton_expert_fused_qkv_rope_attn.py:322-433. */
 int tybok_attention(const void* q, const void* k_cache, const void* v_cache, const void* key_valid, void* out,
                     void* out_planes, int out_shift, int B, int L, int H, int G, int D, int Lk, int Lcap, float scale,
-                    int* status_word, void* stream);
+                    void* workspace, size_t workspace_bytes, int* status_word, void* stream);
+size_t tybok_attention_workspace_bytes(int B, int L, int H, int Lk);
 
 /* tybok_w8x3_geglu on ONE packed weight matrix [2*I, K]: every block of 128 rows holds the 64
  * gate rows of channels 64j..64j+63 followed by their 64 up rows (scale_packed [2*I] likewise),

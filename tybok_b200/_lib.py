@@ -41,7 +41,8 @@ SIGNATURES = {
     "tybok_rope_store": (c_int, [c_void_p, c_i64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                  c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "tybok_attention": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                c_int, c_int, c_int, c_int, ctypes.c_float, c_void_p, c_void_p]),
+                                c_int, c_int, c_int, c_int, ctypes.c_float, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "tybok_attention_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "tybok_w8x3_geglu_packed": (
         c_int,
         [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_i64, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,

@@ -10,12 +10,14 @@
 //   warp 0     TMA: Q tile, K block, V block (four 64-wide swizzled column chunks each).
 //   warp 1     tcgen05.mma: S = Q K^T (128x128x256), then O = P V (128x256x128) with P read from
 //              tensor memory and V as an MN-major shared-memory operand.
-//   warps 2-5  softmax on S straight out of tensor memory (one thread per query row, fp32,
-//              key-validity mask), P written back to tensor memory as bf16; epilogue.
-// The key blocks of one query tile form a thread-block cluster: each CTA stages its
-// un-normalised O and its (max, sum) row statistics in shared memory, the cluster meets at a
-// hardware barrier, and CTA r merges query rows r*R..(r+1)*R-1 over all key blocks in block
-// order through distributed shared memory (bit-reproducible, no global scratch).
+//   warps 2-9  softmax on S straight out of tensor memory (two threads per query row, 64 keys
+//              each, fp32, key-validity mask), P written back to tensor memory as bf16; epilogue.
+// The key blocks of one query tile form a thread-block cluster: each CTA writes its un-normalised
+// O rows (one bulk copy out of shared memory) and its (max, sum) row statistics to a workspace
+// in global memory, the cluster meets at a hardware barrier, and CTA r merges query rows
+// r*R..(r+1)*R-1 over all key blocks in block order out of L2 (bit-reproducible).  Distributed
+// shared memory moves about 20 bytes per clock and SM (measured), L2 several times that, which
+// is why the exchange does not go through the peers' shared memory.
 //
 // Algorithmic bytes: Q + O once per (layer, step), K + V once per (batch, kv head).
 // Flops: 4 * Mq * Lk * D * H.
@@ -35,8 +37,10 @@ constexpr int AT_BQ = 128;       // query rows per CTA (UMMA M)
 constexpr int AT_BK = 128;       // keys per CTA
 constexpr int AT_CHUNK = 16384;  // one 64-column chunk of a 128-row bf16 tile (128 rows x 128 bytes)
 constexpr int AT_TILE = 4 * AT_CHUNK;
-constexpr int AT_THREADS = 192;
+constexpr int AT_THREADS = 320;
+constexpr int AT_WS_PER_CTA = AT_BQ * AT_D * 4 + AT_BQ * 8;  // workspace per CTA: O rows (fp32) + (max, sum) per row
 constexpr int AT_MAX_SPLITS = 8;
+constexpr int AT_MERGE_BATCH = 3;  // query rows a merging thread has in flight
 constexpr int AT_SMEM = 3 * AT_TILE + 1024;
 
 struct RopeParams {
@@ -112,6 +116,7 @@ struct AttnParams {
   float plane_scale;
   int* status;
   int pdl;
+  uint8_t* ws;       // [CTA][AT_WS_PER_CTA] exchange workspace (nsplit > 1)
   long long* trace;  // tuning aid: [CTA][16] SM-clock samples, NULL in production
 };
 
@@ -120,8 +125,10 @@ struct __align__(8) AttnBars {
   uint32_t tmem_base;
   volatile int abort;
   uint32_t valid[4];     // key-validity bits of this CTA's 128 keys
-  float row_max[AT_BQ];  // per query row: running maximum (log2 domain) and sum of this key block
+  float row_max[AT_BQ];  // per query row: maximum (log2 domain) and sum of this key block
   float row_sum[AT_BQ];
+  float hmax[2][AT_BQ];  // the same per half of the key block (one half per thread of a row)
+  float hsum[2][AT_BQ];
   float wn[AT_MAX_SPLITS][AT_BQ];  // merge weights of the rows this CTA owns: exp2(m_s - m) / denominator
 };
 
@@ -174,7 +181,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     mbar_init(&bars.qk_full, 1);
     mbar_init(&bars.v_full, 1);
     mbar_init(&bars.s_full, 1);
-    mbar_init(&bars.p_full, 4);
+    mbar_init(&bars.p_full, 8);
     mbar_init(&bars.o_full, 1);
     bars.abort = 0;
     fence_barrier_init();
@@ -201,6 +208,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   tc_fence_after();
   const uint32_t tmem = bars.tmem_base;
   const uint32_t t_s = tmem, t_p = tmem + 128, t_o = tmem + 256;
+  const int nvalid = min(AT_BQ, p.L - qt * AT_BQ);  // real query rows of this tile
+  uint8_t* my_ws = p.ws + static_cast<long long>((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * AT_WS_PER_CTA;
   long long* tr = p.trace ? p.trace + 16ll * ((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) : nullptr;
   if (tr && tid == 0) { tr[0] = t_start; tr[1] = clock64(); }
 
@@ -250,67 +259,75 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (p.status) atomicCAS(p.status, 0, TYBOK_DEV_TIMEOUT_MMA);
     }
   } else {
-    // ------------------------------------------------------------ softmax, one thread per row
-    const int q = warp & 3;
+    // ------------------------------------------------------------ softmax, two threads per row
+    const int q = warp & 3;          // tensor-memory lane quadrant of this warp
+    const int hf = (warp - 2) >> 2;  // which 64 keys of the block / which 128 output columns
     const int row = q * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    const bool live = q * 32 < nvalid;  // warp-uniform: this quadrant holds real query rows
+    // Every named barrier below is reached by all eight warps whatever the waits returned.
     bool ok = __all_sync(0xffffffffu, at_wait(&bars.s_full, 0, &bars.abort));
-    if (tr && tid == 64) tr[2] = clock64();
-    if (ok) {
+    if (tr && tid == 128) tr[2] = clock64();
+    uint32_t v0[32], v1[32];
+    float mx = -1e30f;
+    if (ok && live) {
       tc_fence_after();
-      float mx = -1e30f;
+      tmem_ld32(t_s + lane_addr + (hf * 2) * 32, v0);
+      tmem_ld32(t_s + lane_addr + (hf * 2 + 1) * 32, v1);
+      tc_wait_ld();
+      const uint32_t b0 = bars.valid[hf * 2], b1 = bars.valid[hf * 2 + 1];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(t_s + lane_addr + c * 32, v);
-        tc_wait_ld();
-        const uint32_t bits = bars.valid[c];
-#pragma unroll
-        for (int e = 0; e < 32; ++e)
-          if ((bits >> e) & 1u) mx = fmaxf(mx, __uint_as_float(v[e]));
+      for (int e = 0; e < 32; ++e) {
+        if ((b0 >> e) & 1u) mx = fmaxf(mx, __uint_as_float(v0[e]));
+        if ((b1 >> e) & 1u) mx = fmaxf(mx, __uint_as_float(v1[e]));
       }
-      const float m2 = mx * p.scale_log2e;  // scale > 0, so the maximum commutes with the scaling
-      float sum = 0.f;
+    }
+    bars.hmax[hf][row] = mx;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    const float m2 = fmaxf(bars.hmax[0][row], bars.hmax[1][row]) * p.scale_log2e;  // scale > 0
+    float sum = 0.f;
+    if (ok && live) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(t_s + lane_addr + c * 32, v);
-        tc_wait_ld();
-        const uint32_t bits = bars.valid[c];
+      for (int c = 0; c < 2; ++c) {
+        const uint32_t bits = bars.valid[hf * 2 + c];
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          const float p0 = ((bits >> e) & 1u) ? exp2f(__uint_as_float(v[e]) * p.scale_log2e - m2) : 0.f;
-          const float p1 = ((bits >> (e + 1)) & 1u) ? exp2f(__uint_as_float(v[e + 1]) * p.scale_log2e - m2) : 0.f;
+          const float s0 = __uint_as_float(c == 0 ? v0[e] : v1[e]), s1 = __uint_as_float(c == 0 ? v0[e + 1] : v1[e + 1]);
+          const float p0 = ((bits >> e) & 1u) ? exp2f(s0 * p.scale_log2e - m2) : 0.f;
+          const float p1 = ((bits >> (e + 1)) & 1u) ? exp2f(s1 * p.scale_log2e - m2) : 0.f;
           sum += p0 + p1;
           const __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
           pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&pp);
         }
-        tmem_st16(t_p + lane_addr + c * 16, pk);
+        tmem_st16(t_p + lane_addr + (hf * 2 + c) * 16, pk);
       }
       tc_wait_st();
-      tc_fence_before();
-      bars.row_max[row] = m2;
-      bars.row_sum[row] = sum;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars.p_full);
-      if (tr && tid == 64) tr[3] = clock64();
-      // -------------------------------------------------------- stage O (un-normalised) as [col][row] fp32
-      ok = __all_sync(0xffffffffu, at_wait(&bars.o_full, 0, &bars.abort));
-      if (tr && tid == 64) tr[4] = clock64();
-      if (ok) {
-        tc_fence_after();
-        // 128 KB staging tile over the (no longer needed) Q and K tiles: [row][64 float4], the
-        // float4 index XORed with (row & 7) so that a warp's 16-byte stores spread over all banks.
-        float4* stage = reinterpret_cast<float4*>(smem);
+    }
+    tc_fence_before();
+    bars.hsum[hf][row] = sum;
+    if (hf == 0) bars.row_max[row] = m2;
+    __syncwarp();
+    if (ok && lane == 0) mbar_arrive(&bars.p_full);
+    if (tr && tid == 128) tr[3] = clock64();
+    // ---------------------------------------------------------- stage O (un-normalised), fp32
+    ok = ok && __all_sync(0xffffffffu, at_wait(&bars.o_full, 0, &bars.abort));
+    if (tr && tid == 128) tr[4] = clock64();
+    if (ok && live) {
+      tc_fence_after();
+      // Staging tile over the (no longer needed) Q and K tiles: [row][64 float4], the float4
+      // index XORed with (row & 7) so that a warp's 16-byte stores spread over all banks.
+      // Only the tile's real query rows are staged.
+      float4* stage = reinterpret_cast<float4*>(smem);
 #pragma unroll 1
-        for (int c = 0; c < 8; ++c) {
-          uint32_t v[32];
-          tmem_ld32(t_o + lane_addr + c * 32, v);
-          tc_wait_ld();
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(t_o + lane_addr + (hf * 4 + c) * 32, v);
+        tc_wait_ld();
+        if (row < nvalid) {
 #pragma unroll
           for (int j = 0; j < 8; ++j)
-            stage[row * 64 + ((c * 8 + j) ^ (row & 7))] =
+            stage[row * 64 + ((hf * 32 + c * 8 + j) ^ (row & 7))] =
                 make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
                             __uint_as_float(v[4 * j + 3]));
         }
@@ -320,31 +337,71 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       bars.abort = 1;
       if (p.status) atomicCAS(p.status, 0, TYBOK_DEV_TIMEOUT_EPILOGUE);
     }
+    if (p.nsplit > 1) {
+      // Publish this block's rows: statistics by plain stores, the staged O rows by one bulk copy
+      // out of shared memory.  Every softmax warp reaches this point, aborted or not.
+      fence_proxy_async();  // the staging stores, for the bulk copy engine
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (!bars.abort) {
+        if (hf == 0 && row < nvalid)
+          reinterpret_cast<float2*>(my_ws + AT_BQ * AT_D * 4)[row] =
+              make_float2(bars.row_max[row], bars.hsum[0][row] + bars.hsum[1][row]);
+        if (tid == 64) {
+          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(my_ws), "r"(smem_u32(smem)),
+                       "r"(nvalid * AT_D * 4)
+                       : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // written, not merely read out of shared memory
+          fence_proxy_async();
+        }
+      }
+    } else {
+      bars.row_sum[row] = bars.hsum[0][row] + bars.hsum[1][row];
+    }
   }
 
-  // ------------------------------------------------------------ meet: every key block staged
+  // ------------------------------------------------------------ meet: every key block published
   if (tr && tid == 64) tr[5] = clock64();
   tc_fence_before();
   if (p.nsplit > 1) {
     __syncwarp();
-    cluster_sync_all();
+    cluster_sync_all();  // release / acquire at cluster scope: the peers' workspace rows are visible
   } else {
     __syncthreads();
   }
 
   if (tr && tid == 64) tr[6] = clock64();
   if (warp >= 2 && !bars.abort) {
-    // Merge: this CTA owns query rows [r0, r1) of the tile; thread = (4 output columns, row parity).
+    // Merge: this CTA owns query rows [r0, r1) of the tile; thread = (4 output columns, row phase).
     const int et = tid - 64;
     const int c4 = et & 63, rsub = et >> 6;
-    // Only the tile's real query rows are merged, split evenly over the key-block CTAs.
-    const int nvalid = min(AT_BQ, p.L - qt * AT_BQ);
     const int rpr = (nvalid + p.nsplit - 1) / p.nsplit;
     const int r0 = sp * rpr, r1 = min(nvalid, r0 + rpr);
-    const uint32_t stage_addr = smem_u32(smem);
-    const uint32_t max_addr = smem_u32(&bars.row_max[0]), sum_addr = smem_u32(&bars.row_sum[0]);
+    const float4* stage = reinterpret_cast<const float4*>(smem);
     const long long hd = static_cast<long long>(p.H) * AT_D;
     const long long plane = static_cast<long long>(p.B) * p.L * hd;
+    const uint8_t* ws0 = my_ws - static_cast<long long>(sp) * AT_WS_PER_CTA;  // block 0 of this cluster
+    // The partial rows come out of L2 (about a microsecond away), so a thread requests a batch of
+    // rows -- every key block of each -- before it needs any of them; the first batch is in
+    // flight while the merge weights are worked out.
+    float4 buf[AT_MERGE_BATCH][AT_MAX_SPLITS];
+    auto fetch = [&](int rb) {
+#pragma unroll
+      for (int j = 0; j < AT_MERGE_BATCH; ++j) {
+        const int r = rb + 4 * j;
+        if (r < r1) {
+          const int idx = r * 64 + (c4 ^ (r & 7));
+#pragma unroll
+          for (int s = 0; s < AT_MAX_SPLITS; ++s)
+            if (s < p.nsplit)
+              buf[j][s] = s == sp ? stage[idx]
+                                  : __ldcg(reinterpret_cast<const float4*>(ws0 + static_cast<long long>(s) * AT_WS_PER_CTA) + idx);
+        }
+      }
+    };
+    int rb = r0 + rsub;
+    fetch(rb);
+    if (tr && tid == 64) tr[9] = clock64();
     if (r0 + et < r1) {  // one thread per owned row: normalised weight of every key block
       const int r = r0 + et;
       float w[AT_MAX_SPLITS], l[AT_MAX_SPLITS];
@@ -354,13 +411,19 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         w[s] = -1e30f;
         l[s] = 0.f;
         if (s < p.nsplit) {
-          const uint32_t am = p.nsplit > 1 ? dsmem_addr(max_addr + r * 4, s) : max_addr + r * 4;
-          const uint32_t al = p.nsplit > 1 ? dsmem_addr(sum_addr + r * 4, s) : sum_addr + r * 4;
-          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(w[s]) : "r"(am));
-          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(l[s]) : "r"(al));
+          if (p.nsplit > 1) {
+            const float2 st = __ldcg(reinterpret_cast<const float2*>(ws0 + static_cast<long long>(s) * AT_WS_PER_CTA +
+                                                                      AT_BQ * AT_D * 4) + r);
+            w[s] = st.x;
+            l[s] = st.y;
+          } else {
+            w[s] = bars.row_max[r];
+            l[s] = bars.row_sum[r];
+          }
         }
         mx = fmaxf(mx, w[s]);
       }
+      if (tr && tid == 64) tr[10] = clock64() + (mx == 12345.f);
       float denom = 0.f;
 #pragma unroll
       for (int s = 0; s < AT_MAX_SPLITS; ++s) {
@@ -370,50 +433,53 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const float inv = denom > 0.f ? 1.0f / denom : 0.f;
 #pragma unroll
       for (int s = 0; s < AT_MAX_SPLITS; ++s) bars.wn[s][et] = w[s] * inv;
+      if (tr && tid == 64) tr[11] = clock64() + (inv == 12345.f);
     }
-    asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps, unconditionally
+    asm volatile("bar.sync 1, 256;" ::: "memory");
     if (tr && tid == 64) tr[7] = clock64();
-#pragma unroll 4
-    for (int r = r0 + rsub; r < r1; r += 2) {
-      const int t = qt * AT_BQ + r;
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      const uint32_t local = stage_addr + (r * 64 + (c4 ^ (r & 7))) * 16;
+#pragma unroll 1
+    for (; rb < r1; rb += 4 * AT_MERGE_BATCH) {
 #pragma unroll
-      for (int s = 0; s < AT_MAX_SPLITS; ++s) {  // block order: bit-reproducible
-        if (s < p.nsplit) {
-          const float ws = bars.wn[s][r - r0];
-          const float4 v = ld_dsmem_f4(p.nsplit > 1 ? dsmem_addr(local, s) : local);
-          acc.x += ws * v.x; acc.y += ws * v.y; acc.z += ws * v.z; acc.w += ws * v.w;
+      for (int j = 0; j < AT_MERGE_BATCH; ++j) {
+        const int r = rb + 4 * j;
+        if (r < r1) {
+          const int t = qt * AT_BQ + r;
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int s = 0; s < AT_MAX_SPLITS; ++s) {  // block order: bit-reproducible
+            if (s < p.nsplit) {
+              const float ws = bars.wn[s][r - r0];
+              const float4 v = buf[j][s];
+              acc.x += ws * v.x; acc.y += ws * v.y; acc.z += ws * v.z; acc.w += ws * v.w;
+            }
+          }
+          const __nv_bfloat162 o01 = __floats2bfloat162_rn(acc.x, acc.y);
+          const __nv_bfloat162 o23 = __floats2bfloat162_rn(acc.z, acc.w);
+          const long long off = (static_cast<long long>(b) * p.L + t) * hd + static_cast<long long>(h) * AT_D + c4 * 4;
+          if (p.out) {
+            uint2 st;
+            st.x = *reinterpret_cast<const uint32_t*>(&o01);
+            st.y = *reinterpret_cast<const uint32_t*>(&o23);
+            *reinterpret_cast<uint2*>(p.out + off) = st;
+          }
+          if (p.out_planes) {
+            const float xs[4] = {__bfloat162float(o01.x) * p.plane_scale, __bfloat162float(o01.y) * p.plane_scale,
+                                 __bfloat162float(o23.x) * p.plane_scale, __bfloat162float(o23.y) * p.plane_scale};
+            uint32_t w1, w2, w3;
+            split3_quad(xs, w1, w2, w3);
+            uint8_t* dst = p.out_planes + off;
+            *reinterpret_cast<uint32_t*>(dst) = w1;
+            *reinterpret_cast<uint32_t*>(dst + plane) = w2;
+            *reinterpret_cast<uint32_t*>(dst + 2 * plane) = w3;
+          }
         }
       }
-      const float inv = 1.0f;
-      const __nv_bfloat162 o01 = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
-      const __nv_bfloat162 o23 = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
-      const long long off = (static_cast<long long>(b) * p.L + t) * hd + static_cast<long long>(h) * AT_D + c4 * 4;
-      if (p.out) {
-        uint2 st;
-        st.x = *reinterpret_cast<const uint32_t*>(&o01);
-        st.y = *reinterpret_cast<const uint32_t*>(&o23);
-        *reinterpret_cast<uint2*>(p.out + off) = st;
-      }
-      if (p.out_planes) {
-        const float xs[4] = {__bfloat162float(o01.x) * p.plane_scale, __bfloat162float(o01.y) * p.plane_scale,
-                             __bfloat162float(o23.x) * p.plane_scale, __bfloat162float(o23.y) * p.plane_scale};
-        uint32_t w1, w2, w3;
-        split3_quad(xs, w1, w2, w3);
-        uint8_t* dst = p.out_planes + off;
-        *reinterpret_cast<uint32_t*>(dst) = w1;
-        *reinterpret_cast<uint32_t*>(dst + plane) = w2;
-        *reinterpret_cast<uint32_t*>(dst + 2 * plane) = w3;
-      }
+      if (rb + 4 * AT_MERGE_BATCH < r1) fetch(rb + 4 * AT_MERGE_BATCH);
     }
   }
 
   if (tr && tid == 64) tr[8] = clock64();
-  if (p.nsplit > 1) {
-    __syncwarp();
-    cluster_sync_all();
-  }
+  // Nothing after the meeting point touches a peer's shared memory: CTAs leave on their own.
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
@@ -457,9 +523,16 @@ int tybok_rope_store(const void* qkv, int64_t ldq, const int* pos, const void* c
   return TYBOK_OK;
 }
 
+size_t tybok_attention_workspace_bytes(int B, int L, int H, int Lk) {
+  using namespace tb;
+  if (B <= 0 || L <= 0 || H <= 0 || Lk <= AT_BK) return 0;  // a single key block merges inside its CTA
+  const size_t nsplit = (static_cast<size_t>(Lk) + AT_BK - 1) / AT_BK, n_qt = (static_cast<size_t>(L) + AT_BQ - 1) / AT_BQ;
+  return nsplit * n_qt * H * B * AT_WS_PER_CTA;
+}
+
 int tybok_attention(const void* q, const void* k_cache, const void* v_cache, const void* key_valid, void* out,
                     void* out_planes, int out_shift, int B, int L, int H, int G, int D, int Lk, int Lcap, float scale,
-                    int* status_word, void* stream) {
+                    void* workspace, size_t workspace_bytes, int* status_word, void* stream) {
   using namespace tb;
   if (!q || !k_cache || !v_cache || (!out && !out_planes)) return host::fail(TYBOK_ERR_ARG, "attention: null pointer argument");
   if (D != AT_D) return host::fail(TYBOK_ERR_ARG, "attention: this kernel is built for head_dim 256");
@@ -471,6 +544,9 @@ int tybok_attention(const void* q, const void* k_cache, const void* v_cache, con
        reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(out_planes)) & 15)
     return host::fail(TYBOK_ERR_ARG, "attention: tensors must be 16-byte aligned");
   if (out_shift < -60 || out_shift > 60) return host::fail(TYBOK_ERR_ARG, "attention: exponent shift out of range");
+  const size_t need = tybok_attention_workspace_bytes(B, L, H, Lk);
+  if (need && (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15)))
+    return host::fail(TYBOK_ERR_WORKSPACE, "attention: workspace must hold tybok_attention_workspace_bytes(), 16-byte aligned");
   if (int rc = host::require_sm100()) return rc;
 
   CUtensorMap tm_q, tm_k, tm_v;
@@ -490,6 +566,7 @@ int tybok_attention(const void* q, const void* k_cache, const void* v_cache, con
   p.plane_scale = ldexpf(1.0f, out_shift);
   p.status = status_word;
   p.pdl = host::pdl_enabled() ? 1 : 0;
+  p.ws = static_cast<uint8_t*>(workspace);
   p.trace = host::trace_buffer();
 
   static bool attr_set[64] = {};
