@@ -149,6 +149,13 @@ int tybok_action_tail(const void* x, int64_t ldx, const float* mod, int64_t ldmo
                       const float* w_out, const float* b_out, float* x_t, float dt, const float* w_in,
                       const float* b_in, void* h, int M, int W, int A, void* stream);
 
+/* Residual add + affine LayerNorm of the SigLIP tower in one kernel (all tensors bf16, rows of W
+ * contiguous): x_out = x + y (bf16 add; y NULL: x_out = x, nothing stored), h = LayerNorm(x_out)
+ * * weight + bias with fp32 statistics.  x_out may alias x.  Replaces the residual adds and
+ * nn.LayerNorm calls of tybok/policies/pi05/models/vision.py (encoder layer forward). */
+int tybok_add_layernorm(const void* x, const void* y, const void* weight, const void* bias, int M, int W, float eps,
+                        void* x_out, void* h, void* stream);
+
 /* RoPE + KV store.  qkv is the packed projection output [B*L, (H+2G)*D] (row stride ldq); q and
  * k are rotated (rotate-half form, bf16 cos/sin tables [max_pos, D], bf16 arithmetic with the
  * reference's rounding points) at positions pos[B*L]; q goes to q_out [B*L, H*D], k and v to the

@@ -143,3 +143,37 @@ def test_engine_interface_on_synthetic_checkpoint():
         PI05B200Engine("synthetic:pi05_tiny", device="cuda", compile_model=True)
     with pytest.raises(RuntimeError):
         PI05B200Engine("synthetic:pi05_tiny", device="cuda", require_fused=True, action_fused=False)
+
+
+def test_fused_bf16_vision_tower_matches_the_torch_layer_chain():
+    """bf16 tower: residual adds inside the LayerNorm kernel, one q/k/v GEMM and the GELU GEMM
+    epilogue against the plain torch chain of the same weights."""
+    from tybok_b200.pi05 import PI05Model
+
+    params = quantize_hot_linears(random_pi05_params(PI05_TINY, seed=0), PI05_TINY)
+    model = PI05Model(params, PI05_TINY, device="cuda", vision_dtype=torch.bfloat16)
+    assert model.vis_layers is not None
+    images, *_ = tiny_inputs(PI05_TINY, seed=5, batch=2)
+    img = torch.cat([t.cuda() for t in images], dim=0)
+    fused = model.embed_image(img)
+    packed, model.vis_layers = model.vis_layers, None
+    plain = model.embed_image(img)
+    model.vis_layers = packed
+    assert fused.dtype == plain.dtype == torch.bfloat16
+    assert w8_ref.rel_l2(fused.float().cpu(), plain.float().cpu()) < 2e-2
+
+
+def test_add_layernorm_kernel():
+    from tybok_b200 import ops
+
+    g = torch.Generator().manual_seed(9)
+    for m, w in ((37, 1152), (5, 128), (64, 2048)):
+        x, y = (torch.empty(m, w).normal_(0, 1, generator=g).to(torch.bfloat16) for _ in range(2))
+        wt, b = (torch.empty(w).normal_(0, 1, generator=g).to(torch.bfloat16) for _ in range(2))
+        xs = x + y
+        ref = torch.nn.functional.layer_norm(xs.float(), (w,), wt.float(), b.float(), 1e-6).to(torch.bfloat16)
+        x_new, h = ops.add_layernorm(x.cuda(), y.cuda(), wt.cuda(), b.cuda())
+        assert torch.equal(x_new.cpu(), xs)
+        assert float((h.cpu().float() - ref.float()).abs().max()) <= 2.0**-6 * float(ref.float().abs().max())
+        _, h0 = ops.add_layernorm(xs.cuda(), None, wt.cuda(), b.cuda())
+        assert torch.equal(h0, h)

@@ -153,6 +153,93 @@ __global__ void __launch_bounds__(128) rmsnorm_kernel(const NormParams p) {
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// Residual add + affine LayerNorm of the vision tower (tybok/policies/pi05/models/vision.py:
+// x = x + sublayer(x); h = LayerNorm(x)): x_out = bf16(x + y), h = bf16(LN_fp32(x_out) * w + b).
+// One warp per row; the two bf16 adds and the norm that torch runs as two kernels are one.
+struct AddLnParams {
+  const __nv_bfloat16* x;
+  const __nv_bfloat16* y;  // or NULL: plain LayerNorm of x
+  const __nv_bfloat16* w;
+  const __nv_bfloat16* b;
+  __nv_bfloat16* x_out;    // or NULL
+  __nv_bfloat16* h;
+  int M, W;
+  float eps;
+  int pdl;
+};
+
+template <int VEC>
+__global__ void __launch_bounds__(128) add_layernorm_kernel(const AddLnParams p) {
+  if (p.pdl) pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m = blockIdx.x * 4 + warp;
+  if (p.pdl) pdl_wait();
+  if (m >= p.M) return;
+  const int nvec = p.W / 8;
+  const long long base = static_cast<long long>(m) * p.W;
+  float v[VEC][8];
+  float sm = 0.f;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    const int c = lane + 32 * i;
+    if (c < nvec) {
+      const uint4 rx = *reinterpret_cast<const uint4*>(p.x + base + c * 8);
+      const __nv_bfloat162* hx = reinterpret_cast<const __nv_bfloat162*>(&rx);
+      __nv_bfloat162 s2[4];
+      if (p.y) {
+        const uint4 ry = *reinterpret_cast<const uint4*>(p.y + base + c * 8);
+        const __nv_bfloat162* hy = reinterpret_cast<const __nv_bfloat162*>(&ry);
+#pragma unroll
+        for (int e = 0; e < 4; ++e)  // bf16 + bf16 -> bf16, as the residual add of the bf16 modules
+          s2[e] = __floats2bfloat162_rn(__bfloat162float(hx[e].x) + __bfloat162float(hy[e].x),
+                                        __bfloat162float(hx[e].y) + __bfloat162float(hy[e].y));
+        if (p.x_out) *reinterpret_cast<uint4*>(p.x_out + base + c * 8) = *reinterpret_cast<const uint4*>(s2);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s2[e] = hx[e];
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        v[i][2 * e] = __bfloat162float(s2[e].x);
+        v[i][2 * e + 1] = __bfloat162float(s2[e].y);
+        sm += v[i][2 * e] + v[i][2 * e + 1];
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sm += __shfl_xor_sync(0xffffffffu, sm, o);
+  const float mean = sm / static_cast<float>(p.W);
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i)
+    if (lane + 32 * i < nvec) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        v[i][e] -= mean;
+        ss += v[i][e] * v[i][e];
+      }
+    }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float rstd = rsqrtf(ss / static_cast<float>(p.W) + p.eps);
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    const int c = lane + 32 * i;
+    if (c < nvec) {
+      const uint4 rw = *reinterpret_cast<const uint4*>(p.w + c * 8), rb = *reinterpret_cast<const uint4*>(p.b + c * 8);
+      const __nv_bfloat16* pw = reinterpret_cast<const __nv_bfloat16*>(&rw);
+      const __nv_bfloat16* pb = reinterpret_cast<const __nv_bfloat16*>(&rb);
+      __nv_bfloat162 o[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        o[e] = __floats2bfloat162_rn(v[i][2 * e] * rstd * __bfloat162float(pw[2 * e]) + __bfloat162float(pb[2 * e]),
+                                     v[i][2 * e + 1] * rstd * __bfloat162float(pw[2 * e + 1]) + __bfloat162float(pb[2 * e + 1]));
+      *reinterpret_cast<uint4*>(p.h + base + c * 8) = *reinterpret_cast<const uint4*>(o);
+    }
+  }
+}
+
 }  // namespace tb
 
 namespace tb {
@@ -208,6 +295,39 @@ int tybok_rmsnorm(const void* x, int64_t ldx, const float* weight, const float* 
                   int M, int W, float eps, void* y, int64_t ldy, void* y_planes, int out_shift, void* stream) {
   return tb::launch_norm(x, ldx, weight, mod, ldmod, rows_per_group, nullptr, nullptr, M, W, eps, y, ldy, y_planes,
                          out_shift, stream);
+}
+
+int tybok_add_layernorm(const void* x, const void* y, const void* weight, const void* bias, int M, int W, float eps,
+                        void* x_out, void* h, void* stream) {
+  using namespace tb;
+  if (!x || !weight || !bias || !h) return host::fail(TYBOK_ERR_ARG, "add_layernorm: null pointer argument");
+  if (M <= 0 || W <= 0 || W % 8 != 0 || W > 8 * 256) return host::fail(TYBOK_ERR_ARG, "add_layernorm: W must be a multiple of 8 and <= 2048");
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(weight) |
+       reinterpret_cast<uintptr_t>(bias) | reinterpret_cast<uintptr_t>(x_out) | reinterpret_cast<uintptr_t>(h)) & 15)
+    return host::fail(TYBOK_ERR_ARG, "add_layernorm: tensors must be 16-byte aligned");
+  if (int rc = host::require_sm100()) return rc;
+  AddLnParams p{static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(y),
+                static_cast<const __nv_bfloat16*>(weight), static_cast<const __nv_bfloat16*>(bias),
+                static_cast<__nv_bfloat16*>(x_out), static_cast<__nv_bfloat16*>(h), M, W, eps, host::pdl_enabled() ? 1 : 0};
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((M + 3) / 4);
+  cfg.blockDim = dim3(128);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 0;  // neighbours are library kernels that know nothing of programmatic launches
+  p.pdl = 0;
+  const int per_lane = (W / 8 + 31) / 32;
+  cudaError_t e;
+  if (per_lane <= 1) e = cudaLaunchKernelEx(&cfg, add_layernorm_kernel<1>, p);
+  else if (per_lane <= 2) e = cudaLaunchKernelEx(&cfg, add_layernorm_kernel<2>, p);
+  else if (per_lane <= 5) e = cudaLaunchKernelEx(&cfg, add_layernorm_kernel<5>, p);
+  else e = cudaLaunchKernelEx(&cfg, add_layernorm_kernel<8>, p);
+  if (e != cudaSuccess) return host::fail_cuda("launch add_layernorm_kernel");
+  host::count_launch();
+  return TYBOK_OK;
 }
 
 int tybok_layernorm_modulate(const void* x, int64_t ldx, const void* shift, const void* scale, int M, int W, float eps,

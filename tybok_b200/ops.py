@@ -52,6 +52,8 @@ _L.define("w8x3_qkv_rope(Tensor planes, int shift, Tensor w8_paired, Tensor scal
           "Tensor sin, Tensor(a!) k_cache, Tensor(b!) v_cache, int heads, int key_off, int token_tile, int splits) "
           "-> Tensor")
 
+_L.define("add_layernorm(Tensor x, Tensor? y, Tensor weight, Tensor bias, float eps) -> (Tensor, Tensor)")
+
 _status: dict[int, torch.Tensor] = {}
 
 
@@ -330,6 +332,24 @@ def _w8x3_geglu_packed_cuda(planes, shift, w8_packed, scale_packed, out_bf16, ou
 
 
 _L.impl("w8x3_geglu_packed", _w8x3_geglu_packed_cuda, "CUDA")
+def _add_layernorm_cuda(x, y, weight, bias, eps):
+    lib = _lib.load()
+    w = x.shape[-1]
+    for t in (x, y, weight, bias):
+        if t is not None and (t.dtype != torch.bfloat16 or not t.is_contiguous()):
+            raise TypeError("add_layernorm: tensors must be contiguous bf16")
+    if (y is not None and y.shape != x.shape) or weight.numel() != w or bias.numel() != w:
+        raise ValueError("add_layernorm: shapes disagree")
+    m = x.numel() // w
+    x_out = torch.empty_like(x) if y is not None else x.new_empty(0)  # an op output must not alias an input
+    h = torch.empty_like(x)
+    rc = lib.tybok_add_layernorm(x.data_ptr(), _ptr(y), weight.data_ptr(), bias.data_ptr(), m, w, float(eps),
+                                 x_out.data_ptr() if y is not None else None, h.data_ptr(), _stream(x))
+    _lib.check(rc, "tybok_add_layernorm")
+    return x_out, h
+
+
+_L.impl("add_layernorm", _add_layernorm_cuda, "CUDA")
 _L.impl("split3", _split3_cuda, "CUDA")
 _L.impl("w8x3_linear", _w8x3_linear_cuda, "CUDA")
 _L.impl("w8x3_geglu", _w8x3_geglu_cuda, "CUDA")
@@ -443,6 +463,13 @@ def action_tail(x, mod, w_out, b_out, x_t, dt, w_in, b_in, *, rows_per_group=1, 
     """Final norm + fp32 out-projection + Euler update of ``x_t`` (in place) + next suffix
     embedding (returned, bf16); ``x=None`` computes only the embedding; see ``tybok_action_tail``."""
     return torch.ops.tybok_b200.action_tail(x, mod, rows_per_group, eps, w_out, b_out, x_t, dt, w_in, b_in, embed)
+
+
+def add_layernorm(x, y, weight, bias, *, eps=1e-6):
+    """``x_new = x + y`` (``y=None``: ``x``) and ``LayerNorm(x_new) * weight + bias``, bf16, one kernel;
+    returns ``(x_new, h)``; see ``tybok_add_layernorm``."""
+    x_new, h = torch.ops.tybok_b200.add_layernorm(x, y, weight, bias, eps)
+    return (x if y is None else x_new), h
 
 
 def launch_count() -> int:

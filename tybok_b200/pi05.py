@@ -117,6 +117,7 @@ class PI05Model:
         dev = self.device
         self.vision_dtype = vision_dtype
         self.vision = {k: v.to(dev, vision_dtype) for k, v in params.items() if k.startswith(VISION)}
+        self.vis_layers = self._pack_vision() if vision_dtype == torch.bfloat16 else None
         self.proj_w = params[f"{PROJECTOR}.weight"].to(dev, vision_dtype)
         self.proj_b = params[f"{PROJECTOR}.bias"].to(dev, vision_dtype)
         self.embed = params[f"{VLM}.embed_tokens.weight"].to(dev)
@@ -160,8 +161,53 @@ class PI05Model:
         self.final_mods = [F.linear(cond[i : i + 1], *self.final_norm).contiguous() for i in range(s.steps)]
 
     # ------------------------------------------------------------------ non-fp8 front end
+    def _pack_vision(self):
+        """Per-layer tensors of the bf16 tower in the form ``_embed_image_fused`` uses: q/k/v as one
+        projection, fc1 transposed for the bias+GELU GEMM epilogue."""
+        p, layers = self.vision, []
+        for i in range(self.shape.vision.layers):
+            base = f"{VISION}.encoder.layers.{i}"
+            g = lambda n: p[f"{base}.{n}"]  # noqa: E731
+            layers.append({
+                "ln1": (g("layer_norm1.weight").contiguous(), g("layer_norm1.bias").contiguous()),
+                "qkv_w": torch.cat([g(f"self_attn.{n}_proj.weight") for n in "qkv"]).contiguous(),
+                "qkv_b": torch.cat([g(f"self_attn.{n}_proj.bias") for n in "qkv"]).contiguous(),
+                "o": (g("self_attn.out_proj.weight"), g("self_attn.out_proj.bias")),
+                "ln2": (g("layer_norm2.weight").contiguous(), g("layer_norm2.bias").contiguous()),
+                "fc1_wt": g("mlp.fc1.weight").t(), "fc1_b": g("mlp.fc1.bias"),
+                "fc2": (g("mlp.fc2.weight"), g("mlp.fc2.bias")),
+            })
+        return layers
+
+    def _embed_image_fused(self, image: torch.Tensor) -> torch.Tensor:
+        """The bf16 tower with 7 kernels per encoder layer instead of 14: each residual add runs
+        inside the LayerNorm kernel that follows it, q/k/v are one GEMM, GELU is the epilogue of
+        fc1 (same layer math as ``embed_image``; vision.py:200-289)."""
+        v, p = self.shape.vision, self.vision
+        x = F.conv2d(image.to(torch.bfloat16), p[f"{VISION}.embeddings.patch_embedding.weight"],
+                     p[f"{VISION}.embeddings.patch_embedding.bias"], stride=v.patch)
+        x = (x.flatten(2).transpose(1, 2) + p[f"{VISION}.embeddings.position_embedding.weight"][None]).contiguous()
+        b, l, hid = x.shape
+        hd = hid // v.heads
+        y = None
+        for lay in self.vis_layers:
+            x, h = ops.add_layernorm(x, y, *lay["ln1"])
+            qkv = F.linear(h, lay["qkv_w"], lay["qkv_b"]).view(b, l, 3, v.heads, hd)
+            q, k, val = (qkv[:, :, j].transpose(1, 2) for j in range(3))
+            a = F.scaled_dot_product_attention(q, k, val, scale=hd**-0.5).transpose(1, 2).reshape(b, l, hid)
+            y = F.linear(a, *lay["o"])
+            x, h = ops.add_layernorm(x, y, *lay["ln2"])
+            h = torch._addmm_activation(lay["fc1_b"], h.view(b * l, hid), lay["fc1_wt"], use_gelu=True)  # tanh GELU
+            y = F.linear(h, *lay["fc2"]).view(b, l, hid)
+        _, h = ops.add_layernorm(x, y, p[f"{VISION}.post_layernorm.weight"].contiguous(),
+                                 p[f"{VISION}.post_layernorm.bias"].contiguous())
+        return F.linear(h, self.proj_w, self.proj_b)
+
     def embed_image(self, image: torch.Tensor) -> torch.Tensor:
-        """SigLIP tower + projector (torch ops; tybok/policies/pi05/models/vision.py:200-289)."""
+        """SigLIP tower + projector (tybok/policies/pi05/models/vision.py:200-289); plain torch ops
+        unless the tower is bf16."""
+        if self.vis_layers is not None:
+            return self._embed_image_fused(image)
         v, p, dt = self.shape.vision, self.vision, self.vision_dtype
         x = F.conv2d(image.to(dt), p[f"{VISION}.embeddings.patch_embedding.weight"],
                      p[f"{VISION}.embeddings.patch_embedding.bias"], stride=v.patch)
