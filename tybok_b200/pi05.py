@@ -184,9 +184,14 @@ class PI05Model:
         inside the LayerNorm kernel that follows it, q/k/v are one GEMM, GELU is the epilogue of
         fc1 (same layer math as ``embed_image``; vision.py:200-289)."""
         v, p = self.shape.vision, self.vision
-        x = F.conv2d(image.to(torch.bfloat16), p[f"{VISION}.embeddings.patch_embedding.weight"],
-                     p[f"{VISION}.embeddings.patch_embedding.bias"], stride=v.patch)
-        x = (x.flatten(2).transpose(1, 2) + p[f"{VISION}.embeddings.position_embedding.weight"][None]).contiguous()
+        # Patch embedding as a GEMM over flattened patches (the stride == kernel convolution of
+        # vision.py; cuDNN runs it as an fp32 direct convolution that takes longer than 20 layers' GEMMs).
+        b, side = image.shape[0], v.image // v.patch
+        patches = image.to(torch.bfloat16).view(b, 3, side, v.patch, side, v.patch).permute(0, 2, 4, 1, 3, 5)
+        patches = patches.reshape(b, side * side, 3 * v.patch * v.patch)
+        wp = p[f"{VISION}.embeddings.patch_embedding.weight"]
+        x = F.linear(patches, wp.view(wp.shape[0], -1), p[f"{VISION}.embeddings.patch_embedding.bias"])
+        x = x + p[f"{VISION}.embeddings.position_embedding.weight"][None]
         b, l, hid = x.shape
         hd = hid // v.heads
         y = None
