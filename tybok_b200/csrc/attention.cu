@@ -117,6 +117,7 @@ struct AttnParams {
   int* status;
   int pdl;
   uint8_t* ws;       // [CTA][AT_WS_PER_CTA] exchange workspace (nsplit > 1)
+  int dsplit;        // 1, or 2: two CTAs per (query tile, key block), each producing half of the output columns
   long long* trace;  // tuning aid: [CTA][16] SM-clock samples, NULL in production
 };
 
@@ -169,7 +170,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
   const int sp = blockIdx.x;  // key block == rank in the cluster
   const int n_qt = (p.L + AT_BQ - 1) / AT_BQ;
-  const int h = blockIdx.y / n_qt, qt = blockIdx.y % n_qt;
+  // Small grids split the value / output columns over two CTAs (both compute the full S and
+  // softmax; each multiplies P by its half of V): half the exchange volume per CTA.
+  const int dh = blockIdx.y % p.dsplit;
+  const int h = (blockIdx.y / p.dsplit) / n_qt, qt = (blockIdx.y / p.dsplit) % n_qt;
+  const int dv = AT_D / p.dsplit;  // output columns of this CTA
   const int b = blockIdx.z;
   const int g = h / (p.H / p.G);
   const int key0 = sp * AT_BK;
@@ -222,8 +227,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       mbar_arrive_expect_tx(&bars.qk_full, 2 * AT_TILE);
       for (int c = 0; c < 4; ++c) tma_load_2d(sq + c * AT_CHUNK, &tm_q, &bars.qk_full, h * AT_D + c * 64, qrow);
       for (int c = 0; c < 4; ++c) tma_load_2d(sk + c * AT_CHUNK, &tm_k, &bars.qk_full, c * 64, krow);
-      mbar_arrive_expect_tx(&bars.v_full, AT_TILE);
-      for (int c = 0; c < 4; ++c) tma_load_2d(sv + c * AT_CHUNK, &tm_v, &bars.v_full, c * 64, krow);
+      const int nvc = dv / 64;  // 64-column chunks of V this CTA multiplies
+      mbar_arrive_expect_tx(&bars.v_full, nvc * AT_CHUNK);
+      for (int c = 0; c < nvc; ++c) tma_load_2d(sv + c * AT_CHUNK, &tm_v, &bars.v_full, dh * dv + c * 64, krow);
     }
   } else if (warp == 1) {
     const bool leader = elect_one();
@@ -245,7 +251,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     if (ok) {
       tc_fence_after();
       // O[128 x 256] = P[128 x 128 keys] . V[keys x 256]: B operand N = D (MN-major), K = keys.
-      const uint32_t idesc_o = idesc_bf16_f32(AT_BQ, AT_D) | (1u << 16);
+      const uint32_t idesc_o = idesc_bf16_f32(AT_BQ, dv) | (1u << 16);
       const uint32_t v_addr = smem_u32(sv);
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {  // 16 keys per step: 16 rows x 128 bytes inside every chunk
@@ -319,15 +325,17 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       // index XORed with (row & 7) so that a warp's 16-byte stores spread over all banks.
       // Only the tile's real query rows are staged.
       float4* stage = reinterpret_cast<float4*>(smem);
+      const int q4 = dv / 4;      // float4 per staged row
+      const int nch = dv / 64;    // 32-column chunks per thread (this thread's half of the row)
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < nch; ++c) {
         uint32_t v[32];
-        tmem_ld32(t_o + lane_addr + (hf * 4 + c) * 32, v);
+        tmem_ld32(t_o + lane_addr + (hf * nch + c) * 32, v);
         tc_wait_ld();
         if (row < nvalid) {
 #pragma unroll
           for (int j = 0; j < 8; ++j)
-            stage[row * 64 + ((hf * 32 + c * 8 + j) ^ (row & 7))] =
+            stage[row * q4 + (((hf * nch + c) * 8 + j) ^ (row & 7))] =
                 make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
                             __uint_as_float(v[4 * j + 3]));
         }
@@ -348,7 +356,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
               make_float2(bars.row_max[row], bars.hsum[0][row] + bars.hsum[1][row]);
         if (tid == 64) {
           asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(my_ws), "r"(smem_u32(smem)),
-                       "r"(nvalid * AT_D * 4)
+                       "r"(nvalid * dv * 4)
                        : "memory");
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // written, not merely read out of shared memory
@@ -374,7 +382,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   if (warp >= 2 && !bars.abort) {
     // Merge: this CTA owns query rows [r0, r1) of the tile; thread = (4 output columns, row phase).
     const int et = tid - 64;
-    const int c4 = et & 63, rsub = et >> 6;
+    const int q4 = dv / 4;          // float4 per row: 64, or 32 with split columns
+    const int rstep = 256 / q4;     // rows per pass of the 256 merging threads
+    const int c4 = et % q4, rsub = et / q4;
     const int rpr = (nvalid + p.nsplit - 1) / p.nsplit;
     const int r0 = sp * rpr, r1 = min(nvalid, r0 + rpr);
     const float4* stage = reinterpret_cast<const float4*>(smem);
@@ -388,9 +398,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     auto fetch = [&](int rb) {
 #pragma unroll
       for (int j = 0; j < AT_MERGE_BATCH; ++j) {
-        const int r = rb + 4 * j;
+        const int r = rb + rstep * j;
         if (r < r1) {
-          const int idx = r * 64 + (c4 ^ (r & 7));
+          const int idx = r * q4 + (c4 ^ (r & 7));
 #pragma unroll
           for (int s = 0; s < AT_MAX_SPLITS; ++s)
             if (s < p.nsplit)
@@ -438,10 +448,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     asm volatile("bar.sync 1, 256;" ::: "memory");
     if (tr && tid == 64) tr[7] = clock64();
 #pragma unroll 1
-    for (; rb < r1; rb += 4 * AT_MERGE_BATCH) {
+    for (; rb < r1; rb += rstep * AT_MERGE_BATCH) {
 #pragma unroll
       for (int j = 0; j < AT_MERGE_BATCH; ++j) {
-        const int r = rb + 4 * j;
+        const int r = rb + rstep * j;
         if (r < r1) {
           const int t = qt * AT_BQ + r;
           float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -455,7 +465,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           }
           const __nv_bfloat162 o01 = __floats2bfloat162_rn(acc.x, acc.y);
           const __nv_bfloat162 o23 = __floats2bfloat162_rn(acc.z, acc.w);
-          const long long off = (static_cast<long long>(b) * p.L + t) * hd + static_cast<long long>(h) * AT_D + c4 * 4;
+          const long long off = (static_cast<long long>(b) * p.L + t) * hd + static_cast<long long>(h) * AT_D + dh * dv + c4 * 4;
           if (p.out) {
             uint2 st;
             st.x = *reinterpret_cast<const uint32_t*>(&o01);
@@ -474,7 +484,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           }
         }
       }
-      if (rb + 4 * AT_MERGE_BATCH < r1) fetch(rb + 4 * AT_MERGE_BATCH);
+      if (rb + rstep * AT_MERGE_BATCH < r1) fetch(rb + rstep * AT_MERGE_BATCH);
     }
   }
 
@@ -527,7 +537,7 @@ size_t tybok_attention_workspace_bytes(int B, int L, int H, int Lk) {
   using namespace tb;
   if (B <= 0 || L <= 0 || H <= 0 || Lk <= AT_BK) return 0;  // a single key block merges inside its CTA
   const size_t nsplit = (static_cast<size_t>(Lk) + AT_BK - 1) / AT_BK, n_qt = (static_cast<size_t>(L) + AT_BQ - 1) / AT_BQ;
-  return nsplit * n_qt * H * B * AT_WS_PER_CTA;
+  return 2 * nsplit * n_qt * H * B * AT_WS_PER_CTA;  // room for the split-column form of small grids
 }
 
 int tybok_attention(const void* q, const void* k_cache, const void* v_cache, const void* key_valid, void* out,
@@ -567,6 +577,8 @@ int tybok_attention(const void* q, const void* k_cache, const void* v_cache, con
   p.status = status_word;
   p.pdl = host::pdl_enabled() ? 1 : 0;
   p.ws = static_cast<uint8_t*>(workspace);
+  const int n_qt = (L + AT_BQ - 1) / AT_BQ;
+  p.dsplit = (nsplit > 1 && 2 * nsplit * H * n_qt * B <= host::sm_count()) ? 2 : 1;
   p.trace = host::trace_buffer();
 
   static bool attr_set[64] = {};
@@ -576,9 +588,8 @@ int tybok_attention(const void* q, const void* k_cache, const void* v_cache, con
       return host::fail_cuda("cudaFuncSetAttribute(attention_kernel)");
     attr_set[dev] = true;
   }
-  const int n_qt = (L + AT_BQ - 1) / AT_BQ;
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(nsplit, H * n_qt, B);
+  cfg.gridDim = dim3(nsplit, H * n_qt * p.dsplit, B);
   cfg.blockDim = dim3(AT_THREADS);
   cfg.dynamicSmemBytes = AT_SMEM;
   cfg.stream = static_cast<cudaStream_t>(stream);
