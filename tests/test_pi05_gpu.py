@@ -177,3 +177,34 @@ def test_add_layernorm_kernel():
         assert float((h.cpu().float() - ref.float()).abs().max()) <= 2.0**-6 * float(ref.float().abs().max())
         _, h0 = ops.add_layernorm(xs.cuda(), None, wt.cuda(), b.cuda())
         assert torch.equal(h0, h)
+
+
+@pytest.mark.parametrize("m,w", [(50, 1024), (50, 2048), (7, 256), (10, 128), (130, 512)])
+def test_action_tail_matches_torch(m, w):
+    """Final AdaRMS norm + fp32 out-projection + Euler update + next embedding
+    (flow_matching.py:193-254,464-556) against the same steps in torch fp32."""
+    from tybok_b200 import ops
+
+    g = torch.Generator().manual_seed(17)
+    rnd = lambda *s, std=1.0: torch.empty(*s).normal_(0, std, generator=g)  # noqa: E731
+    x = rnd(m, w).to(torch.bfloat16)
+    mod = rnd(1, 3 * w, std=0.3)
+    w_out, b_out, w_in, b_in = rnd(32, w, std=0.05), rnd(32, std=0.1), rnd(w, 32, std=0.2), rnd(w, std=0.1)
+    x_t = rnd(m, 32)
+    dt = -0.1
+    y = w8_ref.adarms_norm(x, mod[:, : 2 * w])[0].float()
+    xt_ref = x_t + dt * (y @ w_out.T + b_out)
+    h_ref = (xt_ref @ w_in.T + b_in).to(torch.bfloat16)
+    xt = x_t.cuda().clone()
+    h = ops.action_tail(x.cuda(), mod.cuda(), w_out.cuda(), b_out.cuda(), xt, dt, w_in.cuda(), b_in.cuda(),
+                        rows_per_group=m)
+    torch.cuda.synchronize()
+    assert float((xt.cpu() - xt_ref).abs().max()) <= 2e-4 * max(1.0, float(xt_ref.abs().max()))
+    assert w8_ref.rel_l2(h.float().cpu(), h_ref.float()) <= 4e-3
+    # embedding only (the first step), and update only (the last step)
+    h0 = ops.action_tail(None, None, None, None, xt, dt, w_in.cuda(), b_in.cuda())
+    assert torch.equal(h0, h)
+    xt2 = x_t.cuda().clone()
+    none = ops.action_tail(x.cuda(), mod.cuda(), w_out.cuda(), b_out.cuda(), xt2, dt, w_in.cuda(), b_in.cuda(),
+                           rows_per_group=m, embed=False)
+    assert none.numel() == 0 and torch.equal(xt2, xt)
