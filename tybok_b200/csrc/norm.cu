@@ -46,9 +46,28 @@ __global__ void __launch_bounds__(128) rmsnorm_kernel(const NormParams p) {
   if (p.pdl) pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m = blockIdx.x * 4 + warp;
+  const int nvec = p.W / 8;  // 8-element vectors per row
+  // Scale / shift are constants of the step: fetch them before waiting for the previous kernel.
+  const float* mod = (p.mod && m < p.M) ? p.mod + static_cast<long long>(m / p.rows_per_group) * p.ldmod : nullptr;
+  constexpr bool PRE = VEC <= 8;  // wider rows would not fit the constants in registers
+  float4 csc[PRE ? VEC : 1][2], csh[PRE ? VEC : 1][2];
+  if (PRE && !p.ln_scale && m < p.M) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const int c = lane + 32 * i;
+      if (FULL || c < nvec) {
+        const float* a = mod ? mod + c * 8 : p.weight + c * 8;
+        csc[PRE ? i : 0][0] = *reinterpret_cast<const float4*>(a);
+        csc[PRE ? i : 0][1] = *reinterpret_cast<const float4*>(a + 4);
+        if (mod) {
+          csh[PRE ? i : 0][0] = *reinterpret_cast<const float4*>(a + p.W);
+          csh[PRE ? i : 0][1] = *reinterpret_cast<const float4*>(a + p.W + 4);
+        }
+      }
+    }
+  }
   if (p.pdl) pdl_wait();
   if (m < p.M) {
-    const int nvec = p.W / 8;  // 8-element vectors per row
     const __nv_bfloat16* row = p.x + m * p.ldx;
     float v[VEC][8];
     float ss = 0.f;
@@ -92,7 +111,6 @@ __global__ void __launch_bounds__(128) rmsnorm_kernel(const NormParams p) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     const float rstd = rsqrtf(ss / static_cast<float>(p.W) + p.eps);
-    const float* mod = p.mod ? p.mod + static_cast<long long>(m / p.rows_per_group) * p.ldmod : nullptr;
     const long long plane = static_cast<long long>(p.M) * p.W;
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
@@ -114,16 +132,17 @@ __global__ void __launch_bounds__(128) rmsnorm_kernel(const NormParams p) {
           }
         } else {
         // x * rstd is formed in fp32 (the bf16 x promotes), as in the reference's _norm
-        float sc[8], sh[8];
-        {
+        float4 q0, q1, h0 = make_float4(0.f, 0.f, 0.f, 0.f), h1 = h0;
+        if (PRE) {
+          q0 = csc[PRE ? i : 0][0]; q1 = csc[PRE ? i : 0][1];
+          if (mod) { h0 = csh[PRE ? i : 0][0]; h1 = csh[PRE ? i : 0][1]; }
+        } else {
           const float* a = mod ? mod + c * 8 : p.weight + c * 8;
-          const float4 a0 = *reinterpret_cast<const float4*>(a), a1 = *reinterpret_cast<const float4*>(a + 4);
-          sc[0] = a0.x; sc[1] = a0.y; sc[2] = a0.z; sc[3] = a0.w; sc[4] = a1.x; sc[5] = a1.y; sc[6] = a1.z; sc[7] = a1.w;
-          if (mod) {
-            const float4 b0 = *reinterpret_cast<const float4*>(a + p.W), b1 = *reinterpret_cast<const float4*>(a + p.W + 4);
-            sh[0] = b0.x; sh[1] = b0.y; sh[2] = b0.z; sh[3] = b0.w; sh[4] = b1.x; sh[5] = b1.y; sh[6] = b1.z; sh[7] = b1.w;
-          }
+          q0 = *reinterpret_cast<const float4*>(a); q1 = *reinterpret_cast<const float4*>(a + 4);
+          if (mod) { h0 = *reinterpret_cast<const float4*>(a + p.W); h1 = *reinterpret_cast<const float4*>(a + p.W + 4); }
         }
+        const float sc[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        const float sh[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           float t = v[i][e] * rstd * (1.0f + sc[e]);
