@@ -181,6 +181,8 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
   // Per-thread epilogue constants (4 consecutive channels), fetched while the main loop runs.
   float s0[4] = {0, 0, 0, 0}, s1[4] = {0, 0, 0, 0}, b0[4] = {0, 0, 0, 0};
   uint2 res_pf[4] = {};  // residual of this thread's first four token rows, fetched early
+  float4 gate_pf = make_float4(0.f, 0.f, 0.f, 0.f);  // gate values of the first token row's group (fp32 form)
+  int gate_pf_group = -1;
   // Split-K ownership: the tile's real token rows are divided evenly over the cluster ranks.
   const int m_base = t_tile * p.bt;
   const int nvalid = min(p.bt, p.M - m_base);
@@ -304,6 +306,13 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
         if (p.bias0) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) b0[e] = __bfloat162float(p.bias0[n + e]);
+        }
+        if (p.epi == EPI_RESIDUAL && p.gate && !p.gate_bf16) {
+          // fp32 gates are per-step constants (precomputed modulations), touched once per chunk
+          // and therefore cold in L2: fetch them now, not between the accumulator and the stores.
+          gate_pf_group = (m_base + rank * rpr) / p.rows_per_gate;
+          gate_pf = *reinterpret_cast<const float4*>(static_cast<const float*>(p.gate) +
+                                                     static_cast<long long>(gate_pf_group) * p.ldgate + n);
         }
         if (p.epi == EPI_QKV_ROPE) {
           // Positions and tables are constants: fetch the cos/sin of this thread's first row now.
@@ -507,7 +516,9 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
             gv[0] = __bfloat162float(g01.x); gv[1] = __bfloat162float(g01.y);
             gv[2] = __bfloat162float(g23.x); gv[3] = __bfloat162float(g23.y);
           } else {
-            const float4 gr = *reinterpret_cast<const float4*>(static_cast<const float*>(p.gate) + gi);
+            const float4 gr = m / p.rows_per_gate == gate_pf_group
+                                  ? gate_pf
+                                  : *reinterpret_cast<const float4*>(static_cast<const float*>(p.gate) + gi);
             gv[0] = bf16_round(gr.x); gv[1] = bf16_round(gr.y); gv[2] = bf16_round(gr.z); gv[3] = bf16_round(gr.w);
           }
 #pragma unroll
