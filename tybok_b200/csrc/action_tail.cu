@@ -87,6 +87,23 @@ __global__ void __launch_bounds__(TAIL_THREADS) action_tail_kernel(const TailPar
       for (int q = 0; q < 4; ++q)
         wi[i][q] = *reinterpret_cast<const float4*>(p.w_in + static_cast<long long>(k0 + (tid >> 1) + 128 * i) * TAIL_A + (tid & 1) * 16 + 4 * q);
   }
+  // The modulation row, like the biases, is a per-step constant nobody has touched since the
+  // last chunk (cold in L2): fetch it before waiting as well.
+  constexpr int PT = KS / 64;
+  float msc[PT], msh[PT];
+  float bo = 0.f;
+  if (p.x) {
+    const int t = tid >> 6, c = (tid & 63) * PT;
+    const float* mod = p.mod + static_cast<long long>(m0 + t < p.M ? (m0 + t) / p.rows_per_group : 0) * p.ldmod + k0 + c;
+#pragma unroll
+    for (int e = 0; e < PT; ++e) { msc[e] = mod[e]; msh[e] = mod[p.W + e]; }
+    bo = p.b_out[lane];
+  }
+  float bi[NI];
+  if (p.h) {
+#pragma unroll
+    for (int i = 0; i < NI; ++i) bi[i] = p.b_in[k0 + (tid >> 1) + 128 * i];
+  }
   if (p.pdl) pdl_wait();
   if (tid < TAIL_T * TAIL_A) {
     const int t = tid >> 5;
@@ -94,7 +111,6 @@ __global__ void __launch_bounds__(TAIL_THREADS) action_tail_kernel(const TailPar
   }
   if (p.x) {
     // ---- final AdaRMS norm of this slice: 64 threads per token, KS/64 consecutive columns each
-    constexpr int PT = KS / 64;
     const int t = tid >> 6, c = (tid & 63) * PT;
     const bool live = m0 + t < p.M;
     float xv[PT];
@@ -113,9 +129,8 @@ __global__ void __launch_bounds__(TAIL_THREADS) action_tail_kernel(const TailPar
     float tot = 0.f;
     for (int r = 0; r < C; ++r) tot += tail_peer_f32(&sh.part_ss[t], r, clustered);  // rank order: reproducible
     const float rstd = rsqrtf(tot / static_cast<float>(p.W) + p.eps);
-    const float* mod = p.mod + static_cast<long long>(live ? (m0 + t) / p.rows_per_group : 0) * p.ldmod + k0 + c;
 #pragma unroll
-    for (int e = 0; e < PT; ++e) sh.xn[t][c + e] = live ? bf16_round(xv[e] * rstd * (1.0f + mod[e]) + mod[p.W + e]) : 0.f;
+    for (int e = 0; e < PT; ++e) sh.xn[t][c + e] = live ? bf16_round(xv[e] * rstd * (1.0f + msc[e]) + msh[e]) : 0.f;
     __syncthreads();
     // ---- out-projection partials: warp w owns outputs 4w..4w+3, lane covers 4 columns per 128
     float acc[4][TAIL_T];
@@ -148,7 +163,7 @@ __global__ void __launch_bounds__(TAIL_THREADS) action_tail_kernel(const TailPar
       const int tt = tid >> 5;
       float v = 0.f;
       for (int r = 0; r < C; ++r) v += tail_peer_f32(&sh.vp[tt][lane], r, clustered);
-      const float nx = sh.xt[tt][lane] + p.dt * (v + p.b_out[lane]);
+      const float nx = sh.xt[tt][lane] + p.dt * (v + bo);
       sh.xt[tt][lane] = nx;
       if (rank == 0 && m0 + tt < p.M) p.x_t[static_cast<long long>(m0 + tt) * TAIL_A + lane] = nx;
     }
@@ -171,7 +186,7 @@ __global__ void __launch_bounds__(TAIL_THREADS) action_tail_kernel(const TailPar
         }
         s[tt] += __shfl_xor_sync(0xffffffffu, s[tt], 1);
       }
-      const float bias = p.b_in[k0 + kl];
+      const float bias = bi[i];
 #pragma unroll
       for (int tt = 0; tt < TAIL_T / 2; ++tt) {  // each thread of the pair stores two of the four tokens
         const int tk = half * (TAIL_T / 2) + tt;
