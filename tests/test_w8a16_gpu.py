@@ -228,3 +228,52 @@ def test_geglu_packed_rejects_ragged_width():
     xp = torch.zeros(3, 4, 64, dtype=torch.uint8, device=dev)
     with pytest.raises(ValueError):
         ops.w8x3_geglu_packed(xp, 4, w, torch.ones(192, device=dev))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,n,k", [(544, 8192, 512), (300, 12800, 320), (1200, 2560, 256)])
+def test_multi_wave_launches_run_as_cta_pairs(m, n, k):
+    """Enough full-K tiles for two waves: the launch takes the CTA-pair form (one UMMA of 256
+    weight rows per two CTAs, each loading half of the activation planes).  Same tolerance as the
+    single-CTA form, bit-reproducible, and equal to a forced split-K launch up to summation order."""
+    ops = _ops()
+    x, w8, scale, _ = _case(41, m, n, k)
+    ref = w8_ref.w8_linear(x, w8, scale)
+    xp = ops.split3(x.cuda(), 4)
+    y0, _ = ops.w8x3_linear(xp, 4, w8.cuda(), scale.cuda())
+    y1, _ = ops.w8x3_linear(xp, 4, w8.cuda(), scale.cuda())
+    y2, _ = ops.w8x3_linear(xp, 4, w8.cuda(), scale.cuda(), splits=2)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert torch.equal(y0, y1)
+    assert w8_ref.rel_l2(y0.cpu(), ref) <= TOL
+    assert w8_ref.rel_l2(y0.cpu(), y2.cpu()) <= 2e-3
+
+
+@pytest.mark.gpu
+def test_cta_pair_form_with_paired_and_residual_epilogues():
+    """The CTA-pair launch under the packed gate/up epilogue (bit-equal to the two-matrix form,
+    which never pairs) and under the gated residual epilogue (against the oracle)."""
+    ops = _ops()
+    dev = torch.device("cuda")
+    gen = torch.Generator().manual_seed(43)
+    m, i, k = 544, 4096, 256
+    wg, wu = (torch.empty(i, k).normal_(0, 0.02, generator=gen) for _ in range(2))
+    x = torch.empty(m, k).normal_(0, 1, generator=gen).to(torch.bfloat16)
+    (g8, gs), (u8, us) = w8_ref.quantize_w8(wg), w8_ref.quantize_w8(wu)
+    g8, gs, u8, us = (t.to(dev) for t in (g8, gs, u8, us))
+    p8, ps = ops.pack_gate_up(g8, gs, u8, us)
+    xp = ops.split3(x.to(dev), 4)
+    h0, hp0 = ops.w8x3_geglu(xp, 4, g8, gs, u8, us, out_bf16=True, out_planes=True)
+    h1, hp1 = ops.w8x3_geglu_packed(xp, 4, p8, ps, out_bf16=True, out_planes=True)
+    assert torch.equal(h0, h1) and torch.equal(hp0, hp1)
+    # down-projection-like launch with residual and fp32 gate: 544 x 8192 x 256
+    w8, sc = w8_ref.quantize_w8(torch.empty(8192, k).normal_(0, 0.02, generator=gen))
+    res = torch.empty(m, 8192).normal_(0, 1, generator=gen).to(torch.bfloat16)
+    gate = torch.empty(1, 8192).normal_(0, 0.5, generator=gen)
+    ref = res + w8_ref.w8_linear(x, w8, sc) * gate.to(torch.bfloat16)
+    y, _ = ops.w8x3_linear(xp, 4, w8.to(dev), sc.to(dev), epilogue=ops.EPI_RESIDUAL, residual=res.to(dev),
+                           gate=gate.to(dev), rows_per_gate=m)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert w8_ref.rel_l2(y.cpu(), ref) <= TOL

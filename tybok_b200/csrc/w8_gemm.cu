@@ -81,6 +81,8 @@ struct GemmParams {
   int stage_off;  // byte offset of the epilogue staging tile: 0 (over the idle ring) without split-K,
                   // behind the ring with split-K, because peers write into it while this CTA still streams
   int merge;     // 1: the three planes are one UMMA of N = 3*bt whose column groups the epilogue adds
+  int pair;      // 1: CTA pairs (cluster of 2 along the channel tiles) run one UMMA of M = 256; each CTA
+                 // loads its own weight tile and half of the activation planes (tm_w1 = half-tile map)
   int epi;
   int pdl;
   float out_scale;   // 2^-x_shift: undoes the power-of-two pre-scale of the activation planes
@@ -127,6 +129,9 @@ __device__ __forceinline__ void fail(Barriers* b, int* status, int code) {
 
 // Bounded for two CTAs per SM: multi-wave full-K launches run with a shallow ring so that one
 // tile's epilogue overlaps the other's main loop (register budget 64K / 640 threads).
+// PAIR: the CTA-pair form (cta_group::2 instructions oblige every launch of a kernel that holds
+// them to use clusters of two, so it is an instantiation of its own).
+template <bool PAIR>
 __global__ void __launch_bounds__(THREADS, 2)
 w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1,
                const __grid_constant__ CUtensorMap tm_x, const GemmParams p) {
@@ -140,18 +145,20 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
   const int ns = p.nstages;
-  const int x_bytes = 3 * p.bt * 128;                 // three planes of bt rows x 128 bytes
+  const int x_bytes = PAIR ? 3 * p.bt * 64 : 3 * p.bt * 128;  // three planes of bt rows x 128 bytes (a pair: half each)
   const int x_off = p.nw * W_TILE_BYTES;              // activation planes follow the weight tile(s)
   const int stage_bytes = x_off + x_bytes;
 
-  const int t_tile = blockIdx.x, n_tile = blockIdx.y, split = blockIdx.z;
+  // A pair is two neighbouring channel tiles; pairs lie along x of the grid (and of the cluster).
+  const int t_tile = PAIR ? blockIdx.y : blockIdx.x, n_tile = PAIR ? blockIdx.x : blockIdx.y, split = blockIdx.z;
+  const uint32_t pair_rank = PAIR ? cluster_ctarank() : 0u;  // 0 issues the pair's UMMAs
   const int kb0 = split * p.kb_per_split;
   const int nkb = min(p.kb_total, kb0 + p.kb_per_split) - kb0;
 
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tm_w0);
-    if (p.nw == 2) tma_prefetch_desc(&tm_w1);
-    tma_prefetch_desc(&tm_x);
+    if (p.nw == 2 || PAIR) tma_prefetch_desc(&tm_w1);
+    if (!PAIR) tma_prefetch_desc(&tm_x);
     for (int i = 0; i < MAX_STAGES; ++i) {
       mbar_init(&bars.full[i], 1);
       mbar_init(&bars.empty[i], 1);
@@ -160,22 +167,35 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     bars.abort = 0;
     fence_barrier_init();
     // Weights depend on nothing that runs before this kernel: request the first stages now,
-    // before the rest of the CTA has even finished its set-up.
-    const int pre = min(ns, nkb);
-    for (int i = 0; i < pre; ++i) {
-      uint8_t* st = smem + i * stage_bytes;
-      mbar_arrive_expect_tx(&bars.full[i], stage_bytes);
-      const int k0 = (kb0 + i) * BK;
-      tma_load_2d(st, &tm_w0, &bars.full[i], k0, n_tile * BN);
-      if (p.nw == 2) tma_load_2d(st + W_TILE_BYTES, &tm_w1, &bars.full[i], k0, n_tile * BN);
+    // before the rest of the CTA has even finished its set-up.  (A pair first has to know that
+    // the partner's barriers exist: it requests them after the cluster has met.)
+    if (!PAIR) {
+      const int pre = min(ns, nkb);
+      for (int i = 0; i < pre; ++i) {
+        uint8_t* st = smem + i * stage_bytes;
+        mbar_arrive_expect_tx(&bars.full[i], stage_bytes);
+        const int k0 = (kb0 + i) * BK;
+        tma_load_2d(st, &tm_w0, &bars.full[i], k0, n_tile * BN);
+        if (p.nw == 2) tma_load_2d(st + W_TILE_BYTES, &tm_w1, &bars.full[i], k0, n_tile * BN);
+      }
     }
   }
   if (warp == 1) {
-    tmem_alloc(&bars.tmem_base, p.tmem_cols);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(&bars.tmem_base, p.tmem_cols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(&bars.tmem_base, p.tmem_cols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
-  __syncthreads();
+  if (PAIR) {
+    __syncwarp();
+    cluster_sync_all();
+  } else {
+    __syncthreads();
+  }
   tc_fence_after();
   const uint32_t tmem = bars.tmem_base;
   // Per-thread epilogue constants (4 consecutive channels), fetched while the main loop runs.
@@ -200,9 +220,42 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
       // Dependents may start their own preamble (their weight prefetch) as soon as every CTA of
       // this grid is running; they still wait for this grid to complete before touching its output.
       if (p.pdl) pdl_launch_dependents();
+      const int pre = min(ns, nkb);
+      if (PAIR) {
+        // CTA pair: both CTAs load their own weight tile and their half of the activation planes
+        // (three boxes of bt/2 token rows of one plane); every byte is credited to the full
+        // barrier of the even-ranked CTA, which issues the UMMAs for both.
+        const int hrows = p.bt >> 1;
+        auto pair_stage = [&](int i, bool weights, bool acts) {
+          uint8_t* st = smem + (i % ns) * stage_bytes;
+          const uint32_t bar = dsmem_addr(smem_u32(&bars.full[i % ns]), 0);
+          const int k0 = (kb0 + i) * BK;
+          if (weights) {
+            if (pair_rank == 0) mbar_arrive_expect_tx(&bars.full[i % ns], 2 * stage_bytes);
+            tma_load_2d_pair(st, &tm_w0, bar, k0, n_tile * BN);
+          }
+          if (acts) {
+            for (int j = 0; j < 3; ++j) {
+              const int u = static_cast<int>(pair_rank) * 3 + j;  // half-plane index 0..5
+              tma_load_3d_pair(st + x_off + j * hrows * 128, &tm_w1, bar, k0, t_tile * p.bt + (u & 1) * hrows, u >> 1);
+            }
+          }
+        };
+        for (int i = 0; i < pre; ++i) pair_stage(i, true, false);
+        if (p.pdl) pdl_wait();
+        for (int i = 0; i < pre; ++i) pair_stage(i, false, true);
+        for (int i = pre; i < nkb; ++i) {
+          if (!wait_or_abort(&bars.empty[i % ns], ((i / ns) & 1) ^ 1, &bars.abort)) {
+            fail(&bars, p.status, TYBOK_DEV_TIMEOUT_PRODUCER);
+            break;
+          }
+          pair_stage(i, true, true);
+        }
+        issued = 0;  // completion is observed through the issuing CTA's barriers only
+        ok = true;
+      } else {
       // The weight tiles of the first stages were requested during set-up; the activation planes
       // are requested once the programmatic dependency has resolved.
-      const int pre = min(ns, nkb);
       if (p.pdl) pdl_wait();
       for (int i = 0; i < pre; ++i)
         tma_load_3d(smem + i * stage_bytes + x_off, &tm_x, &bars.full[i], (kb0 + i) * BK, t_tile * p.bt, 0);
@@ -222,7 +275,8 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
         tma_load_3d(st + x_off, &tm_x, &bars.full[s], k0, t_tile * p.bt, 0);
         issued = i + 1;
       }
-      if (!ok || bars.abort) {
+      }
+      if (!PAIR && (!ok || bars.abort)) {
         // Unwinding: do not leave the CTA while its own bulk copies may still land in its
         // shared memory. Wait (bounded) for the newest copy of every stage.
         for (int i = max(0, issued - ns); i < issued; ++i) mbar_wait(&bars.full[i % ns], (i / ns) & 1);
@@ -236,12 +290,13 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     // with N = 3*bt multiplies a K slice by all of them (one column group per plane) -- 4
     // instead of 12 instructions per weight tile and K block.  Larger tiles issue one UMMA per
     // plane into the same accumulator.
-    const uint32_t idesc = idesc_e4m3_e5m2_f32(BN, p.merge ? 3 * p.bt : p.bt);
+    const uint32_t idesc = idesc_e4m3_e5m2_f32(PAIR ? 2 * BN : BN, p.merge ? 3 * p.bt : p.bt);
+    const int nkb_mma = (PAIR && pair_rank != 0) ? 0 : nkb;  // the odd CTA of a pair issues nothing
     const uint64_t desc_const = smem_desc_sw128(0);
     const uint32_t plane16 = static_cast<uint32_t>(p.bt * 128) >> 4;  // plane pitch in 16-byte units
     const int acc_cols = p.merge ? 3 * p.bt : p.bt;
     bool ok = true;
-    for (int i = 0; i < nkb; ++i) {
+    for (int i = 0; i < nkb_mma; ++i) {
       const int s = i % ns;
       const long long c0 = tr ? clock64() : 0;
       const bool ready = wait_or_abort(&bars.full[s], (i / ns) & 1, &bars.abort);
@@ -262,7 +317,10 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
           for (int j = 0; j < 4; ++j) {  // K = 32 per instruction: 32 bytes = 2 sixteen-byte units
             const uint64_t a_desc = desc_const | (w16 + j * 2);
             const uint64_t b_desc = desc_const | (x16 + j * 2);
-            if (leader) umma_ss_f8(d_addr, a_desc, b_desc, idesc, (i > 0 || j > 0) ? 1u : 0u);
+            if (leader) {
+              if (PAIR) umma_ss_f8_pair(d_addr, a_desc, b_desc, idesc, (i > 0 || j > 0) ? 1u : 0u);
+              else umma_ss_f8(d_addr, a_desc, b_desc, idesc, (i > 0 || j > 0) ? 1u : 0u);
+            }
           }
         } else {
 #pragma unroll
@@ -276,10 +334,16 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
           }
         }
       }
-      if (leader) tc_commit(&bars.empty[s]);  // frees the stage once these MMAs have read it
+      if (leader) {  // frees the stage (in both CTAs of a pair) once these MMAs have read it
+        if (PAIR) tc_commit_pair(&bars.empty[s], 3);
+        else tc_commit(&bars.empty[s]);
+      }
       __syncwarp();
     }
-    if (ok && leader) tc_commit(&bars.tmem_full);
+    if (ok && leader && nkb_mma > 0) {
+      if (PAIR) tc_commit_pair(&bars.tmem_full, 3);
+      else tc_commit(&bars.tmem_full);
+    }
     if (tr && leader) tr[3] = clock64();
   } else {
     // ------------------------------------------------------------ epilogue, phase A
@@ -557,10 +621,17 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
 
   if (tr && tid == 64) tr[7] = clock64();
   // After the meeting point nobody touches another CTA's shared memory: CTAs leave on their own.
-  __syncthreads();
+  if (PAIR) {  // tensor memory of a pair is released together, once both CTAs have read theirs
+    tc_fence_before();
+    __syncwarp();
+    cluster_sync_all();
+  } else {
+    __syncthreads();
+  }
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem, p.tmem_cols);
+    if (PAIR) tmem_dealloc_pair(tmem, p.tmem_cols);
+    else tmem_dealloc(tmem, p.tmem_cols);
   }
 }
 
@@ -594,7 +665,7 @@ __global__ void split3_kernel(const __nv_bfloat16* __restrict__ x, long long ldx
 
 // ------------------------------------------------------------------------------------ host
 struct Plan {
-  int bt, t_tiles, n_tiles, splits, kb_total, kb_per_split, nstages, smem_bytes, tmem_cols, merge, stage_off;
+  int bt, t_tiles, n_tiles, splits, kb_total, kb_per_split, nstages, smem_bytes, tmem_cols, merge, stage_off, pair;
 };
 
 static int round_up(int a, int b) { return (a + b - 1) / b * b; }
@@ -636,7 +707,13 @@ static bool make_plan(int M, int N, int K, int nw, int force_bt, int force_split
     if (tiles * 2 <= sms) splits = std::min(sms / tiles, std::max(1, pl.kb_total / 2));  // >= 2 K blocks per split
   }
   splits = std::max(1, std::min(std::min(splits, MAX_SPLITS), pl.kb_total));
-  const int stage_bytes = nw * W_TILE_BYTES + 3 * bt * 128;
+  // Multi-wave full-K launches run as CTA pairs (one UMMA of 256 weight rows per two CTAs): each
+  // CTA then loads half of the activation planes, a third less shared-memory fill per MMA and a
+  // third stage in the same shared memory (4146 x 3072 x 14336: 503 -> 409 us; 544 x 32768 x 2048:
+  // unchanged; single-wave launches lose a microsecond to the pair's set-up, so they stay single).
+  pl.pair = (splits == 1 && nw == 1 && 3 * bt <= 256 && pl.n_tiles % 2 == 0 &&
+             pl.t_tiles * pl.n_tiles >= 2 * host::sm_count()) ? 1 : 0;
+  const int stage_bytes = pl.pair ? W_TILE_BYTES + 3 * bt * 64 : nw * W_TILE_BYTES + 3 * bt * 128;
   for (;; --splits) {  // fewer splits if the split-K staging tile does not fit beside the ring
     pl.kb_per_split = (pl.kb_total + splits - 1) / splits;
     pl.splits = (pl.kb_total + pl.kb_per_split - 1) / pl.kb_per_split;  // no empty split
@@ -694,13 +771,17 @@ static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, co
   if (!make_plan(M, N, K, nw, force_bt, force_splits, pl))
     return host::fail(TYBOK_ERR_ARG, "w8 gemm: unsupported token tile (multiple of 16, <= 256, <= 128 when gated)");
   if (force_splits > MAX_SPLITS) return host::fail(TYBOK_ERR_ARG, "w8 gemm: at most 8 K splits (cluster size)");
-  if (pl.n_tiles > 65535) return host::fail(TYBOK_ERR_ARG, "w8 gemm: grid too large");
+  if ((pl.pair ? pl.t_tiles : pl.n_tiles) > 65535) return host::fail(TYBOK_ERR_ARG, "w8 gemm: grid too large");
 
   CUtensorMap tm_w0, tm_w1, tm_x;
   if (int rc = host::tensor_map_2d(&tm_w0, w0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, N, K, BK, BN)) return rc;
   tm_w1 = tm_w0;
   if (nw == 2)
     if (int rc = host::tensor_map_2d(&tm_w1, w1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, N, K, BK, BN)) return rc;
+  if (pl.pair)  // half-plane boxes of the activation planes: bt/2 token rows of one plane
+    if (int rc = host::tensor_map_3d(&tm_w1, planes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, M, 3, K,
+                                     static_cast<uint64_t>(M) * K, BK, pl.bt / 2, 1))
+      return rc;
   if (int rc = host::tensor_map_3d(&tm_x, planes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, M, 3, K,
                                    static_cast<uint64_t>(M) * K, BK, pl.bt, 3))
     return rc;
@@ -708,7 +789,7 @@ static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, co
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.n_out = n_out;
   p.bt = pl.bt; p.nw = nw; p.splits = pl.splits; p.kb_total = pl.kb_total; p.kb_per_split = pl.kb_per_split;
-  p.nstages = pl.nstages; p.tmem_cols = pl.tmem_cols; p.merge = pl.merge; p.stage_off = pl.stage_off; p.epi = epi; p.pdl = host::pdl_enabled() ? 1 : 0;
+  p.nstages = pl.nstages; p.tmem_cols = pl.tmem_cols; p.merge = pl.merge; p.pair = pl.pair; p.stage_off = pl.stage_off; p.epi = epi; p.pdl = host::pdl_enabled() ? 1 : 0;
   p.out_scale = ldexpf(1.0f, -x_shift);
   p.plane_scale = ldexpf(1.0f, out_shift);
   p.scale0 = s0; p.scale1 = s1; p.bias0 = static_cast<const __nv_bfloat16*>(bias);
@@ -722,13 +803,14 @@ static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, co
   static bool attr_set[64] = {};
   const int dev = host::current_device();
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(w8_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DYN_SMEM_MAX) != cudaSuccess)
+    if (cudaFuncSetAttribute(w8_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DYN_SMEM_MAX) != cudaSuccess ||
+        cudaFuncSetAttribute(w8_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DYN_SMEM_MAX) != cudaSuccess)
       return host::fail_cuda("cudaFuncSetAttribute(w8_gemm_kernel)");
     attr_set[dev] = true;
   }
 
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(pl.t_tiles, pl.n_tiles, pl.splits);
+  cfg.gridDim = pl.pair ? dim3(pl.n_tiles, pl.t_tiles, 1) : dim3(pl.t_tiles, pl.n_tiles, pl.splits);
   cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = pl.smem_bytes;
   cfg.stream = stream;
@@ -739,16 +821,17 @@ static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, co
     attr[na].val.programmaticStreamSerializationAllowed = 1;
     ++na;
   }
-  if (pl.splits > 1) {
+  if (pl.splits > 1 || pl.pair) {
     attr[na].id = cudaLaunchAttributeClusterDimension;
-    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.x = pl.pair ? 2 : 1;
     attr[na].val.clusterDim.y = 1;
-    attr[na].val.clusterDim.z = pl.splits;
+    attr[na].val.clusterDim.z = pl.pair ? 1 : pl.splits;
     ++na;
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  if (cudaLaunchKernelEx(&cfg, w8_gemm_kernel, tm_w0, tm_w1, tm_x, p) != cudaSuccess)
+  if ((pl.pair ? cudaLaunchKernelEx(&cfg, w8_gemm_kernel<true>, tm_w0, tm_w1, tm_x, p)
+               : cudaLaunchKernelEx(&cfg, w8_gemm_kernel<false>, tm_w0, tm_w1, tm_x, p)) != cudaSuccess)
     return host::fail_cuda("launch w8_gemm_kernel");
   host::count_launch();
   return TYBOK_OK;
