@@ -103,13 +103,6 @@ __device__ __forceinline__ uint64_t policy_evict_last() {
 
 
 // 3-D tiled load (crd0 innermost).
-// Bring a tile into L2 without touching shared memory (the copy that follows then pays the L2,
-// not the HBM, round trip).
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* m, int crd0, int crd1) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(m)),
-               "r"(crd0), "r"(crd1)
-               : "memory");
-}
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* m, uint64_t* bar, int crd0, int crd1,
                                             int crd2) {
   asm volatile(

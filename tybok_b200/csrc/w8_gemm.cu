@@ -49,7 +49,6 @@ constexpr int MAX_STAGES = 8;
 constexpr int EPI_WARPS = 8;
 constexpr int THREADS = 32 * (2 + EPI_WARPS);
 constexpr int DYN_SMEM_MAX = 226 * 1024;  // 227 KB per CTA minus 1 KB left for static shared memory
-constexpr int L2_AHEAD = 6;  // K blocks of weights requested into L2 ahead of the shared-memory ring
 constexpr int CORESIDENT_SMEM = 112 * 1024;  // dynamic shared memory of a CTA when two share an SM (228 KB)
 constexpr int MAX_SPLITS = 8;             // portable cluster size
 
@@ -179,12 +178,6 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
         tma_load_2d(st, &tm_w0, &bars.full[i], k0, n_tile * BN);
         if (p.nw == 2) tma_load_2d(st + W_TILE_BYTES, &tm_w1, &bars.full[i], k0, n_tile * BN);
       }
-      // ... and the weight tiles behind them into L2: the ring is too short to cover the HBM
-      // round trip of a long K loop, L2 is not.
-      for (int i = pre; i < min(nkb, pre + L2_AHEAD); ++i) {
-        tma_prefetch_2d(&tm_w0, (kb0 + i) * BK, n_tile * BN);
-        if (p.nw == 2) tma_prefetch_2d(&tm_w1, (kb0 + i) * BK, n_tile * BN);
-      }
     }
   }
   if (warp == 1) {
@@ -249,7 +242,6 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
           }
         };
         for (int i = 0; i < pre; ++i) pair_stage(i, true, false);
-        for (int i = pre; i < min(nkb, pre + L2_AHEAD); ++i) tma_prefetch_2d(&tm_w0, (kb0 + i) * BK, n_tile * BN);
         if (p.pdl) pdl_wait();
         for (int i = 0; i < pre; ++i) pair_stage(i, false, true);
         for (int i = pre; i < nkb; ++i) {
@@ -258,7 +250,6 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
             break;
           }
           pair_stage(i, true, true);
-          if (i + L2_AHEAD < nkb) tma_prefetch_2d(&tm_w0, (kb0 + i + L2_AHEAD) * BK, n_tile * BN);
         }
         issued = 0;  // completion is observed through the issuing CTA's barriers only
         ok = true;
@@ -283,10 +274,6 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
         if (p.nw == 2) tma_load_2d(st + W_TILE_BYTES, &tm_w1, &bars.full[s], k0, n_tile * BN);
         tma_load_3d(st + x_off, &tm_x, &bars.full[s], k0, t_tile * p.bt, 0);
         issued = i + 1;
-        if (i + L2_AHEAD < nkb) {
-          tma_prefetch_2d(&tm_w0, (kb0 + i + L2_AHEAD) * BK, n_tile * BN);
-          if (p.nw == 2) tma_prefetch_2d(&tm_w1, (kb0 + i + L2_AHEAD) * BK, n_tile * BN);
-        }
       }
       }
       if (!PAIR && (!ok || bars.abort)) {
