@@ -231,13 +231,15 @@ class PI05B200Engine(PolicyEngine):
                 img = fr.get(key)
                 present.append(img is not None)
                 if img is None:  # missing camera: all(-1) image, mask 0 (policy.py:222-228)
-                    per.append(torch.full((3, res, res), -1.0))
+                    per.append(torch.full((3, res, res), -1.0, device=self.device))
                     continue
-                img = torch.as_tensor(img).float()
+                # upload the frame as it is (one copy, asynchronous from pinned memory); resize and
+                # rescale on the device
+                img = torch.as_tensor(img).to(self.device, non_blocking=True).float()
                 if img.shape[-2:] != (res, res):
                     img = F.interpolate(img[None], size=(res, res), mode="bilinear", align_corners=False)[0].clamp(0, 1)
                 per.append(img * 2.0 - 1.0)
-            images.append(torch.stack(per).to(self.device, non_blocking=True))
+            images.append(torch.stack(per) if len(per) > 1 else per[0][None])
             img_masks.append(torch.tensor(present, dtype=torch.bool, device=self.device))
         toks = [self._tokens(fr) for fr in frames]
         tokens = torch.stack([t for t, _ in toks]).to(self.device)
