@@ -670,6 +670,35 @@ struct Plan {
 
 static int round_up(int a, int b) { return (a + b - 1) / b * b; }
 
+// How many clusters of `splits` CTAs of the GEMM kernel the device runs at once (a cluster lives
+// inside one GPC, so this is less than SMs / splits: 15 clusters of 8 on a B200).  A launch with
+// more clusters than that runs its last ones as a second wave.
+static int max_active_clusters(int splits) {
+  static int cached[MAX_SPLITS + 1] = {};
+  if (splits <= 1) return 1 << 30;
+  if (cached[splits] == 0) {
+    cudaFuncSetAttribute(w8_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DYN_SMEM_MAX);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(1, 1, splits);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = DYN_SMEM_MAX;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = splits;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, w8_gemm_kernel<false>, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = host::sm_count() / (2 * splits);  // conservative guess
+    }
+    cached[splits] = std::max(1, n);
+  }
+  return cached[splits];
+}
+
 static bool make_plan(int M, int N, int K, int nw, int force_bt, int force_splits, Plan& pl) {
   const int max_bt = nw == 2 ? 128 : 256;
   int bt;
@@ -705,6 +734,9 @@ static bool make_plan(int M, int N, int K, int nw, int force_bt, int force_split
     const int tiles = pl.t_tiles * pl.n_tiles;
     splits = 1;
     if (tiles * 2 <= sms) splits = std::min(sms / tiles, std::max(1, pl.kb_total / 2));  // >= 2 K blocks per split
+    splits = std::max(1, std::min(std::min(splits, MAX_SPLITS), pl.kb_total));
+    // every cluster must be resident at once (2048 x 16384, 16 tiles: 8 splits 17 us, 6 splits 11 us)
+    while (splits > 1 && tiles > max_active_clusters(splits)) --splits;
   }
   splits = std::max(1, std::min(std::min(splits, MAX_SPLITS), pl.kb_total));
   // Multi-wave full-K launches run as CTA pairs (one UMMA of 256 weight rows per two CTAs): each
