@@ -208,3 +208,23 @@ def test_action_tail_matches_torch(m, w):
     none = ops.action_tail(x.cuda(), mod.cuda(), w_out.cuda(), b_out.cuda(), xt2, dt, w_in.cuda(), b_in.cuda(),
                            rows_per_group=m, embed=False)
     assert none.numel() == 0 and torch.equal(xt2, xt)
+
+
+@pytest.mark.parametrize("graph", [False, True])
+def test_first_step_overlapped_with_prefix_gives_the_same_chunk(graph):
+    """The first denoise step pipelined behind the prefix on a second stream (eager, and captured
+    into one CUDA graph) returns bit for bit what the sequential order returns."""
+    from tybok_b200.engine import PI05B200Engine
+
+    seq = PI05B200Engine("synthetic:pi05_small", device="cuda", graph=graph, seed=0, overlap=False)
+    ovl = PI05B200Engine("synthetic:pi05_small", device="cuda", graph=graph, seed=0, overlap=True)
+    assert ovl.model.overlap and not seq.model.overlap
+    g = torch.Generator().manual_seed(3)
+    for i in range(3):
+        frame = {f"observation.images.camera{c + 1}": torch.rand(3, 70, 70, generator=g) for c in range(2)}
+        frame["observation.state"] = torch.randn(8, generator=g)
+        frame["task"] = f"pick up the cube {i}"
+        noise = torch.randn(1, 10, 32, generator=g)
+        a = seq.predict_action_chunk(frame, noise=noise)
+        b = ovl.predict_action_chunk(frame, noise=noise)
+        assert (a == b).all()

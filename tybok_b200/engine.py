@@ -27,12 +27,12 @@ import torch.nn.functional as F  # noqa: N812
 
 from .base import PolicyEngine, register, reject_unsupported_flags
 from .pi05 import PI05Model
-from .shapes import GEMMA_2B, GEMMA_300M, PI05_FULL, PI05_TINY, GemmaSpec, PI05Shape, SiglipSpec
+from .shapes import GEMMA_2B, GEMMA_300M, PI05_FULL, PI05_SMALL, PI05_TINY, GemmaSpec, PI05Shape, SiglipSpec
 from .weights import random_pi05_params
 
 log = logging.getLogger("tybok.pi05_b200")
 
-SYNTHETIC = {"pi05_full": PI05_FULL, "pi05_tiny": PI05_TINY}
+SYNTHETIC = {"pi05_full": PI05_FULL, "pi05_tiny": PI05_TINY, "pi05_small": PI05_SMALL}
 _VARIANTS = {"gemma_2b": GEMMA_2B, "gemma_300m": GEMMA_300M}
 
 
@@ -120,7 +120,7 @@ class PI05B200Engine(PolicyEngine):
         if not str(self.device).startswith("cuda"):
             raise RuntimeError("pi05_b200 needs a CUDA sm_100 device: there is no CPU fallback")
         # *_fused_split (cooperative vs split launches in the reference) has no meaning here.
-        del action_fused_split, video_fused_split, overlap
+        del action_fused_split, video_fused_split
         self.compile_model = False
         self.camera_alias = dict(camera_alias or {})
         self.batch_size = int(batch_size)
@@ -137,7 +137,9 @@ class PI05B200Engine(PolicyEngine):
             shape = shape.with_(steps=int(num_steps))
         self.config = EngineConfig(shape=shape, cameras=cams, num_steps=shape.steps, chunk_size=shape.chunk,
                                    n_action_steps=shape.chunk, action_dim=action_dim)
-        self.model = PI05Model(params, shape, device=str(self.device))
+        # overlap: the first denoise step runs layer by layer behind the prefix (the reference's
+        # --overlap, tybok/policies/pi05/models/flow_matching.py:609-720)
+        self.model = PI05Model(params, shape, device=str(self.device), overlap=overlap)
         del params
         self._gen = torch.Generator(device=self.device)
         if seed is not None:

@@ -109,10 +109,14 @@ class PI05Model:
     """Weights + forward of a pi0.5-shaped policy on one GPU (inference only)."""
 
     def __init__(self, params: dict[str, torch.Tensor], shape: PI05Shape, device: str = "cuda",
-                 vision_dtype: torch.dtype = torch.bfloat16):
+                 vision_dtype: torch.dtype = torch.bfloat16, overlap: bool = False):
         if not str(device).startswith("cuda"):
             raise RuntimeError("tybok_b200 has no CPU path: PI05Model needs a CUDA (sm_100) device")
         self.shape = shape
+        #: run the first denoise step layer by layer behind the prefix, on a second stream
+        #: (flow_matching.py:609-720: expert layer l only needs the prefix keys of layer l)
+        self.overlap = bool(overlap)
+        self._side = None
         self.device = torch.device(device)
         dev = self.device
         self.vision_dtype = vision_dtype
@@ -327,7 +331,7 @@ class PI05Model:
         return x
 
     # ------------------------------------------------------------------ prefix + denoise
-    def prefill(self, prefix_embs: torch.Tensor, pad: torch.Tensor):
+    def prefill(self, prefix_embs: torch.Tensor, pad: torch.Tensor, layer_done=None):
         """VLM prefix pass filling the per-layer post-RoPE (K, V) caches (gemma.py:61-125,
         use_cache); returns views ``[B, G, Lp, D]`` of the prefix part of every layer's cache."""
         spec = self.shape.vlm
@@ -339,6 +343,8 @@ class PI05Model:
         x = prefix_embs.reshape(b * l, w)
         for lay, cache in zip(self.vlm_layers, caches):
             x = self._layer(spec, lay, x, b, l, pos, mask, cache, 0, key_valid, None)
+            if layer_done is not None:
+                layer_done()
         return [(kc[:, :, :l], vc[:, :, :l]) for kc, vc in caches]
 
     def denoise_step(self, step: int, x_t: torch.Tensor, pad: torch.Tensor, kv=None) -> torch.Tensor:
@@ -374,24 +380,78 @@ class PI05Model:
         """Prefix prefill + ``steps`` forward-Euler updates from ``noise`` (flow_matching.py:761-838)."""
         s = self.shape
         embs, pad = self.embed_prefix(images, img_masks, tokens, masks)
-        self.prefill(embs, pad)
         dt = -1.0 / s.steps
         b, l = noise.shape[0], noise.shape[1]
-        if not (s.max_action_dim == 32 and l == s.chunk and s.expert.width in (128, 256, 512, 1024, 2048)):
+        fused_tail = s.max_action_dim == 32 and l == s.chunk and s.expert.width in (128, 256, 512, 1024, 2048)
+        if fused_tail and self.overlap:
+            return self._sample_actions_overlapped(embs, pad, noise, dt)
+        self.prefill(embs, pad)
+        if not fused_tail:
             x_t = noise
             for step in range(s.steps):
                 x_t = x_t + dt * self.denoise_step(step, x_t, pad)
             return x_t
         # Fused tail: one launch per step does final norm + out-projection + Euler update + the
         # next step's suffix embedding; masks and positions are built once per chunk.
+        key_valid, pos, mask = self._suffix_constants(pad, b, l)
+        x_t = noise.float().contiguous().clone()
+        h = ops.action_tail(None, None, None, None, x_t, dt, *self.action_in)
+        for step in range(s.steps):
+            x = self._expert_layers(step, h, b, l, pad, key_valid, pos, mask)
+            h = ops.action_tail(x, self.final_mods[step], *self.action_out, x_t, dt, *self.action_in,
+                                rows_per_group=b * l, embed=step + 1 < s.steps)
+        return x_t
+
+    def _suffix_constants(self, pad: torch.Tensor, b: int, l: int):
         lp = pad.shape[1]
         allowed = torch.cat([pad, torch.ones(b, l, dtype=torch.bool, device=pad.device)], dim=1)
         mask = None if self.fused_attention else _additive(allowed[:, None, None, :].expand(b, 1, l, lp + l))
         key_valid = allowed.to(torch.uint8).contiguous()
         pos = (pad.sum(dim=-1, keepdim=True) + torch.arange(l, device=pad.device)[None, :]).to(torch.int32).reshape(-1)
+        return key_valid, pos, mask
+
+    def _sample_actions_overlapped(self, embs, pad, noise, dt):
+        """``sample_actions`` with the first denoise step pipelined behind the prefix: expert layer
+        l of step 0 starts as soon as prefix layer l has written its keys and values, on a second
+        stream (captured into the same CUDA graph as a fork / join).  Same kernels, same
+        arithmetic; the first of the ten expert passes hides inside the prefix window."""
+        s = self.shape
+        b, l = noise.shape[0], noise.shape[1]
+        lp = pad.shape[1]
+        main = torch.cuda.current_stream(self.device)
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=self.device)
+        side = self._side
+        key_valid, pos, mask = self._suffix_constants(pad, b, l)
         x_t = noise.float().contiguous().clone()
-        h = ops.action_tail(None, None, None, None, x_t, dt, *self.action_in)
-        for step in range(s.steps):
+        caches = self._caches(b)
+        fork = torch.cuda.Event()
+        fork.record(main)
+        with torch.cuda.stream(side):
+            side.wait_event(fork)
+            h = ops.action_tail(None, None, None, None, x_t, dt, *self.action_in)
+        done = []
+
+        def layer_done():
+            ev = torch.cuda.Event()
+            ev.record(main)
+            done.append(ev)
+
+        self.prefill(embs, pad, layer_done)
+        with torch.cuda.stream(side):
+            x = h
+            for i, lay in enumerate(self.exp_layers):
+                side.wait_event(done[i])
+                x = self._layer(s.expert, lay, x, b, l, pos, mask, caches[i], lp, key_valid, self.mods[0][i])
+            h = ops.action_tail(x, self.final_mods[0], *self.action_out, x_t, dt, *self.action_in,
+                                rows_per_group=b * l, embed=s.steps > 1)
+            join = torch.cuda.Event()
+            join.record(side)
+        main.wait_event(join)
+        for t in (h, x_t, key_valid, pos):  # used on both streams: keep the allocator from recycling them early
+            t.record_stream(main)
+            t.record_stream(side)
+        for step in range(1, s.steps):
             x = self._expert_layers(step, h, b, l, pad, key_valid, pos, mask)
             h = ops.action_tail(x, self.final_mods[step], *self.action_out, x_t, dt, *self.action_in,
                                 rows_per_group=b * l, embed=step + 1 < s.steps)
