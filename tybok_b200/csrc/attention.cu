@@ -195,16 +195,18 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     tmem_alloc(&bars.tmem_base, 512);
     tmem_relinquish();
   }
-  if (warp == 2) {  // validity bits of this block's keys
-    uint32_t bits = 0;
+  if (warp == 2) {  // validity bits of this block's keys: the four loads in flight together
+    bool ok[4];
+    if (p.key_valid && p.pdl) pdl_wait();
+#pragma unroll
     for (int w = 0; w < 4; ++w) {
       const int j = key0 + w * 32 + lane;
-      bool ok = j < p.Lk;
-      if (ok && p.key_valid) {
-        if (p.pdl) pdl_wait();
-        ok = p.key_valid[static_cast<long long>(b) * p.Lk + j] != 0;
-      }
-      bits = __ballot_sync(0xffffffffu, ok);
+      ok[w] = j < p.Lk;
+      if (ok[w] && p.key_valid) ok[w] = p.key_valid[static_cast<long long>(b) * p.Lk + j] != 0;
+    }
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const uint32_t bits = __ballot_sync(0xffffffffu, ok[w]);
       if (lane == 0) bars.valid[w] = bits;
     }
   }
