@@ -117,6 +117,7 @@ struct AttnParams {
   int* status;
   int pdl;
   uint8_t* ws;       // [CTA][AT_WS_PER_CTA] exchange workspace (nsplit > 1)
+  int q_rows;        // query rows per bulk copy: 128, or 64 when all real rows fit (the rest of the tile is never read back)
   int dsplit;        // 1, or 2: two CTAs per (query tile, key block), each producing half of the output columns
   long long* trace;  // tuning aid: [CTA][16] SM-clock samples, NULL in production
 };
@@ -226,7 +227,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (p.pdl) pdl_wait();
       const int qrow = b * p.L + qt * AT_BQ;
       const int krow = (b * p.G + g) * p.Lcap + key0;
-      mbar_arrive_expect_tx(&bars.qk_full, 2 * AT_TILE);
+      mbar_arrive_expect_tx(&bars.qk_full, AT_TILE + 4 * p.q_rows * 128);
       for (int c = 0; c < 4; ++c) tma_load_2d(sq + c * AT_CHUNK, &tm_q, &bars.qk_full, h * AT_D + c * 64, qrow);
       for (int c = 0; c < 4; ++c) tma_load_2d(sk + c * AT_CHUNK, &tm_k, &bars.qk_full, c * 64, krow);
       const int nvc = dv / 64;  // 64-column chunks of V this CTA multiplies
@@ -563,7 +564,8 @@ int tybok_attention(const void* q, const void* k_cache, const void* v_cache, con
 
   CUtensorMap tm_q, tm_k, tm_v;
   const uint64_t hd = static_cast<uint64_t>(H) * D;
-  if (int rc = host::tensor_map_2d(&tm_q, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, hd, static_cast<uint64_t>(B) * L, hd * 2, 64, AT_BQ))
+  const int q_rows = L <= 64 ? 64 : AT_BQ;  // short suffixes: half the query tile is enough
+  if (int rc = host::tensor_map_2d(&tm_q, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, hd, static_cast<uint64_t>(B) * L, hd * 2, 64, q_rows))
     return rc;
   const uint64_t krows = static_cast<uint64_t>(B) * G * Lcap;
   if (int rc = host::tensor_map_2d(&tm_k, k_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, krows, D * 2, 64, AT_BK)) return rc;
@@ -579,6 +581,7 @@ int tybok_attention(const void* q, const void* k_cache, const void* v_cache, con
   p.status = status_word;
   p.pdl = host::pdl_enabled() ? 1 : 0;
   p.ws = static_cast<uint8_t*>(workspace);
+  p.q_rows = q_rows;
   const int n_qt = (L + AT_BQ - 1) / AT_BQ;
   p.dsplit = (nsplit > 1 && 2 * nsplit * H * n_qt * B <= host::sm_count()) ? 2 : 1;
   p.trace = host::trace_buffer();
