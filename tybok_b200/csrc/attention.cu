@@ -285,10 +285,22 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       tmem_ld32(t_s + lane_addr + (hf * 2 + 1) * 32, v1);
       tc_wait_ld();
       const uint32_t b0 = bars.valid[hf * 2], b1 = bars.valid[hf * 2 + 1];
+      // per 32-key chunk: all valid -> no per-element selects; none valid -> nothing to do
+      if (b0 == 0xffffffffu) {
 #pragma unroll
-      for (int e = 0; e < 32; ++e) {
-        if ((b0 >> e) & 1u) mx = fmaxf(mx, __uint_as_float(v0[e]));
-        if ((b1 >> e) & 1u) mx = fmaxf(mx, __uint_as_float(v1[e]));
+        for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v0[e]));
+      } else if (b0 != 0u) {
+#pragma unroll
+        for (int e = 0; e < 32; ++e)
+          if ((b0 >> e) & 1u) mx = fmaxf(mx, __uint_as_float(v0[e]));
+      }
+      if (b1 == 0xffffffffu) {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v1[e]));
+      } else if (b1 != 0u) {
+#pragma unroll
+        for (int e = 0; e < 32; ++e)
+          if ((b1 >> e) & 1u) mx = fmaxf(mx, __uint_as_float(v1[e]));
       }
     }
     bars.hmax[hf][row] = mx;
@@ -300,14 +312,28 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       for (int c = 0; c < 2; ++c) {
         const uint32_t bits = bars.valid[hf * 2 + c];
         uint32_t pk[16];
+        if (bits == 0xffffffffu) {
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          const float s0 = __uint_as_float(c == 0 ? v0[e] : v1[e]), s1 = __uint_as_float(c == 0 ? v0[e + 1] : v1[e + 1]);
-          const float p0 = ((bits >> e) & 1u) ? exp2f(s0 * p.scale_log2e - m2) : 0.f;
-          const float p1 = ((bits >> (e + 1)) & 1u) ? exp2f(s1 * p.scale_log2e - m2) : 0.f;
-          sum += p0 + p1;
-          const __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
-          pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&pp);
+          for (int e = 0; e < 32; e += 2) {
+            const float s0 = __uint_as_float(c == 0 ? v0[e] : v1[e]), s1 = __uint_as_float(c == 0 ? v0[e + 1] : v1[e + 1]);
+            const float p0 = exp2f(s0 * p.scale_log2e - m2), p1 = exp2f(s1 * p.scale_log2e - m2);
+            sum += p0 + p1;
+            const __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
+            pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&pp);
+          }
+        } else if (bits == 0u) {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) pk[e] = 0u;
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const float s0 = __uint_as_float(c == 0 ? v0[e] : v1[e]), s1 = __uint_as_float(c == 0 ? v0[e + 1] : v1[e + 1]);
+            const float p0 = ((bits >> e) & 1u) ? exp2f(s0 * p.scale_log2e - m2) : 0.f;
+            const float p1 = ((bits >> (e + 1)) & 1u) ? exp2f(s1 * p.scale_log2e - m2) : 0.f;
+            sum += p0 + p1;
+            const __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
+            pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&pp);
+          }
         }
         tmem_st16(t_p + lane_addr + (hf * 2 + c) * 16, pk);
       }
