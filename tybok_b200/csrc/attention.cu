@@ -123,7 +123,8 @@ struct AttnParams {
 };
 
 struct __align__(8) AttnBars {
-  uint64_t qk_full, v_full, s_full, p_full, o_full;
+  uint64_t qk_full[4];  // one per 64-column chunk of Q and K: S = Q K^T starts when the first pair has landed
+  uint64_t v_full, s_full, p_full, o_full;
   uint32_t tmem_base;
   volatile int abort;
   uint32_t valid[4];     // key-validity bits of this CTA's 128 keys
@@ -184,7 +185,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
-    mbar_init(&bars.qk_full, 1);
+    for (int c = 0; c < 4; ++c) mbar_init(&bars.qk_full[c], 1);
     mbar_init(&bars.v_full, 1);
     mbar_init(&bars.s_full, 1);
     mbar_init(&bars.p_full, 8);
@@ -227,9 +228,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (p.pdl) pdl_wait();
       const int qrow = b * p.L + qt * AT_BQ;
       const int krow = (b * p.G + g) * p.Lcap + key0;
-      mbar_arrive_expect_tx(&bars.qk_full, AT_TILE + 4 * p.q_rows * 128);
-      for (int c = 0; c < 4; ++c) tma_load_2d(sq + c * AT_CHUNK, &tm_q, &bars.qk_full, h * AT_D + c * 64, qrow);
-      for (int c = 0; c < 4; ++c) tma_load_2d(sk + c * AT_CHUNK, &tm_k, &bars.qk_full, c * 64, krow);
+      for (int c = 0; c < 4; ++c) {
+        mbar_arrive_expect_tx(&bars.qk_full[c], AT_CHUNK + p.q_rows * 128);
+        tma_load_2d(sq + c * AT_CHUNK, &tm_q, &bars.qk_full[c], h * AT_D + c * 64, qrow);
+        tma_load_2d(sk + c * AT_CHUNK, &tm_k, &bars.qk_full[c], c * 64, krow);
+      }
       const int nvc = dv / 64;  // 64-column chunks of V this CTA multiplies
       mbar_arrive_expect_tx(&bars.v_full, nvc * AT_CHUNK);
       for (int c = 0; c < nvc; ++c) tma_load_2d(sv + c * AT_CHUNK, &tm_v, &bars.v_full, dh * dv + c * 64, krow);
@@ -237,16 +240,21 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   } else if (warp == 1) {
     const bool leader = elect_one();
     const uint64_t dk = smem_desc_sw128(0);
-    bool ok = __all_sync(0xffffffffu, at_wait(&bars.qk_full, 0, &bars.abort));
-    if (ok) {
-      tc_fence_after();
+    bool ok = true;
+    {
       const uint32_t idesc_s = idesc_bf16_f32(AT_BQ, AT_BK);
       const uint32_t q16 = (smem_u32(sq) & 0x3FFFFu) >> 4, k16 = (smem_u32(sk) & 0x3FFFFu) >> 4;
 #pragma unroll
       for (int ks = 0; ks < 16; ++ks) {  // D = 256 in steps of 16: chunk ks/4, 32 bytes per step
+        if ((ks & 3) == 0 && ok) {
+          ok = __all_sync(0xffffffffu, at_wait(&bars.qk_full[ks >> 2], 0, &bars.abort));
+          tc_fence_after();
+        }
         const uint32_t off = (ks >> 2) * (AT_CHUNK >> 4) + (ks & 3) * 2;
-        if (leader) umma_ss_bf16(t_s, dk | (q16 + off), dk | (k16 + off), idesc_s, ks > 0 ? 1u : 0u);
+        if (ok && leader) umma_ss_bf16(t_s, dk | (q16 + off), dk | (k16 + off), idesc_s, ks > 0 ? 1u : 0u);
       }
+    }
+    if (ok) {
       if (leader) tc_commit(&bars.s_full);
       __syncwarp();
       ok = __all_sync(0xffffffffu, at_wait(&bars.v_full, 0, &bars.abort) && at_wait(&bars.p_full, 0, &bars.abort));
