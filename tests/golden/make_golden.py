@@ -1,8 +1,8 @@
 """Generate the golden fixtures in this directory by running the REFERENCE's own modules.
 
-Run where the reference checkout is importable (``TYBOK_REFERENCE`` or ``/root/reference``):
+Run where the reference checkout is importable, with ``TYBOK_REFERENCE`` naming its root:
 
-    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py
+    TYBOK_REFERENCE=<reference checkout> PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py
 
 Inputs and weights are seeded (``tybok_b200.weights`` + the generators below), so the
 fixtures hold only outputs plus an fp64 checksum of the inputs they belong to.  The
@@ -25,7 +25,8 @@ from torch import nn
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
-sys.path.insert(0, os.environ.get("TYBOK_REFERENCE", "/root/reference"))
+if "TYBOK_REFERENCE" in os.environ:  # only needed by main(); the seeded input generators import without it
+    sys.path.insert(0, os.environ["TYBOK_REFERENCE"])
 sys.dont_write_bytecode = True
 
 from tybok_b200.shapes import PI05_TINY  # noqa: E402
