@@ -30,7 +30,9 @@ def _reference(qkv, b, l, h, g, pos, prefix_k, prefix_v, key_valid):
 
 
 @pytest.mark.parametrize("b,l,lp,h,g", [(1, 50, 544, 8, 1), (2, 50, 300, 8, 1), (1, 544, 0, 8, 1), (2, 130, 0, 4, 2),
-                                        (1, 10, 968, 8, 1), (1, 7, 5, 2, 2)])
+                                        (1, 10, 968, 8, 1), (1, 7, 5, 2, 2),
+                                        # grids beyond one wave: each CTA works through several key blocks
+                                        (2, 544, 0, 8, 1), (2, 300, 400, 8, 1), (4, 130, 300, 8, 1), (1, 544, 480, 8, 1)])
 def test_attention_matches_oracle(b, l, lp, h, g):
     from tybok_b200 import ops
 

@@ -42,6 +42,11 @@ constexpr int AT_WS_PER_CTA = AT_BQ * AT_D * 4 + AT_BQ * 8;  // workspace per CT
 constexpr int AT_MAX_SPLITS = 8;
 constexpr int AT_MERGE_BATCH = 3;  // query rows a merging thread has in flight
 constexpr int AT_SMEM = 3 * AT_TILE + 1024;
+// Push form: the receive area is the half of the V tile that the split-column form leaves idle;
+// partial rows of 128 fp32 first, then 16 bytes of statistics per row.
+constexpr int AT_PUSH_RECV = 2 * AT_CHUNK;    // offset inside the V tile
+constexpr int AT_PUSH_STATS = 28 * 1024;      // offset of the statistics inside the receive area
+constexpr int AT_PUSH_MAX_ROWS = 56;          // nsplit * rows per rank: 56 * 512 B = 28 KB, 56 * 16 B < 4 KB
 
 struct RopeParams {
   const __nv_bfloat16* qkv;
@@ -122,9 +127,11 @@ struct AttnParams {
   long long* trace;  // tuning aid: [CTA][16] SM-clock samples, NULL in production
 };
 
-struct __align__(8) AttnBars {
+struct __align__(16) AttnBars {
+  float4 stat[AT_BQ];    // push form: (max, sum of keys 0..63, sum of keys 64..127, -) of every query row of this block
   uint64_t qk_full[4];  // one per 64-column chunk of Q and K: S = Q K^T starts when the first pair has landed
   uint64_t v_full, s_full, p_full, o_full;
+  uint64_t recv;         // push form: the peers' partial rows of the query rows this CTA merges have arrived
   uint32_t tmem_base;
   volatile int abort;
   uint32_t valid[4];     // key-validity bits of this CTA's 128 keys
@@ -158,6 +165,11 @@ __device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t smem_addr, uint3
   return d;
 }
 
+// PUSH: short suffixes in the split-column form.  Every CTA sends the partial rows a peer will
+// merge straight into that peer's shared memory (the idle half of its V tile) with bulk copies
+// credited to the peer's barrier, so the merge starts when the rows land: no trip through L2,
+// no cluster-wide meeting point before it.
+template <bool PUSH>
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
@@ -191,6 +203,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     mbar_init(&bars.p_full, 8);
     mbar_init(&bars.o_full, 1);
     bars.abort = 0;
+    if (PUSH) {
+      mbar_init(&bars.recv, 1);
+      const int rpr = (min(AT_BQ, p.L) + p.nsplit - 1) / p.nsplit;
+      const int mine = max(0, min(min(AT_BQ, p.L), (sp + 1) * rpr) - sp * rpr);
+      fence_barrier_init();
+      mbar_arrive_expect_tx(&bars.recv, (p.nsplit - 1) * mine * (AT_D / 2 * 4 + 16));
+    }
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -215,6 +234,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  if (PUSH) cluster_arrive_release();  // this CTA's receive barrier is armed
   const uint32_t tmem = bars.tmem_base;
   const uint32_t t_s = tmem, t_p = tmem + 128, t_o = tmem + 256;
   const int nvalid = min(AT_BQ, p.L - qt * AT_BQ);  // real query rows of this tile
@@ -382,7 +402,31 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       bars.abort = 1;
       if (p.status) atomicCAS(p.status, 0, TYBOK_DEV_TIMEOUT_EPILOGUE);
     }
-    if (p.nsplit > 1) {
+    if (PUSH) {
+      // Send every peer the rows it merges: the staged partial rows and their statistics, two
+      // bulk copies per peer, issued by one lane each.
+      if (row < nvalid) {
+        if (hf == 0) {
+          bars.stat[row].x = m2;
+          bars.stat[row].y = sum;
+        } else {
+          bars.stat[row].z = sum;
+        }
+      }
+      fence_proxy_async();  // staging and statistics stores, for the bulk copy engine
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      cluster_wait_acquire();  // every peer's receive barrier is armed
+      if (!bars.abort && warp == 2 && lane < p.nsplit && lane != sp) {
+        const int rpr = (nvalid + p.nsplit - 1) / p.nsplit;
+        const int rs = lane * rpr, ns = min(nvalid, rs + rpr) - rs;
+        if (ns > 0) {
+          const uint32_t recv = smem_u32(sv + AT_PUSH_RECV), bar = dsmem_addr(smem_u32(&bars.recv), lane);
+          bulk_copy_to_peer(dsmem_addr(recv + sp * rpr * (AT_D / 2 * 4), lane), smem + rs * (AT_D / 2 * 4),
+                            ns * (AT_D / 2 * 4), bar);
+          bulk_copy_to_peer(dsmem_addr(recv + AT_PUSH_STATS + sp * rpr * 16, lane), &bars.stat[rs], ns * 16, bar);
+        }
+      }
+    } else if (p.nsplit > 1) {
       // Publish this block's rows: statistics by plain stores, the staged O rows by one bulk copy
       // out of shared memory.  Every softmax warp reaches this point, aborted or not.
       fence_proxy_async();  // the staging stores, for the bulk copy engine
@@ -408,7 +452,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   // ------------------------------------------------------------ meet: every key block published
   if (tr && tid == 64) tr[5] = clock64();
   tc_fence_before();
-  if (p.nsplit > 1) {
+  if (PUSH) {
+    if (warp < 2) {  // the two service warps only keep the cluster barrier's books
+      cluster_wait_acquire();
+      cluster_arrive_release();
+    }
+  } else if (p.nsplit > 1) {
     __syncwarp();
     cluster_sync_all();  // release / acquire at cluster scope: the peers' workspace rows are visible
   } else {
@@ -416,7 +465,98 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   }
 
   if (tr && tid == 64) tr[6] = clock64();
-  if (warp >= 2 && !bars.abort) {
+  // One merged quad of output columns: bf16 row-major and / or the three e5m2 planes.
+  const long long hd = static_cast<long long>(p.H) * AT_D;
+  const long long plane = static_cast<long long>(p.B) * p.L * hd;
+  auto emit = [&](int r, int c4, const float4& acc) {
+    const int t = qt * AT_BQ + r;
+    const __nv_bfloat162 o01 = __floats2bfloat162_rn(acc.x, acc.y);
+    const __nv_bfloat162 o23 = __floats2bfloat162_rn(acc.z, acc.w);
+    const long long off = (static_cast<long long>(b) * p.L + t) * hd + static_cast<long long>(h) * AT_D + dh * dv + c4 * 4;
+    if (p.out) {
+      uint2 st;
+      st.x = *reinterpret_cast<const uint32_t*>(&o01);
+      st.y = *reinterpret_cast<const uint32_t*>(&o23);
+      *reinterpret_cast<uint2*>(p.out + off) = st;
+    }
+    if (p.out_planes) {
+      const float xs[4] = {__bfloat162float(o01.x) * p.plane_scale, __bfloat162float(o01.y) * p.plane_scale,
+                           __bfloat162float(o23.x) * p.plane_scale, __bfloat162float(o23.y) * p.plane_scale};
+      uint32_t w1, w2, w3;
+      split3_quad(xs, w1, w2, w3);
+      uint8_t* dst = p.out_planes + off;
+      *reinterpret_cast<uint32_t*>(dst) = w1;
+      *reinterpret_cast<uint32_t*>(dst + plane) = w2;
+      *reinterpret_cast<uint32_t*>(dst + 2 * plane) = w3;
+    }
+  };
+  // Normalised merge weights of one owned query row from every block's (max, sum).
+  auto merge_weights = [&](int et, const float (&w_in)[AT_MAX_SPLITS], const float (&l)[AT_MAX_SPLITS]) {
+    float w[AT_MAX_SPLITS];
+    float mx = -1e30f;
+#pragma unroll
+    for (int s = 0; s < AT_MAX_SPLITS; ++s) mx = fmaxf(mx, w_in[s]);
+    float denom = 0.f;
+#pragma unroll
+    for (int s = 0; s < AT_MAX_SPLITS; ++s) {
+      w[s] = s < p.nsplit ? exp2f(w_in[s] - mx) : 0.f;  // 0 for a block without valid keys
+      denom += w[s] * l[s];
+    }
+    const float inv = denom > 0.f ? 1.0f / denom : 0.f;
+#pragma unroll
+    for (int s = 0; s < AT_MAX_SPLITS; ++s) bars.wn[s][et] = w[s] * inv;
+  };
+
+  if (PUSH && warp >= 2) {
+    const int et = tid - 64;
+    constexpr int q4 = AT_D / 2 / 4, rstep = 256 / q4;
+    const int c4 = et % q4, rsub = et / q4;
+    const int rpr = (nvalid + p.nsplit - 1) / p.nsplit;
+    const int r0 = sp * rpr, r1 = min(nvalid, r0 + rpr);
+    const float4* stage = reinterpret_cast<const float4*>(smem);
+    const float4* recv = reinterpret_cast<const float4*>(sv + AT_PUSH_RECV);
+    const float4* rstat = reinterpret_cast<const float4*>(sv + AT_PUSH_RECV + AT_PUSH_STATS);
+    const bool got = at_wait(&bars.recv, 0, &bars.abort);
+    cluster_arrive_release();  // this thread needs nothing more from the peers
+    if (tr && tid == 64) tr[6] = clock64();
+    if (got && r0 + et < r1) {
+      float w[AT_MAX_SPLITS], l[AT_MAX_SPLITS];
+#pragma unroll
+      for (int s = 0; s < AT_MAX_SPLITS; ++s) {
+        w[s] = -1e30f;
+        l[s] = 0.f;
+        if (s < p.nsplit) {
+          const float4 st = s == sp ? bars.stat[r0 + et] : rstat[s * rpr + et];
+          w[s] = st.x;
+          l[s] = st.y + st.z;
+        }
+      }
+      merge_weights(et, w, l);
+    }
+    if (!got) {
+      bars.abort = 1;
+      if (p.status) atomicCAS(p.status, 0, TYBOK_DEV_TIMEOUT_EPILOGUE);
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (tr && tid == 64) tr[7] = clock64();
+    if (!bars.abort) {
+      for (int r = r0 + rsub; r < r1; r += rstep) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        const int sw = c4 ^ (r & 7);
+#pragma unroll
+        for (int s = 0; s < AT_MAX_SPLITS; ++s) {  // block order: bit-reproducible
+          if (s < p.nsplit) {
+            const float ws = bars.wn[s][r - r0];
+            const float4 v = s == sp ? stage[r * q4 + sw] : recv[(s * rpr + r - r0) * q4 + sw];
+            acc.x += ws * v.x; acc.y += ws * v.y; acc.z += ws * v.z; acc.w += ws * v.w;
+          }
+        }
+        emit(r, c4, acc);
+      }
+    }
+  }
+
+  if (!PUSH && warp >= 2 && !bars.abort) {
     // Merge: this CTA owns query rows [r0, r1) of the tile; thread = (4 output columns, row phase).
     const int et = tid - 64;
     const int q4 = dv / 4;          // float4 per row: 64, or 32 with split columns
@@ -425,8 +565,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int rpr = (nvalid + p.nsplit - 1) / p.nsplit;
     const int r0 = sp * rpr, r1 = min(nvalid, r0 + rpr);
     const float4* stage = reinterpret_cast<const float4*>(smem);
-    const long long hd = static_cast<long long>(p.H) * AT_D;
-    const long long plane = static_cast<long long>(p.B) * p.L * hd;
     const uint8_t* ws0 = my_ws - static_cast<long long>(sp) * AT_WS_PER_CTA;  // block 0 of this cluster
     // The partial rows come out of L2 (about a microsecond away), so a thread requests a batch of
     // rows -- every key block of each -- before it needs any of them; the first batch is in
@@ -490,7 +628,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       for (int j = 0; j < AT_MERGE_BATCH; ++j) {
         const int r = rb + rstep * j;
         if (r < r1) {
-          const int t = qt * AT_BQ + r;
           float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
           for (int s = 0; s < AT_MAX_SPLITS; ++s) {  // block order: bit-reproducible
@@ -500,25 +637,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
               acc.x += ws * v.x; acc.y += ws * v.y; acc.z += ws * v.z; acc.w += ws * v.w;
             }
           }
-          const __nv_bfloat162 o01 = __floats2bfloat162_rn(acc.x, acc.y);
-          const __nv_bfloat162 o23 = __floats2bfloat162_rn(acc.z, acc.w);
-          const long long off = (static_cast<long long>(b) * p.L + t) * hd + static_cast<long long>(h) * AT_D + dh * dv + c4 * 4;
-          if (p.out) {
-            uint2 st;
-            st.x = *reinterpret_cast<const uint32_t*>(&o01);
-            st.y = *reinterpret_cast<const uint32_t*>(&o23);
-            *reinterpret_cast<uint2*>(p.out + off) = st;
-          }
-          if (p.out_planes) {
-            const float xs[4] = {__bfloat162float(o01.x) * p.plane_scale, __bfloat162float(o01.y) * p.plane_scale,
-                                 __bfloat162float(o23.x) * p.plane_scale, __bfloat162float(o23.y) * p.plane_scale};
-            uint32_t w1, w2, w3;
-            split3_quad(xs, w1, w2, w3);
-            uint8_t* dst = p.out_planes + off;
-            *reinterpret_cast<uint32_t*>(dst) = w1;
-            *reinterpret_cast<uint32_t*>(dst + plane) = w2;
-            *reinterpret_cast<uint32_t*>(dst + 2 * plane) = w3;
-          }
+          emit(r, c4, acc);
         }
       }
       if (rb + rstep * AT_MERGE_BATCH < r1) fetch(rb + rstep * AT_MERGE_BATCH);
@@ -526,7 +645,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   }
 
   if (tr && tid == 64) tr[8] = clock64();
-  // Nothing after the meeting point touches a peer's shared memory: CTAs leave on their own.
+  // Pull form: nothing after the meeting point touches a peer's shared memory, CTAs leave on
+  // their own.  Push form: a CTA stays until every peer holds the rows it was sent, which is
+  // when the copies have finished reading this CTA's shared memory.
+  if (PUSH) cluster_wait_acquire();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
@@ -619,11 +741,14 @@ int tybok_attention(const void* q, const void* k_cache, const void* v_cache, con
   const int n_qt = (L + AT_BQ - 1) / AT_BQ;
   p.dsplit = (nsplit > 1 && 2 * nsplit * H * n_qt * B <= host::sm_count()) ? 2 : 1;
   p.trace = host::trace_buffer();
+  const int rows_per_rank = (std::min(L, AT_BQ) + nsplit - 1) / nsplit;
+  const bool push = p.dsplit == 2 && n_qt == 1 && nsplit * rows_per_rank <= AT_PUSH_MAX_ROWS;
 
   static bool attr_set[64] = {};
   const int dev = host::current_device();
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM) != cudaSuccess)
+    if (cudaFuncSetAttribute(attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM) != cudaSuccess)
       return host::fail_cuda("cudaFuncSetAttribute(attention_kernel)");
     attr_set[dev] = true;
   }
@@ -648,7 +773,7 @@ int tybok_attention(const void* q, const void* k_cache, const void* v_cache, con
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  if (cudaLaunchKernelEx(&cfg, attention_kernel, tm_q, tm_k, tm_v, p) != cudaSuccess)
+  if (cudaLaunchKernelEx(&cfg, push ? attention_kernel<true> : attention_kernel<false>, tm_q, tm_k, tm_v, p) != cudaSuccess)
     return host::fail_cuda("launch attention_kernel");
   host::count_launch();
   return TYBOK_OK;

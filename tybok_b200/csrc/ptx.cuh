@@ -122,6 +122,24 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// The two halves of the cluster barrier, usable from divergent code: a thread that has arrived
+// must wait before it arrives again.
+__device__ __forceinline__ void cluster_arrive_release() {
+  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait_acquire() {
+  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+// Bulk copy out of this CTA's shared memory into a peer CTA's; the bytes are credited to the
+// peer's mbarrier.  Both destination and barrier are shared::cluster addresses (see mapa below);
+// addresses and size are multiples of 16 bytes.
+__device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster_addr, const void* src, uint32_t bytes,
+                                                  uint32_t bar_cluster_addr) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   dst_cluster_addr),
+               "r"(smem_u32(src)), "r"(bytes), "r"(bar_cluster_addr)
+               : "memory");
+}
 // Address of this CTA's shared-memory location `local` in CTA `rank` of the cluster.
 __device__ __forceinline__ uint32_t dsmem_addr(uint32_t local, uint32_t rank) {
   uint32_t r;
