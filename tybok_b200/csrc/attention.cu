@@ -132,6 +132,7 @@ struct __align__(16) AttnBars {
   uint64_t qk_full[4];  // one per 64-column chunk of Q and K: S = Q K^T starts when the first pair has landed
   uint64_t v_full, s_full, p_full, o_full;
   uint64_t recv;         // push form: the peers' partial rows of the query rows this CTA merges have arrived
+  uint64_t recv_stat;    // push form: the statistics of those rows have arrived (sent ahead, while P.V runs)
   uint32_t tmem_base;
   volatile int abort;
   uint32_t valid[4];     // key-validity bits of this CTA's 128 keys
@@ -205,10 +206,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     bars.abort = 0;
     if (PUSH) {
       mbar_init(&bars.recv, 1);
+      mbar_init(&bars.recv_stat, 1);
       const int rpr = (min(AT_BQ, p.L) + p.nsplit - 1) / p.nsplit;
       const int mine = max(0, min(min(AT_BQ, p.L), (sp + 1) * rpr) - sp * rpr);
       fence_barrier_init();
-      mbar_arrive_expect_tx(&bars.recv, (p.nsplit - 1) * mine * (AT_D / 2 * 4 + 16));
+      mbar_arrive_expect_tx(&bars.recv, (p.nsplit - 1) * mine * (AT_D / 2 * 4));
+      mbar_arrive_expect_tx(&bars.recv_stat, (p.nsplit - 1) * mine * 16);
     }
     fence_barrier_init();
   }
@@ -373,6 +376,28 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     __syncwarp();
     if (ok && lane == 0) mbar_arrive(&bars.p_full);
     if (tr && tid == 128) tr[3] = clock64();
+    if (PUSH) {
+      // The statistics are final here: send them to the merging peers while P.V runs, so that
+      // the merge weights are ready before the partial rows arrive.
+      if (row < nvalid) {
+        if (hf == 0) {
+          bars.stat[row].x = m2;
+          bars.stat[row].y = sum;
+        } else {
+          bars.stat[row].z = sum;
+        }
+      }
+      fence_proxy_async();  // the statistics stores, for the bulk copy engine
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      cluster_wait_acquire();  // every peer's receive barriers are armed
+      if (ok && warp == 2 && lane < p.nsplit && lane != sp) {
+        const int rpr = (nvalid + p.nsplit - 1) / p.nsplit;
+        const int rs = lane * rpr, ns = min(nvalid, rs + rpr) - rs;
+        if (ns > 0)
+          bulk_copy_to_peer(dsmem_addr(smem_u32(sv + AT_PUSH_RECV + AT_PUSH_STATS) + sp * rpr * 16, lane), &bars.stat[rs],
+                            ns * 16, dsmem_addr(smem_u32(&bars.recv_stat), lane));
+      }
+    }
     // ---------------------------------------------------------- stage O (un-normalised), fp32
     ok = ok && __all_sync(0xffffffffu, at_wait(&bars.o_full, 0, &bars.abort));
     if (tr && tid == 128) tr[4] = clock64();
@@ -403,19 +428,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (p.status) atomicCAS(p.status, 0, TYBOK_DEV_TIMEOUT_EPILOGUE);
     }
     if (PUSH) {
-      // Send every peer the rows it merges: the staged partial rows and their statistics, two
-      // bulk copies per peer, issued by one lane each.
-      if (row < nvalid) {
-        if (hf == 0) {
-          bars.stat[row].x = m2;
-          bars.stat[row].y = sum;
-        } else {
-          bars.stat[row].z = sum;
-        }
-      }
-      fence_proxy_async();  // staging and statistics stores, for the bulk copy engine
+      // Send every peer the staged partial rows it merges: one bulk copy per peer, one lane each.
+      fence_proxy_async();  // the staging stores, for the bulk copy engine
       asm volatile("bar.sync 1, 256;" ::: "memory");
-      cluster_wait_acquire();  // every peer's receive barrier is armed
       if (!bars.abort && warp == 2 && lane < p.nsplit && lane != sp) {
         const int rpr = (nvalid + p.nsplit - 1) / p.nsplit;
         const int rs = lane * rpr, ns = min(nvalid, rs + rpr) - rs;
@@ -423,7 +438,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           const uint32_t recv = smem_u32(sv + AT_PUSH_RECV), bar = dsmem_addr(smem_u32(&bars.recv), lane);
           bulk_copy_to_peer(dsmem_addr(recv + sp * rpr * (AT_D / 2 * 4), lane), smem + rs * (AT_D / 2 * 4),
                             ns * (AT_D / 2 * 4), bar);
-          bulk_copy_to_peer(dsmem_addr(recv + AT_PUSH_STATS + sp * rpr * 16, lane), &bars.stat[rs], ns * 16, bar);
         }
       }
     } else if (p.nsplit > 1) {
@@ -516,10 +530,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const float4* stage = reinterpret_cast<const float4*>(smem);
     const float4* recv = reinterpret_cast<const float4*>(sv + AT_PUSH_RECV);
     const float4* rstat = reinterpret_cast<const float4*>(sv + AT_PUSH_RECV + AT_PUSH_STATS);
-    const bool got = at_wait(&bars.recv, 0, &bars.abort);
-    cluster_arrive_release();  // this thread needs nothing more from the peers
-    if (tr && tid == 64) tr[6] = clock64();
-    if (got && r0 + et < r1) {
+    bool got = true;
+    if (r0 + et < r1) {  // one thread per owned row: its weights, while the partial rows are in flight
+      got = at_wait(&bars.recv_stat, 0, &bars.abort);
       float w[AT_MAX_SPLITS], l[AT_MAX_SPLITS];
 #pragma unroll
       for (int s = 0; s < AT_MAX_SPLITS; ++s) {
@@ -533,6 +546,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
       merge_weights(et, w, l);
     }
+    if (tr && tid == 64) tr[9] = clock64();
+    got = at_wait(&bars.recv, 0, &bars.abort) && got;
+    cluster_arrive_release();  // this thread needs nothing more from the peers
+    if (tr && tid == 64) tr[6] = clock64();
     if (!got) {
       bars.abort = 1;
       if (p.status) atomicCAS(p.status, 0, TYBOK_DEV_TIMEOUT_EPILOGUE);
