@@ -237,7 +237,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (PUSH) cluster_arrive_release();  // this CTA's receive barrier is armed
+  if (PUSH) cluster_arrive_relaxed();  // this CTA's receive barrier is armed
   const uint32_t tmem = bars.tmem_base;
   const uint32_t t_s = tmem, t_p = tmem + 128, t_o = tmem + 256;
   const int nvalid = min(AT_BQ, p.L - qt * AT_BQ);  // real query rows of this tile

@@ -127,6 +127,11 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void cluster_arrive_release() {
   asm volatile("barrier.cluster.arrive.release;" ::: "memory");
 }
+// Arrival that orders nothing by itself: enough after fence_barrier_init(), whose release at
+// cluster scope already covers the barrier initialisation a peer must see.
+__device__ __forceinline__ void cluster_arrive_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory");
+}
 __device__ __forceinline__ void cluster_wait_acquire() {
   asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
 }
