@@ -673,6 +673,351 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   }
 }
 
+
+// ------------------------------------------------------------------------------ prefill form
+// Long query sequences (more than one query tile): one CTA per (query tile, head, batch) walks
+// over the keys in blocks of 64 and keeps the running output in tensor memory, so nothing is
+// exchanged between CTAs.  Warp 0 streams K and V blocks through two-deep rings, warp 1 issues
+// S_j = Q K_j^T one block ahead and O += P_j V_j, warps 2..5 hold one query row per thread:
+// block maximum, P_j = exp2(s * c - m) as bf16 over the S_j columns, row sum.  The reference
+// maximum m of a row only moves when the block maximum exceeds it by more than 2^8 (P stays
+// below 256, exact enough in bf16 and fp32); then the thread rescales its O row and its sum.
+// All eight epilogue warps normalise and write the output at the end.
+constexpr int PF_BK = 64;                    // keys per block
+constexpr int PF_KCHUNK = PF_BK * 128;       // one 64-column chunk of a K or V block
+constexpr int PF_KV = 4 * PF_KCHUNK;         // one K or V block: 32 KB
+constexpr int PF_MAX_KEYS = 4096;
+constexpr float PF_RESCALE = 8.0f;
+
+struct __align__(8) PrefillBars {
+  uint64_t q_full;
+  uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+  uint64_t s_full[2], p_full[2];
+  uint64_t o_done;    // one phase per P.V product.  S_j is issued after P.V of block j-2, so a thread that
+                      // holds S_j and waits for phase j-1 is never more than one phase behind
+  uint64_t all_done;  // the last P.V product has landed
+  uint32_t tmem_base;
+  volatile int abort;
+  uint32_t valid[PF_MAX_KEYS / 32];
+  float hmax[2][2][AT_BQ];  // [block parity][half of the block's keys][row]: maximum of the valid scores
+  float hsum[2][AT_BQ];     // [half][row]: sum of that half's probabilities over all blocks
+};
+
+__global__ void __launch_bounds__(AT_THREADS, 1)
+attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                         const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ PrefillBars bars;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sq = smem;
+  uint8_t* sk = smem + AT_TILE;             // two K blocks
+  uint8_t* sv = smem + AT_TILE + 2 * PF_KV;  // two V blocks
+
+  const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int g = h / (p.H / p.G);
+  const int nkb = (p.Lk + PF_BK - 1) / PF_BK;
+  const int nvalid = min(AT_BQ, p.L - qt * AT_BQ);
+
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+    mbar_init(&bars.q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars.k_full[i], 1);
+      mbar_init(&bars.k_empty[i], 1);
+      mbar_init(&bars.v_full[i], 1);
+      mbar_init(&bars.v_empty[i], 1);
+      mbar_init(&bars.s_full[i], 1);
+      mbar_init(&bars.p_full[i], 8);
+    }
+    mbar_init(&bars.o_done, 1);
+    mbar_init(&bars.all_done, 1);
+    bars.abort = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars.tmem_base, 512);
+    tmem_relinquish();
+  }
+  if (warp >= 2 && warp < 6) {  // validity bits of every key, 32 per word
+    if (p.key_valid && p.pdl) pdl_wait();
+    for (int w = warp - 2; w < 2 * nkb; w += 4) {
+      const int j = w * 32 + lane;
+      bool ok = j < p.Lk;
+      if (ok && p.key_valid) ok = p.key_valid[static_cast<long long>(b) * p.Lk + j] != 0;
+      const uint32_t bits = __ballot_sync(0xffffffffu, ok);
+      if (lane == 0) bars.valid[w] = bits;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars.tmem_base;
+  const uint32_t t_o = tmem + 256;  // S_j (and P_j over it) at columns 64 * (j & 1)
+  long long* tr = p.trace ? p.trace + 16ll * ((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) : nullptr;
+  const long long t_start = clock64();
+  if (tr && tid == 0) tr[0] = t_start;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      if (p.pdl) pdl_launch_dependents();
+      if (p.pdl) pdl_wait();
+      mbar_arrive_expect_tx(&bars.q_full, AT_TILE);
+      for (int c = 0; c < 4; ++c) tma_load_2d(sq + c * AT_CHUNK, &tm_q, &bars.q_full, h * AT_D + c * 64, b * p.L + qt * AT_BQ);
+      for (int j = 0; j < nkb; ++j) {
+        const int s = j & 1;
+        const uint32_t par = ((j >> 1) & 1) ^ 1;  // the ring slot's previous use
+        const int krow = (b * p.G + g) * p.Lcap + j * PF_BK;
+        if (j >= 2 && !at_wait(&bars.k_empty[s], par, &bars.abort)) break;
+        mbar_arrive_expect_tx(&bars.k_full[s], PF_KV);
+        for (int c = 0; c < 4; ++c) tma_load_2d(sk + s * PF_KV + c * PF_KCHUNK, &tm_k, &bars.k_full[s], c * 64, krow);
+        if (j >= 2 && !at_wait(&bars.v_empty[s], par, &bars.abort)) break;
+        mbar_arrive_expect_tx(&bars.v_full[s], PF_KV);
+        for (int c = 0; c < 4; ++c) tma_load_2d(sv + s * PF_KV + c * PF_KCHUNK, &tm_v, &bars.v_full[s], c * 64, krow);
+      }
+    }
+  } else if (warp == 1) {
+    const bool leader = elect_one();
+    const uint64_t dk = smem_desc_sw128(0);
+    const uint32_t idesc_s = idesc_bf16_f32(AT_BQ, PF_BK);
+    const uint32_t idesc_o = idesc_bf16_f32(AT_BQ, AT_D) | (1u << 16);
+    const uint32_t q16 = (smem_u32(sq) & 0x3FFFFu) >> 4;
+    bool ok = __all_sync(0xffffffffu, at_wait(&bars.q_full, 0, &bars.abort));
+    auto issue_s = [&](int j) {  // S_j = Q K_j^T into columns 64 * (j & 1); frees the K slot when done
+      const int s = j & 1;
+      ok = ok && __all_sync(0xffffffffu, at_wait(&bars.k_full[s], (j >> 1) & 1, &bars.abort));
+      if (!ok) return;
+      tc_fence_after();
+      const uint32_t k16 = (smem_u32(sk + s * PF_KV) & 0x3FFFFu) >> 4;
+#pragma unroll
+      for (int ks = 0; ks < 16; ++ks) {  // D = 256 in steps of 16: chunk ks / 4, 32 bytes per step
+        const uint32_t qo = (ks >> 2) * (AT_CHUNK >> 4) + (ks & 3) * 2, ko = (ks >> 2) * (PF_KCHUNK >> 4) + (ks & 3) * 2;
+        if (leader) umma_ss_bf16(tmem + s * 64, dk | (q16 + qo), dk | (k16 + ko), idesc_s, ks > 0 ? 1u : 0u);
+      }
+      if (leader) {
+        tc_commit(&bars.k_empty[s]);
+        tc_commit(&bars.s_full[s]);
+      }
+      __syncwarp();
+    };
+    if (ok) issue_s(0);
+    if (ok && nkb > 1) issue_s(1);
+#pragma unroll 1
+    for (int j = 0; j < nkb && ok; ++j) {
+      const int s = j & 1;
+      const uint32_t par = (j >> 1) & 1;
+      ok = __all_sync(0xffffffffu, at_wait(&bars.p_full[s], par, &bars.abort) && at_wait(&bars.v_full[s], par, &bars.abort));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t v_addr = smem_u32(sv + s * PF_KV);
+#pragma unroll
+      for (int ks = 0; ks < PF_BK / 16; ++ks) {  // 16 keys per step: 16 rows x 128 bytes inside every chunk
+        const uint64_t bd = smem_desc_sw128_mn(v_addr + ks * 2048, PF_KCHUNK);
+        if (leader) umma_ts_bf16(t_o, tmem + s * 64 + ks * 8, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+      }
+      if (leader) {
+        tc_commit(&bars.v_empty[s]);
+        tc_commit(&bars.o_done);
+        if (j == nkb - 1) tc_commit(&bars.all_done);
+      }
+      __syncwarp();
+      if (j + 2 < nkb) issue_s(j + 2);  // over P_j, which the product just issued reads first
+    }
+    // nothing of this CTA's tensor work may be in flight when it gives up its tensor memory
+    ok = ok && __all_sync(0xffffffffu, at_wait(&bars.all_done, 0, &bars.abort));
+    if (!ok && lane == 0) {
+      bars.abort = 1;
+      if (p.status) atomicCAS(p.status, 0, TYBOK_DEV_TIMEOUT_MMA);
+    }
+  }
+  else {
+    // -------------------------------------------------------------- softmax: two threads per query row
+    const int q = warp & 3;          // tensor-memory lane quadrant of this warp
+    const int hf = (warp - 2) >> 2;  // which 32 keys of a block / which 128 output columns
+    const int row = q * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    const bool live = q * 32 < nvalid;  // warp-uniform: this quadrant holds real query rows
+    // All eight warps walk the blocks in step (one named barrier per block), whatever the waits
+    // return: after a failed wait `ok` stays false and the abort flag makes every later wait return.
+    bool ok = true;
+    float m_ref = -1e30f, l = 0.f;
+#pragma unroll 1
+    for (int j = 0; j < nkb; ++j) {
+      const int s = j & 1;
+      if (ok && !__all_sync(0xffffffffu, at_wait(&bars.s_full[s], (j >> 1) & 1, &bars.abort))) {
+        ok = false;
+        bars.abort = 1;
+      }
+      if (tr && tid == 128 && j < 6) tr[1 + 2 * j] = clock64();
+      uint32_t v[32];
+      const uint32_t bits = bars.valid[2 * j + hf];
+      float mx = -1e30f;
+      if (ok && live) {
+        tc_fence_after();
+        tmem_ld32(tmem + lane_addr + s * 64 + hf * 32, v);
+        tc_wait_ld();
+        if (bits == 0xffffffffu) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
+        } else if (bits != 0u) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if ((bits >> e) & 1u) mx = fmaxf(mx, __uint_as_float(v[e]));
+        }
+      }
+      bars.hmax[s][hf][row] = mx;
+      tc_fence_before();
+      asm volatile("bar.sync 1, 256;" ::: "memory");  // both halves of every row have read S_j
+      if (ok && live) {
+        tc_fence_after();
+        const float m_blk = fmaxf(bars.hmax[s][0][row], bars.hmax[s][1][row]) * p.scale_log2e;  // scale > 0
+        if (j == 0) {
+          m_ref = m_blk;
+        } else {
+          const bool grow = m_blk > m_ref + PF_RESCALE;
+          if (__any_sync(0xffffffffu, grow)) {
+            // Rescale this thread's half of the O row (and its sum) to the new reference maximum;
+            // rows of the warp that keep theirs multiply by one.  The previous P.V product must
+            // have landed (it is at most one phase away, see PrefillBars::o_done).
+            if (!__all_sync(0xffffffffu, at_wait(&bars.o_done, (j - 1) & 1, &bars.abort))) {
+              ok = false;
+              bars.abort = 1;
+            } else {
+              tc_fence_after();
+              const float f = grow ? exp2f(m_ref - m_blk) : 1.0f;
+#pragma unroll 1
+              for (int c = hf * 4; c < hf * 4 + 4; ++c) {
+                uint32_t o[32];
+                tmem_ld32(t_o + lane_addr + c * 32, o);
+                tc_wait_ld();
+#pragma unroll
+                for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * f);
+                tmem_st32(t_o + lane_addr + c * 32, o);
+              }
+              tc_wait_st();
+              l *= f;
+              if (grow) m_ref = m_blk;
+            }
+          }
+        }
+      }
+      if (ok && live) {
+        uint32_t pk[16];
+        float sum = 0.f;
+        if (bits == 0xffffffffu) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const float p0 = exp2f(__uint_as_float(v[e]) * p.scale_log2e - m_ref);
+            const float p1 = exp2f(__uint_as_float(v[e + 1]) * p.scale_log2e - m_ref);
+            sum += p0 + p1;
+            const __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
+            pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&pp);
+          }
+        } else if (bits == 0u) {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) pk[e] = 0u;
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const float p0 = ((bits >> e) & 1u) ? exp2f(__uint_as_float(v[e]) * p.scale_log2e - m_ref) : 0.f;
+            const float p1 = ((bits >> (e + 1)) & 1u) ? exp2f(__uint_as_float(v[e + 1]) * p.scale_log2e - m_ref) : 0.f;
+            sum += p0 + p1;
+            const __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
+            pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&pp);
+          }
+        }
+        l += sum;
+        tmem_st16(tmem + lane_addr + s * 64 + hf * 16, pk);  // P_j: 32 columns over the start of S_j
+        tc_wait_st();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (ok && lane == 0) mbar_arrive(&bars.p_full[s]);
+      if (tr && tid == 128 && j < 6) tr[2 + 2 * j] = clock64();
+    }
+    bars.hsum[hf][row] = l;
+    if (ok && !__all_sync(0xffffffffu, at_wait(&bars.all_done, 0, &bars.abort))) ok = false;
+    if (!ok && lane == 0) {
+      bars.abort = 1;
+      if (p.status) atomicCAS(p.status, 0, TYBOK_DEV_TIMEOUT_EPILOGUE);
+    }
+    // ------------------------------------------------------------ output
+    // Normalised rows go through shared memory (Q, K and V are idle by now): bf16 rows of 512
+    // bytes and three plane rows of 256 bytes, each padded by 16 bytes against bank conflicts,
+    // then one bulk copy per row and array, so that global memory sees whole rows.
+    if (tr && tid == 128) tr[13] = clock64();
+    tc_fence_before();
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    constexpr int OB = AT_D * 2 + 16, OP = AT_D + 16;  // padded row pitches
+    uint8_t* so = smem;
+    uint8_t* sp = smem + AT_BQ * OB;
+    const bool good = !bars.abort;
+    if (good && live) {  // warp-uniform: the tensor-memory loads below are warp-wide
+      tc_fence_after();
+      const float ls = bars.hsum[0][row] + bars.hsum[1][row];
+      const float inv = ls > 0.f ? 1.0f / ls : 0.f;
+#pragma unroll 1
+      for (int c = hf * 4; c < hf * 4 + 4; ++c) {
+        uint32_t o[32];
+        tmem_ld32(t_o + lane_addr + c * 32, o);
+        tc_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; e += 8) {
+          uint32_t ob[4], w1[2], w2[2], w3[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const __nv_bfloat162 o01 = __floats2bfloat162_rn(__uint_as_float(o[e + 4 * u]) * inv, __uint_as_float(o[e + 4 * u + 1]) * inv);
+            const __nv_bfloat162 o23 = __floats2bfloat162_rn(__uint_as_float(o[e + 4 * u + 2]) * inv, __uint_as_float(o[e + 4 * u + 3]) * inv);
+            ob[2 * u] = *reinterpret_cast<const uint32_t*>(&o01);
+            ob[2 * u + 1] = *reinterpret_cast<const uint32_t*>(&o23);
+            const float xs[4] = {__bfloat162float(o01.x) * p.plane_scale, __bfloat162float(o01.y) * p.plane_scale,
+                                 __bfloat162float(o23.x) * p.plane_scale, __bfloat162float(o23.y) * p.plane_scale};
+            split3_quad(xs, w1[u], w2[u], w3[u]);
+          }
+          const int col = c * 32 + e;
+          *reinterpret_cast<uint4*>(so + row * OB + col * 2) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+          *reinterpret_cast<uint2*>(sp + row * OP + col) = make_uint2(w1[0], w1[1]);
+          *reinterpret_cast<uint2*>(sp + (AT_BQ + row) * OP + col) = make_uint2(w2[0], w2[1]);
+          *reinterpret_cast<uint2*>(sp + (2 * AT_BQ + row) * OP + col) = make_uint2(w3[0], w3[1]);
+        }
+      }
+    }
+    fence_proxy_async();  // the staged rows, for the bulk copy engine
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (good) {
+      const int et = tid - 64;           // 256 threads: row et / 2, arrays (bf16, plane 0) or (plane 1, plane 2)
+      const int r = et >> 1, half = et & 1;
+      if (r < nvalid) {
+        const long long hd = static_cast<long long>(p.H) * AT_D;
+        const long long plane = static_cast<long long>(p.B) * p.L * hd;
+        const long long off = (static_cast<long long>(b) * p.L + qt * AT_BQ + r) * hd + static_cast<long long>(h) * AT_D;
+        auto copy_out = [](void* dst, const void* src, uint32_t bytes) {
+          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src)), "r"(bytes)
+                       : "memory");
+        };
+        if (half == 0) {
+          if (p.out) copy_out(p.out + off, so + r * OB, AT_D * 2);
+          if (p.out_planes) copy_out(p.out_planes + off, sp + r * OP, AT_D);
+        } else if (p.out_planes) {
+          copy_out(p.out_planes + plane + off, sp + (AT_BQ + r) * OP, AT_D);
+          copy_out(p.out_planes + 2 * plane + off, sp + (2 * AT_BQ + r) * OP, AT_D);
+        }
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // shared memory is given up at exit
+      }
+    }
+  }
+  if (tr && tid == 128) tr[14] = clock64();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
 }  // namespace tb
 
 extern "C" {
@@ -712,6 +1057,7 @@ int tybok_rope_store(const void* qkv, int64_t ldq, const int* pos, const void* c
 size_t tybok_attention_workspace_bytes(int B, int L, int H, int Lk) {
   using namespace tb;
   if (B <= 0 || L <= 0 || H <= 0 || Lk <= AT_BK) return 0;  // a single key block merges inside its CTA
+  if (L > AT_BQ && Lk <= PF_MAX_KEYS) return 0;             // the prefill form exchanges nothing
   const size_t nsplit = (static_cast<size_t>(Lk) + AT_BK - 1) / AT_BK, n_qt = (static_cast<size_t>(L) + AT_BQ - 1) / AT_BQ;
   return 2 * nsplit * n_qt * H * B * AT_WS_PER_CTA;  // room for the split-column form of small grids
 }
@@ -725,7 +1071,10 @@ int tybok_attention(const void* q, const void* k_cache, const void* v_cache, con
   if (B <= 0 || L <= 0 || H <= 0 || G <= 0 || H % G != 0 || Lk <= 0 || Lk > Lcap)
     return host::fail(TYBOK_ERR_ARG, "attention: bad shape (H % G == 0, 0 < Lk <= Lcap)");
   const int nsplit = (Lk + AT_BK - 1) / AT_BK;
-  if (nsplit > AT_MAX_SPLITS) return host::fail(TYBOK_ERR_ARG, "attention: at most 1024 keys (8 blocks of 128 per cluster)");
+  const bool prefill = L > AT_BQ && Lk <= PF_MAX_KEYS;  // several query tiles: the key-loop form
+  if (!prefill && nsplit > AT_MAX_SPLITS)
+    return host::fail(TYBOK_ERR_ARG, "attention: at most 1024 keys (8 blocks of 128 per cluster) for up to 128 queries, "
+                                     "4096 keys beyond");
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
        reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(out_planes)) & 15)
     return host::fail(TYBOK_ERR_ARG, "attention: tensors must be 16-byte aligned");
@@ -741,8 +1090,9 @@ int tybok_attention(const void* q, const void* k_cache, const void* v_cache, con
   if (int rc = host::tensor_map_2d(&tm_q, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, hd, static_cast<uint64_t>(B) * L, hd * 2, 64, q_rows))
     return rc;
   const uint64_t krows = static_cast<uint64_t>(B) * G * Lcap;
-  if (int rc = host::tensor_map_2d(&tm_k, k_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, krows, D * 2, 64, AT_BK)) return rc;
-  if (int rc = host::tensor_map_2d(&tm_v, v_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, krows, D * 2, 64, AT_BK)) return rc;
+  const int kbox = prefill ? PF_BK : AT_BK;
+  if (int rc = host::tensor_map_2d(&tm_k, k_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, krows, D * 2, 64, kbox)) return rc;
+  if (int rc = host::tensor_map_2d(&tm_v, v_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, krows, D * 2, 64, kbox)) return rc;
 
   AttnParams p{};
   p.B = B; p.L = L; p.H = H; p.G = G; p.Lk = Lk; p.Lcap = Lcap; p.nsplit = nsplit;
@@ -765,12 +1115,13 @@ int tybok_attention(const void* q, const void* k_cache, const void* v_cache, con
   const int dev = host::current_device();
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
     if (cudaFuncSetAttribute(attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM) != cudaSuccess ||
-        cudaFuncSetAttribute(attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM) != cudaSuccess)
+        cudaFuncSetAttribute(attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM) != cudaSuccess)
       return host::fail_cuda("cudaFuncSetAttribute(attention_kernel)");
     attr_set[dev] = true;
   }
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(nsplit, H * n_qt * p.dsplit, B);
+  cfg.gridDim = prefill ? dim3(n_qt, H, B) : dim3(nsplit, H * n_qt * p.dsplit, B);
   cfg.blockDim = dim3(AT_THREADS);
   cfg.dynamicSmemBytes = AT_SMEM;
   cfg.stream = static_cast<cudaStream_t>(stream);
@@ -781,7 +1132,7 @@ int tybok_attention(const void* q, const void* k_cache, const void* v_cache, con
     attr[na].val.programmaticStreamSerializationAllowed = 1;
     ++na;
   }
-  if (nsplit > 1) {
+  if (nsplit > 1 && !prefill) {
     attr[na].id = cudaLaunchAttributeClusterDimension;
     attr[na].val.clusterDim.x = nsplit;
     attr[na].val.clusterDim.y = 1;
@@ -790,7 +1141,8 @@ int tybok_attention(const void* q, const void* k_cache, const void* v_cache, con
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  if (cudaLaunchKernelEx(&cfg, push ? attention_kernel<true> : attention_kernel<false>, tm_q, tm_k, tm_v, p) != cudaSuccess)
+  if (cudaLaunchKernelEx(&cfg, prefill ? attention_prefill_kernel : push ? attention_kernel<true> : attention_kernel<false>,
+                         tm_q, tm_k, tm_v, p) != cudaSuccess)
     return host::fail_cuda("launch attention_kernel");
   host::count_launch();
   return TYBOK_OK;
