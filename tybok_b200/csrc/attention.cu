@@ -688,6 +688,12 @@ constexpr int PF_KCHUNK = PF_BK * 128;       // one 64-column chunk of a K or V 
 constexpr int PF_KV = 4 * PF_KCHUNK;         // one K or V block: 32 KB
 constexpr int PF_MAX_KEYS = 4096;
 constexpr float PF_RESCALE = 8.0f;
+// 2^x by the special-function unit alone (results below 2^-126 flush to zero).
+__device__ __forceinline__ float pf_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 struct __align__(8) PrefillBars {
   uint64_t q_full;
@@ -886,7 +892,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
               bars.abort = 1;
             } else {
               tc_fence_after();
-              const float f = grow ? exp2f(m_ref - m_blk) : 1.0f;
+              const float f = grow ? pf_exp2(m_ref - m_blk) : 1.0f;
 #pragma unroll 1
               for (int c = hf * 4; c < hf * 4 + 4; ++c) {
                 uint32_t o[32];
@@ -909,8 +915,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
         if (bits == 0xffffffffu) {
 #pragma unroll
           for (int e = 0; e < 32; e += 2) {
-            const float p0 = exp2f(__uint_as_float(v[e]) * p.scale_log2e - m_ref);
-            const float p1 = exp2f(__uint_as_float(v[e + 1]) * p.scale_log2e - m_ref);
+            const float p0 = pf_exp2(__uint_as_float(v[e]) * p.scale_log2e - m_ref);
+            const float p1 = pf_exp2(__uint_as_float(v[e + 1]) * p.scale_log2e - m_ref);
             sum += p0 + p1;
             const __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
             pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&pp);
@@ -921,8 +927,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
         } else {
 #pragma unroll
           for (int e = 0; e < 32; e += 2) {
-            const float p0 = ((bits >> e) & 1u) ? exp2f(__uint_as_float(v[e]) * p.scale_log2e - m_ref) : 0.f;
-            const float p1 = ((bits >> (e + 1)) & 1u) ? exp2f(__uint_as_float(v[e + 1]) * p.scale_log2e - m_ref) : 0.f;
+            const float p0 = ((bits >> e) & 1u) ? pf_exp2(__uint_as_float(v[e]) * p.scale_log2e - m_ref) : 0.f;
+            const float p1 = ((bits >> (e + 1)) & 1u) ? pf_exp2(__uint_as_float(v[e + 1]) * p.scale_log2e - m_ref) : 0.f;
             sum += p0 + p1;
             const __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
             pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&pp);
@@ -946,7 +952,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
     // ------------------------------------------------------------ output
     // Normalised rows go through shared memory (Q, K and V are idle by now): bf16 rows of 512
     // bytes and three plane rows of 256 bytes, each padded by 16 bytes against bank conflicts,
-    // then one bulk copy per row and array, so that global memory sees whole rows.
+    // then one warp per row, so that global memory sees whole rows.
     if (tr && tid == 128) tr[13] = clock64();
     tc_fence_before();
     asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -984,28 +990,22 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
         }
       }
     }
-    fence_proxy_async();  // the staged rows, for the bulk copy engine
+    if (tr && tid == 128) tr[15] = clock64();
     asm volatile("bar.sync 1, 256;" ::: "memory");
     if (good) {
-      const int et = tid - 64;           // 256 threads: row et / 2, arrays (bf16, plane 0) or (plane 1, plane 2)
-      const int r = et >> 1, half = et & 1;
-      if (r < nvalid) {
-        const long long hd = static_cast<long long>(p.H) * AT_D;
-        const long long plane = static_cast<long long>(p.B) * p.L * hd;
+      // one warp per row: 32 lanes x 16 bytes of bf16, 32 lanes x 8 bytes of every plane
+      const long long hd = static_cast<long long>(p.H) * AT_D;
+      const long long plane = static_cast<long long>(p.B) * p.L * hd;
+#pragma unroll 2
+      for (int r = warp - 2; r < nvalid; r += 8) {
         const long long off = (static_cast<long long>(b) * p.L + qt * AT_BQ + r) * hd + static_cast<long long>(h) * AT_D;
-        auto copy_out = [](void* dst, const void* src, uint32_t bytes) {
-          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src)), "r"(bytes)
-                       : "memory");
-        };
-        if (half == 0) {
-          if (p.out) copy_out(p.out + off, so + r * OB, AT_D * 2);
-          if (p.out_planes) copy_out(p.out_planes + off, sp + r * OP, AT_D);
-        } else if (p.out_planes) {
-          copy_out(p.out_planes + plane + off, sp + (AT_BQ + r) * OP, AT_D);
-          copy_out(p.out_planes + 2 * plane + off, sp + (2 * AT_BQ + r) * OP, AT_D);
+        if (p.out) *reinterpret_cast<uint4*>(p.out + off + lane * 8) = *reinterpret_cast<const uint4*>(so + r * OB + lane * 16);
+        if (p.out_planes) {
+          uint8_t* dst = p.out_planes + off + lane * 8;
+          *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(sp + r * OP + lane * 8);
+          *reinterpret_cast<uint2*>(dst + plane) = *reinterpret_cast<const uint2*>(sp + (AT_BQ + r) * OP + lane * 8);
+          *reinterpret_cast<uint2*>(dst + 2 * plane) = *reinterpret_cast<const uint2*>(sp + (2 * AT_BQ + r) * OP + lane * 8);
         }
-        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // shared memory is given up at exit
       }
     }
   }
