@@ -75,6 +75,38 @@ def test_attention_matches_oracle(b, l, lp, h, g):
     assert torch.equal(out2.cpu().view(b, l, h * D), out)
 
 
+@pytest.mark.parametrize("pattern", ["rising", "one_late_spike", "masked_first_blocks"])
+def test_prefill_attention_rescales_when_the_row_maximum_grows(pattern):
+    """Long query sequences keep O in tensor memory and move a row's reference maximum only when a
+    key block exceeds it by more than 2^8: keys whose scores grow block by block, a single late
+    outlier, and leading key blocks without a valid key all take that rescale (against the oracle's
+    eager attention evaluated in fp32 on the same bf16 caches, no RoPE; rel-L2 <= 1e-2)."""
+    from tybok_b200 import ops
+
+    b, l, h, g, lk = 1, 200, 4, 1, 200
+    gen = torch.Generator().manual_seed(11)
+    q = torch.empty(b * l, h * D).normal_(0, 1, generator=gen).to(torch.bfloat16)
+    k = torch.empty(b, g, lk, D).normal_(0, 1, generator=gen).to(torch.bfloat16)
+    v = torch.empty(b, g, lk, D).normal_(0, 1, generator=gen).to(torch.bfloat16)
+    key_valid = torch.ones(b, lk, dtype=torch.uint8)
+    if pattern == "rising":
+        k = (k.float() * (1.0 + 3.0 * (torch.arange(lk) // 64))[None, None, :, None]).to(torch.bfloat16)
+    elif pattern == "one_late_spike":
+        k[:, :, 170] = (k[:, :, 170].float() * 12.0).to(torch.bfloat16)
+    else:
+        key_valid[:, :130] = 0
+    qh = q.view(b, l, h, D).transpose(1, 2)
+    mask = torch.where(key_valid[:, None, None, :].bool(), 0.0, w8_ref.MASK_VALUE).expand(b, 1, l, lk)
+    # fp32 logits here: at these magnitudes the oracle's bf16 logits are themselves 1e-1 apart
+    ref = w8_ref.gqa_attention(qh.float(), k.float(), v.float(), mask, D**-0.5)
+    out, _ = ops.attention(q.cuda(), k.cuda().contiguous(), v.cuda().contiguous(), key_valid.cuda(), tokens=l, keys=lk,
+                           scale=D**-0.5)
+    ops.check_status()
+    out = out.cpu().view(b, l, h * D)
+    assert torch.isfinite(out.float()).all()
+    assert w8_ref.rel_l2(out.float(), ref) <= 1e-2
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("b,l,h,g,k,key_off", [(1, 50, 8, 1, 1024, 544), (2, 10, 2, 1, 128, 130), (1, 130, 2, 2, 256, 0)])
 def test_qkv_rope_epilogue_matches_projection_then_rope_store(b, l, h, g, k, key_off):
