@@ -177,13 +177,16 @@ int tybok_w8x3_qkv_rope(const void* x_planes, int x_shift, const void* w8_paired
                         int splits, int* status_word, void* stream);
 
 /* GQA/MQA attention of L query tokens per batch element over the first Lk keys of the caches
- * (head_dim 256, Lk <= 1024): softmax(q k^T * scale + mask) v with fp32 softmax, bf16 P.
+ * (head_dim 256; Lk <= 1024 for L <= 128, Lk <= 4096 for longer query sequences):
+ * softmax(q k^T * scale + mask) v with fp32 softmax, bf16 P.
  *   q          [B*L, H*D] bf16 (already rotated);  k_cache / v_cache  [B, G, Lcap, D] bf16, finite
  *   key_valid  NULL or uint8 [B, Lk]: 0 masks a key for every query of that batch element
  *   out        bf16 [B*L, H*D] and/or out_planes [3][B*L][H*D] planes of out * 2^out_shift
  *   workspace  >= tybok_attention_workspace_bytes(B, L, H, Lk) bytes, 16-byte aligned (0 bytes, and
- *              NULL allowed, when Lk <= 128): the key blocks of a query tile exchange their
- *              partial outputs through it (L2), then merge in block order
+ *              NULL allowed, when Lk <= 128 or L > 128): where the key blocks of a query tile are
+ *              spread over a cluster and the partial outputs do not fit the exchange through
+ *              shared memory, they pass through it (L2) and merge in block order.  L > 128 runs
+ *              one CTA per query tile and head over all keys and exchanges nothing.
  * Replaces GemmaAttention._forward_eager (tybok/policies/pi05/models/layers.py:166-191) and the
  * split-K flash kernels of tybok/policies/pi05/models/triton_expert_fused_qkv_rope_attn.py:322-433. */
 int tybok_attention(const void* q, const void* k_cache, const void* v_cache, const void* key_valid, void* out,
