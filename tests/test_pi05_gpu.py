@@ -145,6 +145,34 @@ def test_engine_interface_on_synthetic_checkpoint():
         PI05B200Engine("synthetic:pi05_tiny", device="cuda", require_fused=True, action_fused=False)
 
 
+def test_static_buffer_request_path_equals_the_general_path():
+    """A batch-1 request whose frames have the model's resolution is copied straight into the
+    graph's input buffers; it returns bit for bit what the general preprocessing path returns
+    (eager engine, same seed), also when requests of the other kind (a frame that needs resizing,
+    a missing camera) come in between."""
+    from tybok_b200.engine import PI05B200Engine
+
+    fast = PI05B200Engine("synthetic:pi05_tiny", device="cuda", graph=True, seed=0)
+    gen = PI05B200Engine("synthetic:pi05_tiny", device="cuda", graph=False, seed=0)
+    spec = fast.describe()
+    res = spec["resize"][0]
+    g = torch.Generator().manual_seed(5)
+    noise = torch.randn(1, PI05_TINY.chunk, PI05_TINY.max_action_dim, generator=g)
+    cams = spec["cameras"]
+    for kind in ("at_res", "resize", "at_res", "missing", "at_res"):
+        side = res if kind != "resize" else res + 14
+        images = {c: torch.rand(3, side, side, generator=g) for c in cams}
+        frame = fast.make_frame(images, torch.rand(8, generator=g), f"task {kind}")
+        if kind == "missing":
+            key = [k for k in frame if k.startswith("observation.images.")][-1]
+            frame[key] = None
+        took_static = fast._predict_chunk_static(frame, noise) is not None
+        assert took_static == (kind == "at_res")
+        a = fast.predict_action_chunk(frame, noise=noise)
+        b = gen.predict_action_chunk(frame, noise=noise)
+        assert a.shape == b.shape and (a == b).all()
+
+
 def test_fused_bf16_vision_tower_matches_the_torch_layer_chain():
     """bf16 tower: residual adds inside the LayerNorm kernel, one q/k/v GEMM and the GELU GEMM
     epilogue against the plain torch chain of the same weights."""
