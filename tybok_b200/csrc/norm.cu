@@ -198,7 +198,16 @@ __global__ void __launch_bounds__(128) add_layernorm_kernel(const AddLnParams p)
   const int nvec = p.W / 8;
   const long long base = static_cast<long long>(m) * p.W;
   float v[VEC][8];
+  uint4 rw[VEC], rb[VEC];  // scale and bias: requested with the row, not after its two reductions
   float sm = 0.f;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    const int c = lane + 32 * i;
+    if (c < nvec) {
+      rw[i] = *reinterpret_cast<const uint4*>(p.w + c * 8);
+      rb[i] = *reinterpret_cast<const uint4*>(p.b + c * 8);
+    }
+  }
 #pragma unroll
   for (int i = 0; i < VEC; ++i) {
     const int c = lane + 32 * i;
@@ -246,9 +255,8 @@ __global__ void __launch_bounds__(128) add_layernorm_kernel(const AddLnParams p)
   for (int i = 0; i < VEC; ++i) {
     const int c = lane + 32 * i;
     if (c < nvec) {
-      const uint4 rw = *reinterpret_cast<const uint4*>(p.w + c * 8), rb = *reinterpret_cast<const uint4*>(p.b + c * 8);
-      const __nv_bfloat16* pw = reinterpret_cast<const __nv_bfloat16*>(&rw);
-      const __nv_bfloat16* pb = reinterpret_cast<const __nv_bfloat16*>(&rb);
+      const __nv_bfloat16* pw = reinterpret_cast<const __nv_bfloat16*>(&rw[i]);
+      const __nv_bfloat16* pb = reinterpret_cast<const __nv_bfloat16*>(&rb[i]);
       __nv_bfloat162 o[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e)
