@@ -195,7 +195,7 @@ def test_add_layernorm_kernel():
     from tybok_b200 import ops
 
     g = torch.Generator().manual_seed(9)
-    for m, w in ((37, 1152), (5, 128), (64, 2048)):
+    for m, w in ((37, 1152), (5, 128), (64, 2048), (512, 1152), (200, 1160), (70, 72)):
         x, y = (torch.empty(m, w).normal_(0, 1, generator=g).to(torch.bfloat16) for _ in range(2))
         wt, b = (torch.empty(w).normal_(0, 1, generator=g).to(torch.bfloat16) for _ in range(2))
         xs = x + y

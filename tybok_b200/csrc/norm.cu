@@ -267,6 +267,78 @@ __global__ void __launch_bounds__(128) add_layernorm_kernel(const AddLnParams p)
   }
 }
 
+// The same operation with one CTA per row and eight elements per thread: for rows of a thousand
+// elements and a few hundred rows the warp-per-row form leaves most of the machine idle and each
+// lane walks five dependent-latency loads; here every thread has one load in flight and the two
+// reductions cross the warps through shared memory.
+__global__ void __launch_bounds__(256) add_layernorm_row_kernel(const AddLnParams p) {
+  __shared__ float red[2][8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int c = threadIdx.x, nvec = p.W / 8;
+  const bool live = c < nvec;
+  const long long base = static_cast<long long>(blockIdx.x) * p.W;
+  uint4 rw = {}, rb = {};
+  float v[8];
+  float sm = 0.f;
+  if (live) {
+    rw = *reinterpret_cast<const uint4*>(p.w + c * 8);
+    rb = *reinterpret_cast<const uint4*>(p.b + c * 8);
+    const uint4 rx = *reinterpret_cast<const uint4*>(p.x + base + c * 8);
+    const __nv_bfloat162* hx = reinterpret_cast<const __nv_bfloat162*>(&rx);
+    __nv_bfloat162 s2[4];
+    if (p.y) {
+      const uint4 ry = *reinterpret_cast<const uint4*>(p.y + base + c * 8);
+      const __nv_bfloat162* hy = reinterpret_cast<const __nv_bfloat162*>(&ry);
+#pragma unroll
+      for (int e = 0; e < 4; ++e)  // bf16 + bf16 -> bf16, as the residual add of the bf16 modules
+        s2[e] = __floats2bfloat162_rn(__bfloat162float(hx[e].x) + __bfloat162float(hy[e].x),
+                                      __bfloat162float(hx[e].y) + __bfloat162float(hy[e].y));
+      if (p.x_out) *reinterpret_cast<uint4*>(p.x_out + base + c * 8) = *reinterpret_cast<const uint4*>(s2);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s2[e] = hx[e];
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      v[2 * e] = __bfloat162float(s2[e].x);
+      v[2 * e + 1] = __bfloat162float(s2[e].y);
+      sm += v[2 * e] + v[2 * e + 1];
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sm += __shfl_xor_sync(0xffffffffu, sm, o);
+  if (lane == 0) red[0][warp] = sm;
+  __syncthreads();
+  float tot = 0.f;
+  for (int w = 0; w < nwarps; ++w) tot += red[0][w];
+  const float mean = tot / static_cast<float>(p.W);
+  float ss = 0.f;
+  if (live) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      v[e] -= mean;
+      ss += v[e] * v[e];
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (lane == 0) red[1][warp] = ss;
+  __syncthreads();
+  tot = 0.f;
+  for (int w = 0; w < nwarps; ++w) tot += red[1][w];
+  const float rstd = rsqrtf(tot / static_cast<float>(p.W) + p.eps);
+  if (live) {
+    const __nv_bfloat16* pw = reinterpret_cast<const __nv_bfloat16*>(&rw);
+    const __nv_bfloat16* pb = reinterpret_cast<const __nv_bfloat16*>(&rb);
+    __nv_bfloat162 o[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      o[e] = __floats2bfloat162_rn(v[2 * e] * rstd * __bfloat162float(pw[2 * e]) + __bfloat162float(pb[2 * e]),
+                                   v[2 * e + 1] * rstd * __bfloat162float(pw[2 * e + 1]) + __bfloat162float(pb[2 * e + 1]));
+    *reinterpret_cast<uint4*>(p.h + base + c * 8) = *reinterpret_cast<const uint4*>(o);
+  }
+}
+
 }  // namespace tb
 
 namespace tb {
@@ -348,7 +420,11 @@ int tybok_add_layernorm(const void* x, const void* y, const void* weight, const 
   p.pdl = 0;
   const int per_lane = (W / 8 + 31) / 32;
   cudaError_t e;
-  if (per_lane <= 1) e = cudaLaunchKernelEx(&cfg, add_layernorm_kernel<1>, p);
+  if (per_lane >= 2 && M >= 64) {  // one CTA per row
+    cfg.gridDim = dim3(M);
+    cfg.blockDim = dim3(per_lane * 32);
+    e = cudaLaunchKernelEx(&cfg, add_layernorm_row_kernel, p);
+  } else if (per_lane <= 1) e = cudaLaunchKernelEx(&cfg, add_layernorm_kernel<1>, p);
   else if (per_lane <= 2) e = cudaLaunchKernelEx(&cfg, add_layernorm_kernel<2>, p);
   else if (per_lane <= 5) e = cudaLaunchKernelEx(&cfg, add_layernorm_kernel<5>, p);
   else e = cudaLaunchKernelEx(&cfg, add_layernorm_kernel<8>, p);
