@@ -172,6 +172,79 @@ __global__ void __launch_bounds__(128) rmsnorm_kernel(const NormParams p) {
   }
 }
 
+// The RMS forms with one CTA per row and eight elements per thread (rows of 512..4096
+// elements): one load in flight per thread instead of W / 256 per lane, an eighth of the
+// per-thread arithmetic, and the sum of squares crosses the warps through shared memory.
+__global__ void __launch_bounds__(512) rmsnorm_row_kernel(const NormParams p) {
+  __shared__ float red[16];
+  if (p.pdl) pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int m = blockIdx.x, c = threadIdx.x;
+  const bool live = c < p.W / 8;
+  // Scale / shift are constants of the step: fetch them before waiting for the previous kernel.
+  const float* mod = p.mod ? p.mod + static_cast<long long>(m / p.rows_per_group) * p.ldmod : nullptr;
+  float4 q0 = {}, q1 = {}, h0 = {}, h1 = {};
+  if (live) {
+    const float* a = mod ? mod + c * 8 : p.weight + c * 8;
+    q0 = *reinterpret_cast<const float4*>(a);
+    q1 = *reinterpret_cast<const float4*>(a + 4);
+    if (mod) {
+      h0 = *reinterpret_cast<const float4*>(a + p.W);
+      h1 = *reinterpret_cast<const float4*>(a + p.W + 4);
+    }
+  }
+  if (p.pdl) pdl_wait();
+  float v[8];
+  float ss = 0.f;
+  if (live) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p.x + m * p.ldx + c * 8);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      v[2 * e] = __bfloat162float(h[e].x);
+      v[2 * e + 1] = __bfloat162float(h[e].y);
+      ss += v[2 * e] * v[2 * e] + v[2 * e + 1] * v[2 * e + 1];
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (lane == 0) red[warp] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int w = 0; w < nwarps; ++w) tot += red[w];
+  const float rstd = rsqrtf(tot / static_cast<float>(p.W) + p.eps);
+  if (live) {
+    // x * rstd is formed in fp32 (the bf16 x promotes), as in the reference's _norm
+    const float sc[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+    const float sh[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+    float o[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float t = v[e] * rstd * (1.0f + sc[e]);
+      if (mod) t = v[e] * rstd * (1.0f + sc[e]) + sh[e];
+      o[e] = t;
+    }
+    __nv_bfloat162 b[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) b[e] = __floats2bfloat162_rn(o[2 * e], o[2 * e + 1]);
+    if (p.y) *reinterpret_cast<uint4*>(p.y + m * p.ldy + c * 8) = *reinterpret_cast<const uint4*>(b);
+    if (p.planes) {
+      const float lo[4] = {__bfloat162float(b[0].x) * p.plane_scale, __bfloat162float(b[0].y) * p.plane_scale,
+                           __bfloat162float(b[1].x) * p.plane_scale, __bfloat162float(b[1].y) * p.plane_scale};
+      const float hi[4] = {__bfloat162float(b[2].x) * p.plane_scale, __bfloat162float(b[2].y) * p.plane_scale,
+                           __bfloat162float(b[3].x) * p.plane_scale, __bfloat162float(b[3].y) * p.plane_scale};
+      uint2 w1, w2, w3;
+      split3_quad(lo, w1.x, w2.x, w3.x);
+      split3_quad(hi, w1.y, w2.y, w3.y);
+      const long long plane = static_cast<long long>(p.M) * p.W;
+      uint8_t* dst = p.planes + static_cast<long long>(m) * p.W + c * 8;
+      *reinterpret_cast<uint2*>(dst) = w1;
+      *reinterpret_cast<uint2*>(dst + plane) = w2;
+      *reinterpret_cast<uint2*>(dst + 2 * plane) = w3;
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 // Residual add + affine LayerNorm of the vision tower (tybok/policies/pi05/models/vision.py:
 // x = x + sublayer(x); h = LayerNorm(x)): x_out = bf16(x + y), h = bf16(LN_fp32(x_out) * w + b).
@@ -373,7 +446,11 @@ static int launch_norm(const void* x, int64_t ldx, const float* weight, const fl
   const int per_lane = (W / 8 + 31) / 32;
   const bool full = W % 256 == 0 && W / 256 == per_lane && (per_lane & (per_lane - 1)) == 0;
   cudaError_t e;
-  if (full && per_lane == 4) e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<4, true>, p);
+  if (!ln_scale && per_lane >= 2) {  // one CTA per row
+    cfg.gridDim = dim3(M);
+    cfg.blockDim = dim3(per_lane * 32);
+    e = cudaLaunchKernelEx(&cfg, rmsnorm_row_kernel, p);
+  } else if (full && per_lane == 4) e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<4, true>, p);
   else if (full && per_lane == 8) e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<8, true>, p);
   else if (full && per_lane == 1) e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<1, true>, p);
   else if (full && per_lane == 2) e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<2, true>, p);
