@@ -46,8 +46,10 @@ constexpr int BN = 128;  // weight rows per tile = UMMA M
 constexpr int BK = 128;  // K per pipeline stage (one 128-byte swizzle row of 8-bit elements)
 constexpr int W_TILE_BYTES = BN * BK;
 constexpr int MAX_STAGES = 8;
-constexpr int EPI_WARPS = 8;
+constexpr int EPI_WARPS = 8;       // epilogue warps of the full-K forms (two CTAs share an SM)
+constexpr int EPI_WARPS_WIDE = 16; // ... of the split-K form: four warps per tensor-memory lane quadrant
 constexpr int THREADS = 32 * (2 + EPI_WARPS);
+constexpr int THREADS_WIDE = 32 * (2 + EPI_WARPS_WIDE);
 constexpr int DYN_SMEM_MAX = 226 * 1024;  // 227 KB per CTA minus 1 KB left for static shared memory
 constexpr int CORESIDENT_SMEM = 112 * 1024;  // dynamic shared memory of a CTA when two share an SM (228 KB)
 constexpr int MAX_SPLITS = 8;             // portable cluster size
@@ -131,8 +133,10 @@ __device__ __forceinline__ void fail(Barriers* b, int* status, int code) {
 // tile's epilogue overlaps the other's main loop (register budget 64K / 640 threads).
 // PAIR: the CTA-pair form (cta_group::2 instructions oblige every launch of a kernel that holds
 // them to use clusters of two, so it is an instantiation of its own).
-template <bool PAIR>
-__global__ void __launch_bounds__(THREADS, 2)
+// EW: epilogue warps.  A split-K CTA has the SM to itself and a long serial epilogue per thread
+// (accumulator groups to push, rows to finish): sixteen warps halve both.
+template <bool PAIR, int EW = EPI_WARPS>
+__global__ void __launch_bounds__(32 * (2 + EW), EW == EPI_WARPS ? 2 : 1)
 w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1,
                const __grid_constant__ CUtensorMap tm_x, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -351,7 +355,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     // at the start of the (by now idle) stage ring.
     const int ew = warp - 2;
     const int q = warp & 3;   // TMEM lane quadrant this warp may access
-    const int half = ew >> 2;
+    const int half = ew >> 2;  // which of the EW / 4 warps of this lane quadrant
     const int row = q * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     {
@@ -401,7 +405,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
           // first, long before the accumulator is ready.
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
-            const int rl = ((tid - 64) >> 5) + 8 * u;
+            const int rl = ((tid - 64) >> 5) + EW * u;
             if (rl < own_rows)
               res_pf[u] = *reinterpret_cast<const uint2*>(
                   p.res + static_cast<long long>(m_base + rank * rpr + rl) * p.ldres + n);
@@ -422,7 +426,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
       const int ngroups = (nvalid + 15) / 16;
       const int acc_cols = p.merge ? 3 * p.bt : p.bt;
       for (int w = 0; w < p.nw; ++w) {
-        for (int g = half; g < ngroups; g += 2) {
+        for (int g = half; g < ngroups; g += EW / 4) {
           uint32_t v[16];
           const uint32_t col = tmem + lane_addr + w * acc_cols + g * 16;
           tmem_ld16(col, v);
@@ -492,7 +496,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     const int n = p.epi == EPI_GEGLU_PACKED ? n_tile * (BN / 2) + col0 : n_tile * BN + col0;
     const bool n_ok = n < p.n_out;  // n_out % 4 == 0, so all four channels are valid together
     const int row0 = packed ? rgrp * 2 + (v4 >> 4) : rgrp;
-    const int rstep = packed ? 16 : 8;
+    const int rstep = packed ? 2 * EW : EW;
     const float* stage = reinterpret_cast<const float*>(smem + p.stage_off);
     const long long plane = static_cast<long long>(p.M) * p.n_out;
     if (tr && tid == 64) tr[10] = clock64();
@@ -588,7 +592,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
 #pragma unroll
           for (int e = 0; e < 4; ++e) o[e] = bf16_round(o[e] * gv[e]);
         }
-        const int u = (rl - rgrp) >> 3;
+        const int u = (rl - rgrp) / EW;
         const uint2 rr = u < 4 ? res_pf[u < 4 ? u : 0]
                                : *reinterpret_cast<const uint2*>(p.res + static_cast<long long>(m) * p.ldres + n);
         const __nv_bfloat162 r01 = *reinterpret_cast<const __nv_bfloat162*>(&rr.x);
@@ -677,10 +681,10 @@ static int max_active_clusters(int splits) {
   static int cached[MAX_SPLITS + 1] = {};
   if (splits <= 1) return 1 << 30;
   if (cached[splits] == 0) {
-    cudaFuncSetAttribute(w8_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DYN_SMEM_MAX);
+    cudaFuncSetAttribute(w8_gemm_kernel<false, EPI_WARPS_WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, DYN_SMEM_MAX);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(1, 1, splits);
-    cfg.blockDim = dim3(THREADS);
+    cfg.blockDim = dim3(THREADS_WIDE);
     cfg.dynamicSmemBytes = DYN_SMEM_MAX;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -690,7 +694,7 @@ static int max_active_clusters(int splits) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, w8_gemm_kernel<false>, &cfg) != cudaSuccess || n <= 0) {
+    if (cudaOccupancyMaxActiveClusters(&n, w8_gemm_kernel<false, EPI_WARPS_WIDE>, &cfg) != cudaSuccess || n <= 0) {
       cudaGetLastError();
       n = host::sm_count() / (2 * splits);  // conservative guess
     }
@@ -836,6 +840,7 @@ static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, co
   const int dev = host::current_device();
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
     if (cudaFuncSetAttribute(w8_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DYN_SMEM_MAX) != cudaSuccess ||
+        cudaFuncSetAttribute(w8_gemm_kernel<false, EPI_WARPS_WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, DYN_SMEM_MAX) != cudaSuccess ||
         cudaFuncSetAttribute(w8_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DYN_SMEM_MAX) != cudaSuccess)
       return host::fail_cuda("cudaFuncSetAttribute(w8_gemm_kernel)");
     attr_set[dev] = true;
@@ -843,7 +848,7 @@ static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, co
 
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = pl.pair ? dim3(pl.n_tiles, pl.t_tiles, 1) : dim3(pl.t_tiles, pl.n_tiles, pl.splits);
-  cfg.blockDim = dim3(THREADS);
+  cfg.blockDim = dim3(pl.splits > 1 ? THREADS_WIDE : THREADS);
   cfg.dynamicSmemBytes = pl.smem_bytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -862,8 +867,9 @@ static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, co
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  if ((pl.pair ? cudaLaunchKernelEx(&cfg, w8_gemm_kernel<true>, tm_w0, tm_w1, tm_x, p)
-               : cudaLaunchKernelEx(&cfg, w8_gemm_kernel<false>, tm_w0, tm_w1, tm_x, p)) != cudaSuccess)
+  if ((pl.pair         ? cudaLaunchKernelEx(&cfg, w8_gemm_kernel<true>, tm_w0, tm_w1, tm_x, p)
+       : pl.splits > 1 ? cudaLaunchKernelEx(&cfg, w8_gemm_kernel<false, EPI_WARPS_WIDE>, tm_w0, tm_w1, tm_x, p)
+                       : cudaLaunchKernelEx(&cfg, w8_gemm_kernel<false>, tm_w0, tm_w1, tm_x, p)) != cudaSuccess)
     return host::fail_cuda("launch w8_gemm_kernel");
   host::count_launch();
   return TYBOK_OK;
