@@ -848,7 +848,9 @@ static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, co
 
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = pl.pair ? dim3(pl.n_tiles, pl.t_tiles, 1) : dim3(pl.t_tiles, pl.n_tiles, pl.splits);
-  cfg.blockDim = dim3(pl.splits > 1 ? THREADS_WIDE : THREADS);
+  // sixteen epilogue warps wherever a CTA has its SM to itself: split-K, and full-K grids of one wave
+  const bool wide = !pl.pair && (pl.splits > 1 || pl.t_tiles * pl.n_tiles <= host::sm_count());
+  cfg.blockDim = dim3(wide ? THREADS_WIDE : THREADS);
   cfg.dynamicSmemBytes = pl.smem_bytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -868,7 +870,7 @@ static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, co
   cfg.attrs = attr;
   cfg.numAttrs = na;
   if ((pl.pair         ? cudaLaunchKernelEx(&cfg, w8_gemm_kernel<true>, tm_w0, tm_w1, tm_x, p)
-       : pl.splits > 1 ? cudaLaunchKernelEx(&cfg, w8_gemm_kernel<false, EPI_WARPS_WIDE>, tm_w0, tm_w1, tm_x, p)
+       : wide          ? cudaLaunchKernelEx(&cfg, w8_gemm_kernel<false, EPI_WARPS_WIDE>, tm_w0, tm_w1, tm_x, p)
                        : cudaLaunchKernelEx(&cfg, w8_gemm_kernel<false>, tm_w0, tm_w1, tm_x, p)) != cudaSuccess)
     return host::fail_cuda("launch w8_gemm_kernel");
   host::count_launch();
