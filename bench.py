@@ -165,7 +165,7 @@ def _gemm_roofline(engine, peaks, peaks_kind) -> dict:
         # dram__bytes_read + write of one captured launch of the expert down projection (M=50, N=1024,
         # K=4096; profiles/w8_gemm_m50_n1024_k4096.md) against its 4,710,400 algorithmic bytes
         "traffic": NCU_TRAFFIC_DOWN_PROJ if (b * s.chunk, s.expert.width, s.expert.mlp_dim) == (50, 1024, 4096) else None,
-        "traffic_case": "M=50 N=1024 K=4096: 4858112 B measured (ncu) vs 4710400 B algorithmic per launch",
+        "traffic_case": "M=50 N=1024 K=4096: 4859136 B measured (ncu) vs 4710400 B algorithmic per launch",
         "peak_source": peaks_kind, "per_shape": strip(out["expert"]),
         "prefix": {"bound": "tensor", "achieved": round(tc, 1), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                    "frac": round(tc / peaks["bf16_tflops"], 4), "per_shape": strip(out["prefix"])},
