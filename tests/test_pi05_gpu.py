@@ -70,6 +70,27 @@ def test_small_policy_with_attention_kernel_matches_oracle(batch):
     assert w8_ref.rel_l2(out.cpu(), ref) <= 1e-2
 
 
+def test_chunk_does_not_depend_on_programmatic_dependent_launch():
+    """Every kernel is launched with programmatic stream serialisation and waits for its
+    predecessor itself; with that switched off (plain stream order) the chunk is bit for bit
+    the same."""
+    from tybok_b200 import _lib, ops
+
+    params, model = _tiny_model(PI05_SMALL)
+    images, img_masks, tokens, masks, noise = tiny_inputs(PI05_SMALL, seed=8, batch=2)
+    noise = torch.randn(noise.shape, generator=torch.Generator().manual_seed(2))
+    args = ([t.cuda() for t in images], [t.cuda() for t in img_masks], tokens.cuda(), masks.cuda(), noise.cuda())
+    with_pdl = model.sample_actions(*args).clone()
+    lib = _lib.load()
+    lib.tybok_set_pdl(0)
+    try:
+        without = model.sample_actions(*args).clone()
+    finally:
+        lib.tybok_set_pdl(1)
+    ops.check_status()
+    assert torch.equal(with_pdl, without)
+
+
 def test_tiny_policy_chunk_matches_oracle():
     from tybok_b200 import ops
 
