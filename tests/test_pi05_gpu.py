@@ -20,7 +20,8 @@ from tybok_b200.weights import quantize_hot_linears, random_pi05_params  # noqa:
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("m,w,ada", [(50, 1024, True), (544, 2048, False), (7, 128, True), (3, 4096, False)])
+@pytest.mark.parametrize("m,w,ada", [(50, 1024, True), (544, 2048, False), (7, 128, True), (3, 4096, False),
+                                     (9, 520, True), (33, 2056, False), (5, 264, True)])  # ragged row widths
 def test_rmsnorm_planes_and_bf16(m, w, ada):
     """tybok/policies/pi05/models/layers.py:51-84 on the GPU: bf16 output bit-exact up to one
     bf16 ulp of rounding-order difference, planes exactly equal to the bf16 output."""
