@@ -178,6 +178,11 @@ def _cpu_chunk_times(reps: int, seed: int = 0) -> tuple[list[float], dict]:
     from tybok_b200.shapes import PI05_FULL
     from tybok_b200.weights import quantize_hot_linears, random_pi05_params
 
+    # every host thread this process may use (a torchrun launch sets OMP_NUM_THREADS=1 for its ranks)
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except (AttributeError, RuntimeError):
+        torch.set_num_threads(max(1, os.cpu_count() or 1))
     dev = "cuda" if torch.cuda.is_available() else "cpu"  # weights are generated where it is fast
     params = quantize_hot_linears(random_pi05_params(PI05_FULL, seed=seed, device=dev), PI05_FULL)
     params = {k: v.cpu() for k, v in params.items()}
