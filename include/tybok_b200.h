@@ -98,7 +98,9 @@ int tybok_w8a16_geglu(const void* x, const void* w8_gate, const float* scale_gat
  * capture.  All calls share the one array, which keeps whatever the previous call left in it
  * (nothing needs clearing: each call overwrites every byte it later reads); two calls that can
  * overlap on the GPU (different streams, or graph branches) race on it -- serialise them.
- * Arguments as tybok_w8a16_linear, minus the workspace, token_tile and splits. */
+ * Arguments as tybok_w8a16_linear, minus the workspace, token_tile and splits: the token tile and
+ * the split-K factor are always chosen automatically (as token_tile = splits = 0 there).  A call
+ * that is refused (bad argument, too large) launches nothing and leaves the array untouched. */
 #define TYBOK_STATIC_PLANES_BYTES (3u * 128u * 4096u)
 int tybok_w8a16_linear_noalloc(const void* x, const void* w8, const float* scale, const void* bias, void* y, int M,
                                int N, int K, int64_t ldx, int64_t ldy, int epilogue, const void* residual,

@@ -10,13 +10,13 @@ pytestmark = pytest.mark.gpu
 D = 256
 
 
-def _tables(max_pos):
+def _tables(max_pos, D=D):
     pos = torch.arange(max_pos)[None]
     cos, sin = w8_ref.rope_cos_sin(pos, D, torch.bfloat16)
     return cos[0].contiguous(), sin[0].contiguous()
 
 
-def _reference(qkv, b, l, h, g, pos, prefix_k, prefix_v, key_valid):
+def _reference(qkv, b, l, h, g, pos, prefix_k, prefix_v, key_valid, D=D):
     """Oracle path: split, RoPE, concat with the prefix cache, eager attention with additive mask."""
     q = qkv[:, : h * D].view(b, l, h, D).transpose(1, 2)
     k = qkv[:, h * D : (h + g) * D].view(b, l, g, D).transpose(1, 2)
@@ -29,11 +29,17 @@ def _reference(qkv, b, l, h, g, pos, prefix_k, prefix_v, key_valid):
     return w8_ref.gqa_attention(q, kk, vv, mask, D**-0.5), k, v
 
 
-@pytest.mark.parametrize("b,l,lp,h,g", [(1, 50, 544, 8, 1), (2, 50, 300, 8, 1), (1, 544, 0, 8, 1), (2, 130, 0, 4, 2),
-                                        (1, 10, 968, 8, 1), (1, 7, 5, 2, 2),
-                                        # grids beyond one wave: each CTA works through several key blocks
-                                        (2, 544, 0, 8, 1), (2, 300, 400, 8, 1), (4, 130, 300, 8, 1), (1, 544, 480, 8, 1)])
-def test_attention_matches_oracle(b, l, lp, h, g):
+_CASES = [(1, 50, 544, 8, 1), (2, 50, 300, 8, 1), (1, 544, 0, 8, 1), (2, 130, 0, 4, 2), (1, 10, 968, 8, 1),
+          (1, 7, 5, 2, 2),
+          # grids beyond one wave: each CTA works through several key blocks
+          (2, 544, 0, 8, 1), (2, 300, 400, 8, 1), (4, 130, 300, 8, 1), (1, 544, 480, 8, 1)]
+
+
+@pytest.mark.parametrize("b,l,lp,h,g,D", [c + (256,) for c in _CASES] + [
+    # head_dim 128 (always the key-loop kernel): short suffixes over a prefix, prefill, MHA, many heads
+    (1, 50, 544, 8, 1, 128), (2, 10, 130, 2, 1, 128), (1, 7, 5, 2, 2, 128), (2, 130, 0, 4, 4, 128),
+    (1, 544, 480, 8, 1, 128), (1, 300, 0, 24, 24, 128), (3, 70, 129, 6, 6, 128)])
+def test_attention_matches_oracle(b, l, lp, h, g, D):
     from tybok_b200 import ops
 
     gen = torch.Generator().manual_seed(b * 1000 + l + lp)
@@ -49,7 +55,7 @@ def test_attention_matches_oracle(b, l, lp, h, g):
     if lp:
         prefix_k = torch.empty(b, g, lp, D).normal_(0, 1, generator=gen).to(torch.bfloat16)
         prefix_v = torch.empty(b, g, lp, D).normal_(0, 1, generator=gen).to(torch.bfloat16)
-    ref, rk, rv = _reference(qkv, b, l, h, g, pos, prefix_k, prefix_v, key_valid)
+    ref, rk, rv = _reference(qkv, b, l, h, g, pos, prefix_k, prefix_v, key_valid, D)
 
     lcap = lk + 3
     kc = torch.zeros(b, g, lcap, D, dtype=torch.bfloat16, device="cuda")
@@ -57,7 +63,7 @@ def test_attention_matches_oracle(b, l, lp, h, g):
     if lp:
         kc[:, :, :lp] = prefix_k.cuda()
         vc[:, :, :lp] = prefix_v.cuda()
-    cos, sin = _tables(lk + 8)
+    cos, sin = _tables(lk + 8, D)
     q = ops.rope_store(qkv.cuda(), pos.reshape(-1).int().cuda(), cos.cuda(), sin.cuda(), kc, vc, heads=h, key_off=lp)
     # RoPE uses the same bf16 operations as torch: the stored keys are bit-identical
     assert torch.equal(kc[:, :, lp:lk].cpu(), rk) and torch.equal(vc[:, :, lp:lk].cpu(), rv)
@@ -75,8 +81,9 @@ def test_attention_matches_oracle(b, l, lp, h, g):
     assert torch.equal(out2.cpu().view(b, l, h * D), out)
 
 
+@pytest.mark.parametrize("D", [256, 128])
 @pytest.mark.parametrize("pattern", ["rising", "one_late_spike", "masked_first_blocks"])
-def test_prefill_attention_rescales_when_the_row_maximum_grows(pattern):
+def test_prefill_attention_rescales_when_the_row_maximum_grows(pattern, D):
     """Long query sequences keep O in tensor memory and move a row's reference maximum only when a
     key block exceeds it by more than 2^8: keys whose scores grow block by block, a single late
     outlier, and leading key blocks without a valid key all take that rescale (against the oracle's
@@ -108,13 +115,14 @@ def test_prefill_attention_rescales_when_the_row_maximum_grows(pattern):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("b,l,h,g,k,key_off", [(1, 50, 8, 1, 1024, 544), (2, 10, 2, 1, 128, 130), (1, 130, 2, 2, 256, 0)])
-def test_qkv_rope_epilogue_matches_projection_then_rope_store(b, l, h, g, k, key_off):
+@pytest.mark.parametrize("b,l,h,g,k,key_off,d", [(1, 50, 8, 1, 1024, 544, 256), (2, 10, 2, 1, 128, 130, 256),
+                                                  (1, 130, 2, 2, 256, 0, 256), (2, 10, 2, 1, 128, 38, 128),
+                                                  (1, 130, 3, 3, 256, 0, 128)])
+def test_qkv_rope_epilogue_matches_projection_then_rope_store(b, l, h, g, k, key_off, d):
     """The projection with RoPE + KV store as its epilogue writes bit-for-bit what the plain
     projection followed by the rope_store kernel writes (same split count)."""
     from tybok_b200 import ops
 
-    d = 256
     dev = torch.device("cuda")
     gen = torch.Generator().manual_seed(5)
     w = torch.empty((h + 2 * g) * d, k).normal_(0, 0.02, generator=gen)
@@ -137,3 +145,32 @@ def test_qkv_rope_epilogue_matches_projection_then_rope_store(b, l, h, g, k, key
     assert torch.equal(q0, q1)
     assert torch.equal(caches[0], caches[2]) and torch.equal(caches[1], caches[3])
     assert w8_ref.rel_l2(q2.float().cpu(), q0.float().cpu()) < 2e-3  # other split count: fp32 summation order only
+
+
+def test_long_self_attention_at_head_dim_128():
+    """The DiT self-attention geometry at reduced head count: 4146 queries over 4146 keys (65 key
+    blocks per CTA, 33 query tiles), MHA, no mask, fp32-SDPA oracle as the reference's DiT block
+    uses it (tybok/policies/fastwam/models/dit_block.py:72-98); rel-L2 <= 1e-2."""
+    from tybok_b200 import ops
+
+    b, l, h, d = 1, 4146, 3, 128
+    gen = torch.Generator().manual_seed(23)
+    q = torch.empty(b * l, h * d).normal_(0, 1, generator=gen).to(torch.bfloat16)
+    k = torch.empty(b, h, l, d).normal_(0, 1, generator=gen).to(torch.bfloat16)
+    v = torch.empty(b, h, l, d).normal_(0, 1, generator=gen).to(torch.bfloat16)
+    ref = torch.nn.functional.scaled_dot_product_attention(q.view(b, l, h, d).transpose(1, 2).float(), k.float(), v.float())
+    ref = ref.transpose(1, 2).reshape(b, l, h * d)
+    out, _ = ops.attention(q.cuda(), k.cuda(), v.cuda(), None, tokens=l, keys=l, scale=d**-0.5)
+    ops.check_status()
+    out = out.cpu().view(b, l, h * d)
+    assert torch.isfinite(out.float()).all()
+    assert w8_ref.rel_l2(out.float(), ref) <= 1e-2
+
+
+def test_attention_refuses_other_head_sizes():
+    from tybok_b200 import _lib, ops
+
+    q = torch.zeros(4, 2 * 64, dtype=torch.bfloat16, device="cuda")
+    kc = torch.zeros(1, 2, 8, 64, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(_lib.TybokError, match="head_dim must be 128 or 256"):
+        ops.attention(q, kc, kc.clone(), None, tokens=4, keys=4, scale=0.125)

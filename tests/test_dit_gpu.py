@@ -1,4 +1,4 @@
-"""DiT FFN tail (BASELINE config 3 geometry: hidden 3072, ffn 14336) against the oracle, single
+"""DiT FFN tail (fastWAM-class geometry: hidden 3072, ffn 14336) against the oracle, single
 rank and tensor-parallel (ranks emulated on one GPU: each shard's partial is computed in turn and
 the partials are summed as the all-reduce would).  Tolerance rel-L2 <= 1e-2."""
 

@@ -1,6 +1,6 @@
 """W8A16 linear / gated FFN front half on the GPU against the CPU oracle.
 
-Tolerance (BASELINE north_star): rel-L2 <= 1e-2 on bf16 outputs.  The kernel multiplies the
+Tolerance: rel-L2 <= 1e-2 on bf16 outputs.  The kernel multiplies the
 exact e4m3 weights with the exact bf16 activations and applies the per-channel scale to the
 fp32 accumulator; the oracle rounds ``w8*scale`` to bf16 per weight before the GEMM.  That
 difference measures ~2.6e-3 rel-L2.
@@ -159,6 +159,30 @@ def test_planes_in_planes_out_chain():
     got, want = hp.cpu().view(torch.float8_e5m2).float().sum(0), h.cpu().float() * 64.0
     inside = want.abs() >= 2.0**-7
     assert torch.equal(got[inside], want[inside]) and float((got - want).abs().max()) <= 2.0**-17 + 2.0**-24
+
+
+@pytest.mark.parametrize("m,k,i", [(50, 1024, 4096), (544, 2048, 16384)])
+def test_ffn_chain_at_the_model_shapes(m, k, i):
+    """The gated FFN exactly as a decoder layer of the full policy runs it -- packed gate/up GEMM
+    writing planes, down projection with the residual epilogue -- at the action-expert shape
+    (50 tokens, 1024 -> 4096 -> 1024) and the prefix shape (544 tokens, 2048 -> 16384 -> 2048),
+    against ``x + GemmaMLP(x)`` of the oracle (tybok/policies/pi05/models/layers.py:87-95,295-308)."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(31)
+    x = torch.empty(m, k).normal_(0, 1, generator=g).to(torch.bfloat16)
+    res = torch.empty(m, k).normal_(0, 1, generator=g).to(torch.bfloat16)
+    gate, up, down = (w8_ref.quantize_w8(torch.empty(s).normal_(0, 0.02, generator=g)) for s in ((i, k), (i, k), (k, i)))
+    mlp = w8_ref.gemma_mlp(x, gate, up, down)
+    ref = res + mlp
+    cu = lambda t: tuple(a.cuda() for a in t)  # noqa: E731
+    packed = ops.pack_gate_up(*cu(gate), *cu(up))
+    xp = ops.split3(x.cuda(), 4)
+    _, hp = ops.w8x3_geglu_packed(xp, 4, *packed, out_bf16=False, out_planes=True, out_shift=4)
+    y, _ = ops.w8x3_linear(hp, 4, *cu(down), epilogue=ops.EPI_RESIDUAL, residual=res.cuda())
+    ops.check_status()
+    # the tolerance applies to the FFN output; the residual only changes the last rounding
+    assert w8_ref.rel_l2(y.cpu().float() - res.float(), mlp.float()) <= TOL
+    assert w8_ref.rel_l2(y.cpu(), ref) <= TOL
 
 
 def test_c_abi_bf16_entry_point_with_workspace():

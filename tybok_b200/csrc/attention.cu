@@ -12,12 +12,13 @@
 //              tensor memory and V as an MN-major shared-memory operand.
 //   warps 2-9  softmax on S straight out of tensor memory (two threads per query row, 64 keys
 //              each, fp32, key-validity mask), P written back to tensor memory as bf16; epilogue.
-// The key blocks of one query tile form a thread-block cluster: each CTA writes its un-normalised
-// O rows (one bulk copy out of shared memory) and its (max, sum) row statistics to a workspace
-// in global memory, the cluster meets at a hardware barrier, and CTA r merges query rows
-// r*R..(r+1)*R-1 over all key blocks in block order out of L2 (bit-reproducible).  Distributed
-// shared memory moves about 20 bytes per clock and SM (measured), L2 several times that, which
-// is why the exchange does not go through the peers' shared memory.
+// The key blocks of one query tile form a thread-block cluster and CTA r merges query rows
+// r*R..(r+1)*R-1 over all key blocks in block order (bit-reproducible).  Two exchange forms:
+// short suffixes in the split-column form push every partial row straight into the shared
+// memory of the CTA that merges it (bulk copies credited to the receiver's barrier); everything
+// else stages its rows in a global workspace that stays in L2, meets at the cluster barrier
+// and pulls.  Sequences of more than 128 queries, and every head_dim 128 call, take the
+// key-loop kernel further down, which exchanges nothing.
 //
 // Algorithmic bytes: Q + O once per (layer, step), K + V once per (batch, kv head).
 // Flops: 4 * Mq * Lk * D * H.
@@ -685,8 +686,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 // All eight epilogue warps normalise and write the output at the end.
 constexpr int PF_BK = 64;                    // keys per block
 constexpr int PF_KCHUNK = PF_BK * 128;       // one 64-column chunk of a K or V block
-constexpr int PF_KV = 4 * PF_KCHUNK;         // one K or V block: 32 KB
-constexpr int PF_MAX_KEYS = 4096;
+constexpr int PF_MAX_KEYS = 8192;
+// Shared memory of the key-loop kernel: the Q tile and two K and two V blocks, D / 64 chunks each.
+constexpr int pf_smem(int d) { return (d / 64) * (AT_CHUNK + 4 * PF_KCHUNK) + 1024; }
 constexpr float PF_RESCALE = 8.0f;
 // 2^x by the special-function unit alone (results below 2^-126 flush to zero).
 __device__ __forceinline__ float pf_exp2(float x) {
@@ -709,16 +711,24 @@ struct __align__(8) PrefillBars {
   float hsum[2][AT_BQ];     // [half][row]: sum of that half's probabilities over all blocks
 };
 
-__global__ void __launch_bounds__(AT_THREADS, 1)
+// HD = head dimension, 128 or 256.  With 128 two CTAs share an SM (96 KB of shared memory and 256
+// tensor-memory columns each), so one tile's softmax runs under the other's products.
+template <int HD>
+__global__ void __launch_bounds__(AT_THREADS, HD == 128 ? 2 : 1)
 attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                          const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ PrefillBars bars;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int NCH = HD / 64;              // 64-column chunks of a Q, K or V row
+  constexpr int PF_KV = NCH * PF_KCHUNK;    // one K or V block: 64 keys x HD
+  constexpr int Q_TILE = NCH * AT_CHUNK;    // 128 query rows x HD
+  constexpr int T_COLS = HD == 256 ? 512 : 256;  // tensor memory: S / P at columns 0 and 64, O behind them
+  constexpr int OCH = HD / 64;              // 32-column chunks of O per thread (its half of the row)
   uint8_t* sq = smem;
-  uint8_t* sk = smem + AT_TILE;             // two K blocks
-  uint8_t* sv = smem + AT_TILE + 2 * PF_KV;  // two V blocks
+  uint8_t* sk = smem + Q_TILE;               // two K blocks
+  uint8_t* sv = smem + Q_TILE + 2 * PF_KV;   // two V blocks
 
   const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int g = h / (p.H / p.G);
@@ -744,7 +754,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
     fence_barrier_init();
   }
   if (warp == 1) {
-    tmem_alloc(&bars.tmem_base, 512);
+    tmem_alloc(&bars.tmem_base, T_COLS);
     tmem_relinquish();
   }
   if (warp >= 2 && warp < 6) {  // validity bits of every key, 32 per word
@@ -761,7 +771,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bars.tmem_base;
-  const uint32_t t_o = tmem + 256;  // S_j (and P_j over it) at columns 64 * (j & 1)
+  const uint32_t t_o = tmem + (HD == 256 ? 256 : 128);  // S_j (and P_j over it) at columns 64 * (j & 1)
   long long* tr = p.trace ? p.trace + 16ll * ((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) : nullptr;
   const long long t_start = clock64();
   if (tr && tid == 0) tr[0] = t_start;
@@ -770,25 +780,25 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
     if (lane == 0) {
       if (p.pdl) pdl_launch_dependents();
       if (p.pdl) pdl_wait();
-      mbar_arrive_expect_tx(&bars.q_full, AT_TILE);
-      for (int c = 0; c < 4; ++c) tma_load_2d(sq + c * AT_CHUNK, &tm_q, &bars.q_full, h * AT_D + c * 64, b * p.L + qt * AT_BQ);
+      mbar_arrive_expect_tx(&bars.q_full, Q_TILE);
+      for (int c = 0; c < NCH; ++c) tma_load_2d(sq + c * AT_CHUNK, &tm_q, &bars.q_full, h * HD + c * 64, b * p.L + qt * AT_BQ);
       for (int j = 0; j < nkb; ++j) {
         const int s = j & 1;
         const uint32_t par = ((j >> 1) & 1) ^ 1;  // the ring slot's previous use
         const int krow = (b * p.G + g) * p.Lcap + j * PF_BK;
         if (j >= 2 && !at_wait(&bars.k_empty[s], par, &bars.abort)) break;
         mbar_arrive_expect_tx(&bars.k_full[s], PF_KV);
-        for (int c = 0; c < 4; ++c) tma_load_2d(sk + s * PF_KV + c * PF_KCHUNK, &tm_k, &bars.k_full[s], c * 64, krow);
+        for (int c = 0; c < NCH; ++c) tma_load_2d(sk + s * PF_KV + c * PF_KCHUNK, &tm_k, &bars.k_full[s], c * 64, krow);
         if (j >= 2 && !at_wait(&bars.v_empty[s], par, &bars.abort)) break;
         mbar_arrive_expect_tx(&bars.v_full[s], PF_KV);
-        for (int c = 0; c < 4; ++c) tma_load_2d(sv + s * PF_KV + c * PF_KCHUNK, &tm_v, &bars.v_full[s], c * 64, krow);
+        for (int c = 0; c < NCH; ++c) tma_load_2d(sv + s * PF_KV + c * PF_KCHUNK, &tm_v, &bars.v_full[s], c * 64, krow);
       }
     }
   } else if (warp == 1) {
     const bool leader = elect_one();
     const uint64_t dk = smem_desc_sw128(0);
     const uint32_t idesc_s = idesc_bf16_f32(AT_BQ, PF_BK);
-    const uint32_t idesc_o = idesc_bf16_f32(AT_BQ, AT_D) | (1u << 16);
+    const uint32_t idesc_o = idesc_bf16_f32(AT_BQ, HD) | (1u << 16);
     const uint32_t q16 = (smem_u32(sq) & 0x3FFFFu) >> 4;
     bool ok = __all_sync(0xffffffffu, at_wait(&bars.q_full, 0, &bars.abort));
     auto issue_s = [&](int j) {  // S_j = Q K_j^T into columns 64 * (j & 1); frees the K slot when done
@@ -798,7 +808,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
       tc_fence_after();
       const uint32_t k16 = (smem_u32(sk + s * PF_KV) & 0x3FFFFu) >> 4;
 #pragma unroll
-      for (int ks = 0; ks < 16; ++ks) {  // D = 256 in steps of 16: chunk ks / 4, 32 bytes per step
+      for (int ks = 0; ks < HD / 16; ++ks) {  // the head dimension in steps of 16: chunk ks / 4, 32 bytes per step
         const uint32_t qo = (ks >> 2) * (AT_CHUNK >> 4) + (ks & 3) * 2, ko = (ks >> 2) * (PF_KCHUNK >> 4) + (ks & 3) * 2;
         if (leader) umma_ss_bf16(tmem + s * 64, dk | (q16 + qo), dk | (k16 + ko), idesc_s, ks > 0 ? 1u : 0u);
       }
@@ -894,7 +904,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
               tc_fence_after();
               const float f = grow ? pf_exp2(m_ref - m_blk) : 1.0f;
 #pragma unroll 1
-              for (int c = hf * 4; c < hf * 4 + 4; ++c) {
+              for (int c = hf * OCH; c < hf * OCH + OCH; ++c) {
                 uint32_t o[32];
                 tmem_ld32(t_o + lane_addr + c * 32, o);
                 tc_wait_ld();
@@ -956,7 +966,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
     if (tr && tid == 128) tr[13] = clock64();
     tc_fence_before();
     asm volatile("bar.sync 1, 256;" ::: "memory");
-    constexpr int OB = AT_D * 2 + 16, OP = AT_D + 16;  // padded row pitches
+    constexpr int OB = HD * 2 + 16, OP = HD + 16;  // padded row pitches
     uint8_t* so = smem;
     uint8_t* sp = smem + AT_BQ * OB;
     const bool good = !bars.abort;
@@ -965,7 +975,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
       const float ls = bars.hsum[0][row] + bars.hsum[1][row];
       const float inv = ls > 0.f ? 1.0f / ls : 0.f;
 #pragma unroll 1
-      for (int c = hf * 4; c < hf * 4 + 4; ++c) {
+      for (int c = hf * OCH; c < hf * OCH + OCH; ++c) {
         uint32_t o[32];
         tmem_ld32(t_o + lane_addr + c * 32, o);
         tc_wait_ld();
@@ -993,18 +1003,28 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
     if (tr && tid == 128) tr[15] = clock64();
     asm volatile("bar.sync 1, 256;" ::: "memory");
     if (good) {
-      // one warp per row: 32 lanes x 16 bytes of bf16, 32 lanes x 8 bytes of every plane
-      const long long hd = static_cast<long long>(p.H) * AT_D;
+      // one warp per row: every lane moves HD / 32 elements of the bf16 row and of every plane
+      const long long hd = static_cast<long long>(p.H) * HD;
       const long long plane = static_cast<long long>(p.B) * p.L * hd;
 #pragma unroll 2
       for (int r = warp - 2; r < nvalid; r += 8) {
-        const long long off = (static_cast<long long>(b) * p.L + qt * AT_BQ + r) * hd + static_cast<long long>(h) * AT_D;
-        if (p.out) *reinterpret_cast<uint4*>(p.out + off + lane * 8) = *reinterpret_cast<const uint4*>(so + r * OB + lane * 16);
-        if (p.out_planes) {
-          uint8_t* dst = p.out_planes + off + lane * 8;
-          *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(sp + r * OP + lane * 8);
-          *reinterpret_cast<uint2*>(dst + plane) = *reinterpret_cast<const uint2*>(sp + (AT_BQ + r) * OP + lane * 8);
-          *reinterpret_cast<uint2*>(dst + 2 * plane) = *reinterpret_cast<const uint2*>(sp + (2 * AT_BQ + r) * OP + lane * 8);
+        const long long off = (static_cast<long long>(b) * p.L + qt * AT_BQ + r) * hd + static_cast<long long>(h) * HD;
+        if (HD == 256) {
+          if (p.out) *reinterpret_cast<uint4*>(p.out + off + lane * 8) = *reinterpret_cast<const uint4*>(so + r * OB + lane * 16);
+          if (p.out_planes) {
+            uint8_t* dst = p.out_planes + off + lane * 8;
+            *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(sp + r * OP + lane * 8);
+            *reinterpret_cast<uint2*>(dst + plane) = *reinterpret_cast<const uint2*>(sp + (AT_BQ + r) * OP + lane * 8);
+            *reinterpret_cast<uint2*>(dst + 2 * plane) = *reinterpret_cast<const uint2*>(sp + (2 * AT_BQ + r) * OP + lane * 8);
+          }
+        } else {
+          if (p.out) *reinterpret_cast<uint2*>(p.out + off + lane * 4) = *reinterpret_cast<const uint2*>(so + r * OB + lane * 8);
+          if (p.out_planes) {
+            uint8_t* dst = p.out_planes + off + lane * 4;
+            *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(sp + r * OP + lane * 4);
+            *reinterpret_cast<uint32_t*>(dst + plane) = *reinterpret_cast<const uint32_t*>(sp + (AT_BQ + r) * OP + lane * 4);
+            *reinterpret_cast<uint32_t*>(dst + 2 * plane) = *reinterpret_cast<const uint32_t*>(sp + (2 * AT_BQ + r) * OP + lane * 4);
+          }
         }
       }
     }
@@ -1014,7 +1034,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem, 512);
+    tmem_dealloc(tmem, T_COLS);
   }
 }
 
@@ -1057,7 +1077,7 @@ int tybok_rope_store(const void* qkv, int64_t ldq, const int* pos, const void* c
 size_t tybok_attention_workspace_bytes(int B, int L, int H, int Lk) {
   using namespace tb;
   if (B <= 0 || L <= 0 || H <= 0 || Lk <= AT_BK) return 0;  // a single key block merges inside its CTA
-  if (L > AT_BQ && Lk <= PF_MAX_KEYS) return 0;             // the prefill form exchanges nothing
+  if (L > AT_BQ && Lk <= PF_MAX_KEYS) return 0;             // the key-loop form exchanges nothing
   const size_t nsplit = (static_cast<size_t>(Lk) + AT_BK - 1) / AT_BK, n_qt = (static_cast<size_t>(L) + AT_BQ - 1) / AT_BQ;
   return 2 * nsplit * n_qt * H * B * AT_WS_PER_CTA;  // room for the split-column form of small grids
 }
@@ -1067,26 +1087,28 @@ int tybok_attention(const void* q, const void* k_cache, const void* v_cache, con
                     void* workspace, size_t workspace_bytes, int* status_word, void* stream) {
   using namespace tb;
   if (!q || !k_cache || !v_cache || (!out && !out_planes)) return host::fail(TYBOK_ERR_ARG, "attention: null pointer argument");
-  if (D != AT_D) return host::fail(TYBOK_ERR_ARG, "attention: this kernel is built for head_dim 256");
+  if (D != AT_D && D != 128) return host::fail(TYBOK_ERR_ARG, "attention: head_dim must be 128 or 256");
   if (B <= 0 || L <= 0 || H <= 0 || G <= 0 || H % G != 0 || Lk <= 0 || Lk > Lcap)
     return host::fail(TYBOK_ERR_ARG, "attention: bad shape (H % G == 0, 0 < Lk <= Lcap)");
   const int nsplit = (Lk + AT_BK - 1) / AT_BK;
-  const bool prefill = L > AT_BQ && Lk <= PF_MAX_KEYS;  // several query tiles: the key-loop form
+  // several query tiles, or head_dim 128: the key-loop form
+  const bool prefill = (L > AT_BQ || D == 128) && Lk <= PF_MAX_KEYS;
+  if (D == 128 && !prefill) return host::fail(TYBOK_ERR_ARG, "attention: at most 8192 keys at head_dim 128");
   if (!prefill && nsplit > AT_MAX_SPLITS)
     return host::fail(TYBOK_ERR_ARG, "attention: at most 1024 keys (8 blocks of 128 per cluster) for up to 128 queries, "
-                                     "4096 keys beyond");
+                                     "8192 keys beyond");
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
        reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(out_planes)) & 15)
     return host::fail(TYBOK_ERR_ARG, "attention: tensors must be 16-byte aligned");
   if (out_shift < -60 || out_shift > 60) return host::fail(TYBOK_ERR_ARG, "attention: exponent shift out of range");
-  const size_t need = tybok_attention_workspace_bytes(B, L, H, Lk);
+  const size_t need = prefill ? 0 : tybok_attention_workspace_bytes(B, L, H, Lk);
   if (need && (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15)))
     return host::fail(TYBOK_ERR_WORKSPACE, "attention: workspace must hold tybok_attention_workspace_bytes(), 16-byte aligned");
   if (int rc = host::require_sm100()) return rc;
 
   CUtensorMap tm_q, tm_k, tm_v;
   const uint64_t hd = static_cast<uint64_t>(H) * D;
-  const int q_rows = L <= 64 ? 64 : AT_BQ;  // short suffixes: half the query tile is enough
+  const int q_rows = (L <= 64 && !prefill) ? 64 : AT_BQ;  // short suffixes: half the query tile is enough
   if (int rc = host::tensor_map_2d(&tm_q, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, hd, static_cast<uint64_t>(B) * L, hd * 2, 64, q_rows))
     return rc;
   const uint64_t krows = static_cast<uint64_t>(B) * G * Lcap;
@@ -1116,14 +1138,15 @@ int tybok_attention(const void* q, const void* k_cache, const void* v_cache, con
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
     if (cudaFuncSetAttribute(attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM) != cudaSuccess ||
         cudaFuncSetAttribute(attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM) != cudaSuccess ||
-        cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM) != cudaSuccess)
+        cudaFuncSetAttribute(attention_prefill_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, pf_smem(256)) != cudaSuccess ||
+        cudaFuncSetAttribute(attention_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, pf_smem(128)) != cudaSuccess)
       return host::fail_cuda("cudaFuncSetAttribute(attention_kernel)");
     attr_set[dev] = true;
   }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = prefill ? dim3(n_qt, H, B) : dim3(nsplit, H * n_qt * p.dsplit, B);
   cfg.blockDim = dim3(AT_THREADS);
-  cfg.dynamicSmemBytes = AT_SMEM;
+  cfg.dynamicSmemBytes = prefill ? pf_smem(D) : AT_SMEM;
   cfg.stream = static_cast<cudaStream_t>(stream);
   cudaLaunchAttribute attr[2];
   int na = 0;
@@ -1141,7 +1164,8 @@ int tybok_attention(const void* q, const void* k_cache, const void* v_cache, con
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  if (cudaLaunchKernelEx(&cfg, prefill ? attention_prefill_kernel : push ? attention_kernel<true> : attention_kernel<false>,
+  if (cudaLaunchKernelEx(&cfg, prefill ? (D == 128 ? attention_prefill_kernel<128> : attention_prefill_kernel<256>)
+                                       : push ? attention_kernel<true> : attention_kernel<false>,
                          tm_q, tm_k, tm_v, p) != cudaSuccess)
     return host::fail_cuda("launch attention_kernel");
   host::count_launch();

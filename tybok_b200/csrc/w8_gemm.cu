@@ -31,6 +31,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -781,7 +782,7 @@ static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, co
                        const void* bias, void* y, void* y_planes, int M, int N, int K, long long ldy, int epi,
                        const void* res, long long ldres, const void* gate, long long ldgate, int rows_per_gate,
                        int gate_bf16, int x_shift, int out_shift, int force_bt, int force_splits, int* status,
-                       cudaStream_t stream, const RopeEpi* rope = nullptr) {
+                       cudaStream_t stream, const RopeEpi* rope = nullptr, bool check_only = false) {
   const int nw = w1 ? 2 : 1;
   if (!planes || !w0 || !s0 || (!y && !y_planes && !rope)) return host::fail(TYBOK_ERR_ARG, "w8 gemm: null pointer argument");
   if (M <= 0 || N <= 0 || K <= 0) return host::fail(TYBOK_ERR_ARG, "w8 gemm: M, N, K must be positive");
@@ -808,6 +809,7 @@ static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, co
     return host::fail(TYBOK_ERR_ARG, "w8 gemm: unsupported token tile (multiple of 16, <= 256, <= 128 when gated)");
   if (force_splits > MAX_SPLITS) return host::fail(TYBOK_ERR_ARG, "w8 gemm: at most 8 K splits (cluster size)");
   if ((pl.pair ? pl.t_tiles : pl.n_tiles) > 65535) return host::fail(TYBOK_ERR_ARG, "w8 gemm: grid too large");
+  if (check_only) return TYBOK_OK;  // every argument check has passed; nothing was launched
 
   CUtensorMap tm_w0, tm_w1, tm_x;
   if (int rc = host::tensor_map_2d(&tm_w0, w0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, N, K, BK, BN)) return rc;
@@ -905,6 +907,19 @@ static int launch_split3(const void* x, long long ldx, void* planes, int M, int 
   return TYBOK_OK;
 }
 
+// The argument checks of tybok_w8x3_linear without its launch (for the two-launch entry points,
+// which must not start their first kernel when the second would be refused).
+static int check_linear_args(const void* planes, const void* w8, const float* scale, const void* bias, void* y,
+                             long long ldy, int M, int N, int K, int epilogue, const void* residual, long long ldres,
+                             const void* gate, long long ldgate, int rows_per_gate, int gate_is_bf16, int token_tile,
+                             int splits) {
+  if (epilogue != TYBOK_EPI_NONE && epilogue != TYBOK_EPI_GELU && epilogue != TYBOK_EPI_RESIDUAL)
+    return host::fail(TYBOK_ERR_ARG, "w8x3_linear: unknown epilogue");
+  return launch_gemm(static_cast<const uint8_t*>(planes), w8, nullptr, scale, nullptr, bias, y, nullptr, M, N, K, ldy,
+                     epilogue, residual, ldres, gate, ldgate, rows_per_gate, gate_is_bf16, TYBOK_DEFAULT_X_SHIFT, 0,
+                     token_tile, splits, nullptr, nullptr, nullptr, true);
+}
+
 }  // namespace tb
 
 extern "C" {
@@ -975,6 +990,10 @@ int tybok_w8a16_linear(const void* x, const void* w8, const float* scale, const 
   if (!workspace || workspace_bytes < tybok_w8a16_workspace_bytes(M, N, K, 0))
     return tb::host::fail(TYBOK_ERR_WORKSPACE, "w8a16_linear: workspace must hold 3*M*K bytes of activation planes");
   const int shift = TYBOK_DEFAULT_X_SHIFT;
+  // Refuse a bad GEMM argument before the split kernel has written anything.
+  if (int rc = tb::check_linear_args(workspace, w8, scale, bias, y, ldy, M, N, K, epilogue, residual, ldres, gate, ldgate,
+                                     rows_per_gate, gate_is_bf16, token_tile, splits))
+    return rc;
   if (int rc = tybok_split3(x, ldx, workspace, M, K, shift, stream)) return rc;
   return tybok_w8x3_linear(workspace, shift, w8, scale, bias, y, ldy, nullptr, 0, M, N, K, epilogue, residual, ldres,
                            gate, ldgate, rows_per_gate, gate_is_bf16, token_tile, splits, status_word, stream);
@@ -993,22 +1012,22 @@ static __device__ __align__(256) uint8_t g_static_planes[TYBOK_STATIC_PLANES_BYT
 // that name is only a stand-in for the symbol.  Its device address is looked up once per
 // device, with that device current.
 static void* static_planes_ptr(int* rc) {
-  static void* ptr[64] = {};
+  static std::atomic<void*> ptr[64];  // zero-initialised; two threads racing on a first call store the same address
   *rc = TYBOK_OK;
   const int dev = tb::host::current_device();
   if (dev < 0 || dev >= 64) {
     *rc = tb::host::fail(TYBOK_ERR_CUDA, "w8a16_linear_noalloc: no current CUDA device");
     return nullptr;
   }
-  if (!ptr[dev]) {
-    void* p = nullptr;
+  void* p = ptr[dev].load(std::memory_order_acquire);
+  if (!p) {
     if (cudaGetSymbolAddress(&p, g_static_planes) != cudaSuccess || !p) {
       *rc = tb::host::fail_cuda("w8a16_linear_noalloc: cudaGetSymbolAddress(g_static_planes)");
       return nullptr;
     }
-    ptr[dev] = p;
+    ptr[dev].store(p, std::memory_order_release);
   }
-  return ptr[dev];
+  return p;
 }
 
 int tybok_w8a16_linear_noalloc(const void* x, const void* w8, const float* scale, const void* bias, void* y, int M,
@@ -1026,6 +1045,10 @@ int tybok_w8a16_linear_noalloc(const void* x, const void* w8, const float* scale
   if (!planes) return rc;
   // Nothing in the array has to start at zero: split3 overwrites all 3*M*K bytes the GEMM reads.
   const int shift = TYBOK_DEFAULT_X_SHIFT;
+  // A call the GEMM would refuse must leave the shared array as it found it.
+  if (int r = tb::check_linear_args(planes, w8, scale, bias, y, ldy, M, N, K, epilogue, residual, ldres, gate, ldgate,
+                                    rows_per_gate, gate_is_bf16, 0, 0))
+    return r;
   if (int r = tybok_split3(x, ldx, planes, M, K, shift, stream)) return r;
   return tybok_w8x3_linear(planes, shift, w8, scale, bias, y, ldy, nullptr, 0, M, N, K, epilogue, residual, ldres,
                            gate, ldgate, rows_per_gate, gate_is_bf16, 0, 0, status_word, stream);
@@ -1037,6 +1060,11 @@ int tybok_w8a16_geglu(const void* x, const void* w8_gate, const float* scale_gat
   if (!workspace || workspace_bytes < tybok_w8a16_workspace_bytes(M, I, K, 1))
     return tb::host::fail(TYBOK_ERR_WORKSPACE, "w8a16_geglu: workspace must hold 3*M*K bytes of activation planes");
   const int shift = TYBOK_DEFAULT_X_SHIFT;
+  if (!w8_up || !scale_up) return tb::host::fail(TYBOK_ERR_ARG, "w8a16_geglu: null up-projection");
+  if (int rc = tb::launch_gemm(static_cast<const uint8_t*>(workspace), w8_gate, w8_up, scale_gate, scale_up, nullptr, h,
+                               nullptr, M, I, K, ldh, tb::EPI_GEGLU, nullptr, 0, nullptr, 0, 1, 0, shift, 0, token_tile,
+                               splits, nullptr, nullptr, nullptr, true))
+    return rc;
   if (int rc = tybok_split3(x, ldx, workspace, M, K, shift, stream)) return rc;
   return tybok_w8x3_geglu(workspace, shift, w8_gate, scale_gate, w8_up, scale_up, h, ldh, nullptr, 0, M, I, K,
                           token_tile, splits, status_word, stream);

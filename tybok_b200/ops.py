@@ -229,7 +229,8 @@ def _attention_cuda(q, k_cache, v_cache, key_valid, tokens, keys, scale, out_bf1
                                   or not key_valid.is_contiguous()):
         raise TypeError("attention: key_valid must be contiguous uint8 [B, Lk]")
     y, yp = _outputs(b * tokens, h * d, q.device, out_bf16, out_planes)
-    need = int(lib.tybok_attention_workspace_bytes(b, int(tokens), h, int(keys)))
+    # head_dim 128 always takes the key-loop kernel, which exchanges nothing
+    need = 0 if d == 128 else int(lib.tybok_attention_workspace_bytes(b, int(tokens), h, int(keys)))
     ws = torch.empty(need, dtype=torch.uint8, device=q.device) if need else None
     rc = lib.tybok_attention(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _ptr(key_valid),
                              y.data_ptr() if out_bf16 else None, yp.data_ptr() if out_planes else None, int(out_shift),

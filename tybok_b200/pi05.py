@@ -37,7 +37,7 @@ SHIFT_FFN = 4  # gelu(gate) * up
 class _Layer:
     """Packed weights of one Gemma decoder layer."""
 
-    __slots__ = ("qkv", "qkv_paired", "o", "gate", "up", "gate_up", "down", "norm_in", "norm_post")
+    __slots__ = ("qkv_paired", "o", "gate", "up", "gate_up", "down", "norm_in", "norm_post")
 
 
 def _q(params: dict, name: str, device) -> tuple[torch.Tensor, torch.Tensor]:
@@ -50,19 +50,16 @@ def _q(params: dict, name: str, device) -> tuple[torch.Tensor, torch.Tensor]:
     return w8, s
 
 
-def _pack_decoder(params: dict, root: str, spec: GemmaSpec, adarms: bool, device, pair_rope: bool) -> list[_Layer]:
+def _pack_decoder(params: dict, root: str, spec: GemmaSpec, adarms: bool, device) -> list[_Layer]:
     layers = []
     for i in range(spec.depth):
         base = f"{root}.layers.{i}"
         lay = _Layer()
         q, k, v = (_q(params, f"{base}.self_attn.{n}_proj", device) for n in ("q", "k", "v"))
-        lay.qkv = (torch.cat([q[0].view(torch.uint8), k[0].view(torch.uint8), v[0].view(torch.uint8)]).contiguous(),
-                   torch.cat([q[1], k[1], v[1]]).contiguous())
-        # head sizes the attention kernel takes: RoPE runs in the projection's epilogue on paired rows
-        lay.qkv_paired = None
-        if pair_rope:
-            lay.qkv_paired = ops.pair_qkv_rows(lay.qkv[0].view(torch.float8_e4m3fn), lay.qkv[1], spec.head_dim)
-            lay.qkv = None
+        qkv8 = torch.cat([q[0].view(torch.uint8), k[0].view(torch.uint8), v[0].view(torch.uint8)]).contiguous()
+        # RoPE runs in the projection's epilogue, on rows paired with their rotate-half partners
+        lay.qkv_paired = ops.pair_qkv_rows(qkv8.view(torch.float8_e4m3fn), torch.cat([q[1], k[1], v[1]]).contiguous(),
+                                           spec.head_dim)
         lay.o = _q(params, f"{base}.self_attn.o_proj", device)
         gate = _q(params, f"{base}.mlp.gate_proj", device)
         up = _q(params, f"{base}.mlp.up_proj", device)
@@ -93,18 +90,6 @@ def _rope_table(head_dim: int, max_pos: int, device) -> tuple[torch.Tensor, torc
     return emb.cos().to(torch.bfloat16), emb.sin().to(torch.bfloat16)
 
 
-def _additive(allowed: torch.Tensor) -> torch.Tensor:
-    """Boolean mask -> additive bf16 mask with the reference's large finite negative
-    (flow_matching.py:24,179-182): a fully masked (padding) query row then softmaxes to a
-    uniform, finite row instead of NaN, exactly as in the reference."""
-    return torch.where(allowed, 0.0, -2.3819763e38).to(torch.bfloat16)
-
-
-def _rotate_half(x: torch.Tensor) -> torch.Tensor:
-    h = x.shape[-1] // 2
-    return torch.cat((-x[..., h:], x[..., :h]), dim=-1)
-
-
 class PI05Model:
     """Weights + forward of a pi0.5-shaped policy on one GPU (inference only)."""
 
@@ -112,6 +97,12 @@ class PI05Model:
                  vision_dtype: torch.dtype = torch.bfloat16, overlap: bool = False):
         if not str(device).startswith("cuda"):
             raise RuntimeError("tybok_b200 has no CPU path: PI05Model needs a CUDA (sm_100) device")
+        hd = shape.vlm.head_dim
+        if hd not in (128, 256) or shape.expert.head_dim != hd:
+            raise ValueError(f"PI05Model: both decoder stacks need the same head_dim, 128 or 256 (the sizes the "
+                             f"attention kernels are built for); got {hd} and {shape.expert.head_dim}")
+        if shape.vlm.num_kv_heads != shape.expert.num_kv_heads:
+            raise ValueError("PI05Model: prefix and expert must have the same number of KV heads (shared caches)")
         self.shape = shape
         #: run the first denoise step layer by layer behind the prefix, on a second stream
         #: (flow_matching.py:609-720: expert layer l only needs the prefix keys of layer l)
@@ -126,9 +117,8 @@ class PI05Model:
         self.proj_b = params[f"{PROJECTOR}.bias"].to(dev, vision_dtype)
         self.embed = params[f"{VLM}.embed_tokens.weight"].to(dev)
         self.embed_scale = torch.tensor(shape.vlm.width**0.5, dtype=self.embed.dtype, device=dev)
-        self.fused_attention = shape.vlm.head_dim == 256 and shape.expert.head_dim == 256
-        self.vlm_layers = _pack_decoder(params, VLM, shape.vlm, False, dev, self.fused_attention)
-        self.exp_layers = _pack_decoder(params, EXPERT, shape.expert, True, dev, self.fused_attention)
+        self.vlm_layers = _pack_decoder(params, VLM, shape.vlm, False, dev)
+        self.exp_layers = _pack_decoder(params, EXPERT, shape.expert, True, dev)
         self.final_norm = (params[f"{EXPERT}.norm.dense.weight"].to(dev).float(),
                            params[f"{EXPERT}.norm.dense.bias"].to(dev).float())
         f32 = lambda n: params[n].to(dev).float()  # noqa: E731
@@ -137,9 +127,6 @@ class PI05Model:
         self.time_in = (f32("time_mlp_in.weight"), f32("time_mlp_in.bias"))
         self.time_out = (f32("time_mlp_out.weight"), f32("time_mlp_out.bias"))
         self.cos, self.sin = _rope_table(shape.vlm.head_dim, shape.prefix_len + shape.chunk + 8, dev)
-        # The tcgen05 attention kernel is built for head_dim 256 (both Gemma stacks of pi0.5);
-        # other head sizes use torch SDPA on the same caches.
-        self.fused_attention = shape.vlm.head_dim == 256 and shape.expert.head_dim == 256
         self._cache_by_batch: dict[int, list] = {}
         self._precompute_step_constants()
 
@@ -254,29 +241,6 @@ class PI05Model:
         return torch.cat(embs, dim=1), torch.cat(pads, dim=1)
 
     # ------------------------------------------------------------------ decoder pieces
-    def _rope(self, t: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
-        """t ``[B, L, H, D]`` bf16, pos ``[B, L]`` -> rotate-half RoPE in bf16 (rope.py:67-75)."""
-        cos = self.cos[pos][:, :, None, :]
-        sin = self.sin[pos][:, :, None, :]
-        return t * cos + _rotate_half(t) * sin
-
-    def _attention(self, spec: GemmaSpec, qkv: torch.Tensor, b: int, l: int, pos, mask, prefix_kv):
-        """Packed qkv ``[B*L, (H+2Hkv)*D]`` -> attention output ``[B*L, H*D]`` and this layer's
-        post-RoPE ``(K, V)`` ``[B, Hkv, L, D]``.  GQA over ``[prefix ; own]`` keys with a boolean
-        mask (layers.py:145-191).  torch SDPA: only used when the head size is not the 256 the
-        attention kernel of this package is built for."""
-        h, g, d = spec.num_heads, spec.num_kv_heads, spec.head_dim
-        qkv = qkv.view(b, l, h + 2 * g, d)
-        q = self._rope(qkv[:, :, :h], pos).transpose(1, 2)
-        k = self._rope(qkv[:, :, h : h + g], pos).transpose(1, 2)
-        v = qkv[:, :, h + g :].transpose(1, 2)
-        kk, vv = k, v
-        if prefix_kv is not None:
-            kk = torch.cat([prefix_kv[0], k], dim=2)
-            vv = torch.cat([prefix_kv[1], v], dim=2)
-        a = F.scaled_dot_product_attention(q, kk, vv, attn_mask=mask, scale=d**-0.5, enable_gqa=(g != h))
-        return a.transpose(1, 2).reshape(b * l, h * d), k, v
-
     def _caches(self, b: int):
         """Per-layer K/V caches ``[B, G, prefix_len + chunk, D]`` (zero-initialised once per batch
         size): the prefill writes keys [0, Lp), every expert layer-step rewrites [Lp, Lp + L)."""
@@ -290,7 +254,7 @@ class PI05Model:
             self._cache_by_batch[b] = c
         return c
 
-    def _layer(self, spec, lay: _Layer, x, b, l, pos, mask, cache, key_off, key_valid, mods):
+    def _layer(self, spec, lay: _Layer, x, b, l, pos, cache, key_off, key_valid, mods):
         """One decoder layer on ``x [B*L, W]`` bf16 (layers.py:268-308). ``mods`` is None for the
         VLM (plain norms) or ``(mod_in, mod_post)`` ``[1, 3W]`` AdaRMS modulations.  ``cache`` is
         this layer's ``(K, V)`` cache; the layer appends its keys at ``key_off``."""
@@ -302,18 +266,10 @@ class PI05Model:
         else:
             _, xp = ops.rmsnorm(x, mod=mods[0], rows_per_group=m, out_shift=SHIFT_NORMED)
             gate_in, gate_post = mods[0][:, 2 * w :], mods[1][:, 2 * w :]
-        if self.fused_attention:
-            q = ops.w8x3_qkv_rope(xp, SHIFT_NORMED, *lay.qkv_paired, pos, self.cos, self.sin, cache[0], cache[1],
-                                  heads=spec.num_heads, key_off=key_off)
-            _, ap = ops.attention(q, cache[0], cache[1], key_valid, tokens=l, keys=key_off + l,
-                                  scale=spec.head_dim**-0.5, out_bf16=False, out_planes=True, out_shift=SHIFT_ATTN)
-        else:
-            qkv, _ = ops.w8x3_linear(xp, SHIFT_NORMED, *lay.qkv)
-            prefix_kv = (cache[0][:, :, :key_off], cache[1][:, :, :key_off]) if key_off else None
-            a, k, v = self._attention(spec, qkv, b, l, pos.view(b, l).long(), mask, prefix_kv)
-            cache[0][:, :, key_off : key_off + l] = k
-            cache[1][:, :, key_off : key_off + l] = v
-            ap = ops.split3(a, SHIFT_ATTN)
+        q = ops.w8x3_qkv_rope(xp, SHIFT_NORMED, *lay.qkv_paired, pos, self.cos, self.sin, cache[0], cache[1],
+                              heads=spec.num_heads, key_off=key_off)
+        _, ap = ops.attention(q, cache[0], cache[1], key_valid, tokens=l, keys=key_off + l,
+                              scale=spec.head_dim**-0.5, out_bf16=False, out_planes=True, out_shift=SHIFT_ATTN)
         x, _ = ops.w8x3_linear(ap, SHIFT_ATTN, *lay.o, epilogue=ops.EPI_RESIDUAL, residual=x, gate=gate_in,
                                rows_per_gate=m)
         if mods is None:
@@ -337,12 +293,11 @@ class PI05Model:
         spec = self.shape.vlm
         b, l, w = prefix_embs.shape
         caches = self._caches(b)
-        mask = None if self.fused_attention else _additive(pad[:, None, :, None] & pad[:, None, None, :])
         pos = (torch.cumsum(pad, dim=1) - 1).clamp_min(0).to(torch.int32).reshape(-1)
         key_valid = pad.to(torch.uint8).contiguous()
         x = prefix_embs.reshape(b * l, w)
         for lay, cache in zip(self.vlm_layers, caches):
-            x = self._layer(spec, lay, x, b, l, pos, mask, cache, 0, key_valid, None)
+            x = self._layer(spec, lay, x, b, l, pos, cache, 0, key_valid, None)
             if layer_done is not None:
                 layer_done()
         return [(kc[:, :, :l], vc[:, :, :l]) for kc, vc in caches]
@@ -357,22 +312,21 @@ class PI05Model:
         caches = self._caches(b)
         x = F.linear(x_t, *self.action_in).to(torch.bfloat16).reshape(b * l, spec.width)
         allowed = torch.cat([pad, torch.ones(b, l, dtype=torch.bool, device=x.device)], dim=1)  # [B, Lp+L]
-        mask = None if self.fused_attention else _additive(allowed[:, None, None, :].expand(b, 1, l, lp + l))
         key_valid = allowed.to(torch.uint8).contiguous()
         pos = (pad.sum(dim=-1, keepdim=True) + torch.arange(l, device=x.device)[None, :]).to(torch.int32).reshape(-1)
         for i, lay in enumerate(self.exp_layers):
-            x = self._layer(spec, lay, x, b, l, pos, mask, caches[i], lp, key_valid, self.mods[step][i])
+            x = self._layer(spec, lay, x, b, l, pos, caches[i], lp, key_valid, self.mods[step][i])
         y, _ = ops.rmsnorm(x, mod=self.final_mods[step], rows_per_group=b * l, out_bf16=True, out_planes=False)
         y = y.view(b, l, spec.width)[:, -s.chunk :].float()
         return F.linear(y, *self.action_out)
 
-    def _expert_layers(self, step: int, h: torch.Tensor, b: int, l: int, pad: torch.Tensor, key_valid, pos, mask):
+    def _expert_layers(self, step: int, h: torch.Tensor, b: int, l: int, pad: torch.Tensor, key_valid, pos):
         """All expert layers of one denoise step on the suffix embedding ``h [B*L, W]``."""
         caches = self._caches(b)
         lp = pad.shape[1]
         x = h
         for i, lay in enumerate(self.exp_layers):
-            x = self._layer(self.shape.expert, lay, x, b, l, pos, mask, caches[i], lp, key_valid, self.mods[step][i])
+            x = self._layer(self.shape.expert, lay, x, b, l, pos, caches[i], lp, key_valid, self.mods[step][i])
         return x
 
     @torch.no_grad()
@@ -393,11 +347,11 @@ class PI05Model:
             return x_t
         # Fused tail: one launch per step does final norm + out-projection + Euler update + the
         # next step's suffix embedding; masks and positions are built once per chunk.
-        key_valid, pos, mask = self._suffix_constants(pad, b, l)
+        key_valid, pos = self._suffix_constants(pad, b, l)
         x_t = noise.float().contiguous().clone()
         h = ops.action_tail(None, None, None, None, x_t, dt, *self.action_in)
         for step in range(s.steps):
-            x = self._expert_layers(step, h, b, l, pad, key_valid, pos, mask)
+            x = self._expert_layers(step, h, b, l, pad, key_valid, pos)
             h = ops.action_tail(x, self.final_mods[step], *self.action_out, x_t, dt, *self.action_in,
                                 rows_per_group=b * l, embed=step + 1 < s.steps)
         return x_t
@@ -405,10 +359,9 @@ class PI05Model:
     def _suffix_constants(self, pad: torch.Tensor, b: int, l: int):
         lp = pad.shape[1]
         allowed = torch.cat([pad, torch.ones(b, l, dtype=torch.bool, device=pad.device)], dim=1)
-        mask = None if self.fused_attention else _additive(allowed[:, None, None, :].expand(b, 1, l, lp + l))
         key_valid = allowed.to(torch.uint8).contiguous()
         pos = (pad.sum(dim=-1, keepdim=True) + torch.arange(l, device=pad.device)[None, :]).to(torch.int32).reshape(-1)
-        return key_valid, pos, mask
+        return key_valid, pos
 
     def _sample_actions_overlapped(self, embs, pad, noise, dt):
         """``sample_actions`` with the first denoise step pipelined behind the prefix: expert layer
@@ -422,7 +375,7 @@ class PI05Model:
         if self._side is None:
             self._side = torch.cuda.Stream(device=self.device)
         side = self._side
-        key_valid, pos, mask = self._suffix_constants(pad, b, l)
+        key_valid, pos = self._suffix_constants(pad, b, l)
         x_t = noise.float().contiguous().clone()
         caches = self._caches(b)
         fork = torch.cuda.Event()
@@ -442,7 +395,7 @@ class PI05Model:
             x = h
             for i, lay in enumerate(self.exp_layers):
                 side.wait_event(done[i])
-                x = self._layer(s.expert, lay, x, b, l, pos, mask, caches[i], lp, key_valid, self.mods[0][i])
+                x = self._layer(s.expert, lay, x, b, l, pos, caches[i], lp, key_valid, self.mods[0][i])
             h = ops.action_tail(x, self.final_mods[0], *self.action_out, x_t, dt, *self.action_in,
                                 rows_per_group=b * l, embed=s.steps > 1)
             join = torch.cuda.Event()
@@ -452,7 +405,7 @@ class PI05Model:
             t.record_stream(main)
             t.record_stream(side)
         for step in range(1, s.steps):
-            x = self._expert_layers(step, h, b, l, pad, key_valid, pos, mask)
+            x = self._expert_layers(step, h, b, l, pad, key_valid, pos)
             h = ops.action_tail(x, self.final_mods[step], *self.action_out, x_t, dt, *self.action_in,
                                 rows_per_group=b * l, embed=step + 1 < s.steps)
         return x_t

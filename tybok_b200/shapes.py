@@ -67,15 +67,15 @@ class PI05Shape:
 GEMMA_2B = GemmaSpec(2048, 18, 16384, 8, 1, 256)
 GEMMA_300M = GemmaSpec(1024, 18, 4096, 8, 1, 256)
 
-#: BASELINE config 2: the pi0.5-shaped policy the headline latency is quoted on.
+#: The pi0.5-shaped policy the headline latency is quoted on: SigLIP-So400m on two 224x224
+#: cameras, a Gemma-2B-shaped prefix over 544 tokens, a Gemma-300M-shaped expert, chunk 50, 10 steps.
 PI05_FULL = PI05Shape(vlm=GEMMA_2B, expert=GEMMA_300M)
 
-#: A tiny policy with the same structure (GQA 4:1... kept MQA like pi0.5), used by
-#: CPU parity tests and the smoke run.  Every dimension keeps the alignment the
-#: kernels need (K multiple of 64, head_dim 256 optional -> 64 here).
+#: A tiny policy with the same structure (MQA like pi0.5) and head_dim 128, the smaller of the
+#: two head sizes the attention kernels serve; used by the CPU oracle fixtures and GPU parity tests.
 PI05_TINY = PI05Shape(
-    vlm=GemmaSpec(256, 2, 512, 4, 1, 64),
-    expert=GemmaSpec(128, 2, 256, 4, 1, 64),
+    vlm=GemmaSpec(256, 2, 512, 2, 1, 128),
+    expert=GemmaSpec(128, 2, 256, 2, 1, 128),
     vision=SiglipSpec(hidden=128, heads=4, layers=2, mlp_dim=256, image=56, patch=14),
     n_cams=2,
     lang_len=16,
@@ -97,15 +97,15 @@ PI05_SMALL = PI05Shape(
     steps=3,
 )
 
-#: The W8 linear sweep of BASELINE config 1: (N, K) pairs and token counts M.
+#: The W8 linear sweep: the Gemma-2B and Gemma-300M-expert projection shapes (N, K) and token counts M.
 W8_SWEEP_NK = ((16384, 2048), (2048, 16384), (2560, 2048), (4096, 1024), (1024, 4096))
 W8_SWEEP_M = (1, 50, 256, 800)
 
 
 @dataclass(frozen=True)
 class DiTShape:
-    """fastWAM-class DiT denoiser of BASELINE config 3
-    (tybok/policies/fastwam/models/dit_block.py:328-400)."""
+    """fastWAM-class DiT denoiser: 30 blocks of hidden 3072, 24 heads x 128, FFN 14336 over 4096
+    latent-video + 50 action tokens (tybok/policies/fastwam/models/dit_block.py:328-400)."""
 
     hidden: int = 3072
     heads: int = 24
