@@ -68,6 +68,20 @@ def dit_case(seed=4, m=70, h=256, f=512):
     return x, mods, ws
 
 
+def request_case(seed=6):
+    """Seeded inputs of the request-path fixture: a state vector with its statistics, an action
+    chunk with its statistics, and two non-square camera frames."""
+    g = torch.Generator().manual_seed(seed)
+    state = torch.empty(8).normal_(0, 1.5, generator=g)
+    stats = {"observation.state.mean": torch.empty(8).normal_(0, 0.5, generator=g),
+             "observation.state.std": torch.empty(8).uniform_(0.5, 2.0, generator=g),
+             "action.mean": torch.empty(7).normal_(0, 0.5, generator=g),
+             "action.std": torch.empty(7).uniform_(0.5, 2.0, generator=g)}
+    actions = torch.empty(1, 10, 7).normal_(0, 1, generator=g)
+    frames = [torch.rand(3, 96, 160, generator=g), torch.rand(3, 150, 75, generator=g)]
+    return state, stats, actions, frames
+
+
 def main() -> None:
     from tybok.policies.fastwam.models.fp8_linear import FP8Linear
     from tybok.policies.fastwam.models.policy import _dequant_fp8_weight
@@ -124,6 +138,21 @@ def main() -> None:
     with torch.no_grad():
         y = x + gate * blk.ffn(modulate(blk.apply_norm2(x), shift, scale))
     out["dit_ffn"] = {"in_sum": checksum(x, *mods, *[t for pair in ws for t in pair]), "y": y}
+
+    # ---- request path: normaliser, prompt text, centred-padding resize -------------------
+    from tybok.policies.pi05.models.flow_matching import resize_with_pad_torch
+    from tybok.policies.pi05.preprocess import Normalizer, build_prompt
+
+    state, stats, actions, frames = request_case()
+    norm = Normalizer.from_state_dict({"VISUAL": "IDENTITY", "STATE": "MEAN_STD", "ACTION": "MEAN_STD"}, stats)
+    nstate = norm.normalize(state[None], "observation.state", "STATE")
+    out["request"] = {
+        "in_sum": checksum(state, actions, *frames, *stats.values()),
+        "state": nstate.clone(),
+        "prompt": build_prompt("pick_up the\nred block ", nstate[0]),
+        "actions": norm.unnormalize(actions, "action", "ACTION").clone(),
+        "resized": [resize_with_pad_torch(f[None], 56, 56)[0].clone() for f in frames],
+    }
 
     # ---- whole tiny policy -------------------------------------------------------------
     shape = PI05_TINY

@@ -131,25 +131,36 @@ class PI05Model:
         self._precompute_step_constants()
 
     # ------------------------------------------------------------------ constants
-    def _precompute_step_constants(self) -> None:
-        """Per-step AdaRMS modulations ``dense(silu(time_mlp_out(silu(time_mlp_in(temb)))))``
-        for every expert norm: ``mods[step][layer] = (in [1,3W], post [1,3W])`` and the final
-        norm's ``[1,3W]`` (tybok/policies/pi05/models/flow_matching.py:321-407)."""
+    def _adarms_cond(self, times: torch.Tensor) -> torch.Tensor:
+        """AdaRMS conditioning ``silu(time_mlp_out(silu(time_mlp_in(temb(t)))))`` ``[n, W]`` fp32 for
+        flow times ``[n]`` (fp64 sinusoid cast to fp32; flow_matching.py:153-168,376-381)."""
         s = self.shape
         w = s.expert.width
-        dt = -1.0 / s.steps
-        times = torch.tensor([1.0 + i * dt for i in range(s.steps)], dtype=torch.float32)
         frac = torch.linspace(0.0, 1.0, w // 2, dtype=torch.float64)
         period = s.min_period * (s.max_period / s.min_period) ** frac
-        ang = (1.0 / period * 2 * math.pi)[None, :] * times[:, None]
+        ang = (1.0 / period * 2 * math.pi)[None, :] * times.to(torch.float32)[:, None]
         temb = torch.cat([torch.sin(ang), torch.cos(ang)], dim=1).float().to(self.device)
-        cond = F.silu(F.linear(F.silu(F.linear(temb, *self.time_in)), *self.time_out))  # [steps, W]
-        self.mods = []
+        return F.silu(F.linear(F.silu(F.linear(temb, *self.time_in)), *self.time_out))
+
+    def _layer_mods(self, cond_row: torch.Tensor):
+        """Per-layer ``(in [1,3W], post [1,3W])`` modulations and the final norm's ``[1,3W]`` for one
+        conditioning row ``[1, W]``."""
+        mods = [(F.linear(cond_row, *lay.norm_in).contiguous(), F.linear(cond_row, *lay.norm_post).contiguous())
+                for lay in self.exp_layers]
+        return mods, F.linear(cond_row, *self.final_norm).contiguous()
+
+    def _precompute_step_constants(self) -> None:
+        """Per-step AdaRMS modulations ``dense(cond)`` for every expert norm:
+        ``mods[step][layer] = (in [1,3W], post [1,3W])`` and the final norm's ``[1,3W]``
+        (tybok/policies/pi05/models/flow_matching.py:321-407)."""
+        s = self.shape
+        dt = -1.0 / s.steps
+        cond = self._adarms_cond(torch.tensor([1.0 + i * dt for i in range(s.steps)], dtype=torch.float32))
+        self.mods, self.final_mods = [], []
         for i in range(s.steps):
-            c = cond[i : i + 1]
-            self.mods.append([(F.linear(c, *lay.norm_in).contiguous(), F.linear(c, *lay.norm_post).contiguous())
-                              for lay in self.exp_layers])
-        self.final_mods = [F.linear(cond[i : i + 1], *self.final_norm).contiguous() for i in range(s.steps)]
+            mods, final = self._layer_mods(cond[i : i + 1])
+            self.mods.append(mods)
+            self.final_mods.append(final)
 
     # ------------------------------------------------------------------ non-fp8 front end
     def _pack_vision(self):
@@ -302,9 +313,17 @@ class PI05Model:
                 layer_done()
         return [(kc[:, :, :l], vc[:, :, :l]) for kc, vc in caches]
 
-    def denoise_step(self, step: int, x_t: torch.Tensor, pad: torch.Tensor, kv=None) -> torch.Tensor:
+    @torch.no_grad()
+    def velocity_at(self, t: float, x_t: torch.Tensor, pad: torch.Tensor) -> torch.Tensor:
+        """One expert pass at an arbitrary flow time ``t`` over the caches the last ``prefill`` wrote
+        (the single-step check of the reference's ``validate``, tybok/policies/pi05/engine.py:796-826)."""
+        mods, final = self._layer_mods(self._adarms_cond(torch.tensor([float(t)])))
+        return self.denoise_step(0, x_t, pad, mods=(mods, final))
+
+    def denoise_step(self, step: int, x_t: torch.Tensor, pad: torch.Tensor, mods=None) -> torch.Tensor:
         """One expert pass over the prefix caches -> velocity ``[B, chunk, A]`` fp32
-        (flow_matching.py:505-556)."""
+        (flow_matching.py:505-556).  ``mods`` overrides the precomputed modulations of ``step``."""
+        layer_mods, final_mod = mods if mods is not None else (self.mods[step], self.final_mods[step])
         s = self.shape
         spec = s.expert
         b, l = x_t.shape[0], x_t.shape[1]
@@ -315,8 +334,8 @@ class PI05Model:
         key_valid = allowed.to(torch.uint8).contiguous()
         pos = (pad.sum(dim=-1, keepdim=True) + torch.arange(l, device=x.device)[None, :]).to(torch.int32).reshape(-1)
         for i, lay in enumerate(self.exp_layers):
-            x = self._layer(spec, lay, x, b, l, pos, caches[i], lp, key_valid, self.mods[step][i])
-        y, _ = ops.rmsnorm(x, mod=self.final_mods[step], rows_per_group=b * l, out_bf16=True, out_planes=False)
+            x = self._layer(spec, lay, x, b, l, pos, caches[i], lp, key_valid, layer_mods[i])
+        y, _ = ops.rmsnorm(x, mod=final_mod, rows_per_group=b * l, out_bf16=True, out_planes=False)
         y = y.view(b, l, spec.width)[:, -s.chunk :].float()
         return F.linear(y, *self.action_out)
 

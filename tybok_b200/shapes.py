@@ -67,6 +67,11 @@ class PI05Shape:
 GEMMA_2B = GemmaSpec(2048, 18, 16384, 8, 1, 256)
 GEMMA_300M = GemmaSpec(1024, 18, 4096, 8, 1, 256)
 
+#: Variant names a checkpoint's ``config.json`` may carry (``paligemma_variant`` /
+#: ``action_expert_variant``).  A plain module dict, as the reference's ``GEMMA_VARIANTS``
+#: (tybok/policies/pi05/config.py:15-32): tests register small variants at run time.
+GEMMA_VARIANTS: dict[str, GemmaSpec] = {"gemma_2b": GEMMA_2B, "gemma_300m": GEMMA_300M}
+
 #: The pi0.5-shaped policy the headline latency is quoted on: SigLIP-So400m on two 224x224
 #: cameras, a Gemma-2B-shaped prefix over 544 tokens, a Gemma-300M-shaped expert, chunk 50, 10 steps.
 PI05_FULL = PI05Shape(vlm=GEMMA_2B, expert=GEMMA_300M)
