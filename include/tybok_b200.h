@@ -214,6 +214,14 @@ void tybok_set_pdl(int enabled);
  * kernels record SM clock samples at their phase boundaries into it.  NULL (default) = off. */
 void tybok_debug_set_trace(void* device_buffer);
 
+/* Test aid: how many SM clocks the epilogue warps of the following GEMM launches wait for their
+ * accumulator before they give up, record TYBOK_DEV_TIMEOUT_EPILOGUE in the status word and skip
+ * their stores (the producer, the MMA warp and the unwinding keep the production limit of about a
+ * second).  0 (default) restores the production limit.  The error contract it lets a test
+ * exercise is the reference's "error instead of exit" rule for its cooperative kernels
+ * (tybok/policies/fastwam/kernels/coop_grid.h:20-27). */
+void tybok_debug_set_epilogue_wait_limit(long long sm_clocks);
+
 #ifdef __cplusplus
 }
 #endif

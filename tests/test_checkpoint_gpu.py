@@ -121,7 +121,7 @@ def test_engine_on_a_checkpoint_directory(ckpt):
 
     # the same weights handed over in memory, inputs prepared by hand
     st, images, tokens, mask = _expected_inputs(frame, stats, path)
-    assert int(tokens[0, 0]) == 2 and not bool(mask.all())  # <bos> first, padded tail: the checkpoint's tokenizer ran
+    assert int(tokens[0, 0]) == 2 and int(tokens.max()) < 300  # <bos> first, word-level ids: the checkpoint's tokenizer ran
     model = PI05Model(params, PI05_TINY, device="cuda")
     ones = [torch.ones(1, dtype=torch.bool, device="cuda") for _ in images]
     full_noise = torch.zeros(1, PI05_TINY.chunk, PI05_TINY.max_action_dim, device="cuda")

@@ -301,3 +301,35 @@ def test_cta_pair_form_with_paired_and_residual_epilogues():
     torch.cuda.synchronize()
     ops.check_status()
     assert w8_ref.rel_l2(y.cpu(), ref) <= TOL
+
+
+def test_epilogue_wait_time_out_is_reported_and_the_device_stays_usable():
+    """A bounded device wait that runs out ends in an error status, not in a hang or a fault: with
+    the epilogue's wait for its accumulator cut to a few hundred SM clocks, a single-CTA launch
+    over a long K (its products take far longer than that) gives up, skips its stores and records
+    ``TYBOK_DEV_TIMEOUT_EPILOGUE``; the producer drains its copies, the MMA warp sees its products
+    retire before the tensor memory is freed, the kernel returns, ``check_status`` raises, and the
+    next launch on the device is correct.  (The reference's rule for its cooperative kernels:
+    an error, never an exit -- tybok/policies/fastwam/kernels/coop_grid.h:20-27.)"""
+    ops = _ops()
+    lib = ops._lib.load()
+    x, w8, scale, _ = _case(41, 64, 128, 32768)
+    xp = ops.split3(x.cuda(), 4)
+    w8d, sd = w8.cuda(), scale.cuda()
+    ref = w8_ref.w8_linear(x, w8, scale)
+    good, _ = ops.w8x3_linear(xp, 4, w8d, sd, token_tile=64, splits=1)
+    ops.check_status()
+    assert w8_ref.rel_l2(good.cpu(), ref) <= TOL
+    torch.cuda.synchronize()
+    lib.tybok_debug_set_epilogue_wait_limit(300)
+    try:
+        ops.w8x3_linear(xp, 4, w8d, sd, token_tile=64, splits=1)
+        torch.cuda.synchronize()  # the kernel came back
+    finally:
+        lib.tybok_debug_set_epilogue_wait_limit(0)
+    assert int(ops.status_word(xp.device).item()) == 104  # TYBOK_DEV_TIMEOUT_EPILOGUE
+    with pytest.raises(ops._lib.TybokError, match="bounded wait"):
+        ops.check_status()
+    again, _ = ops.w8x3_linear(xp, 4, w8d, sd, token_tile=64, splits=1)
+    ops.check_status()  # the status word was cleared by the raise; this launch reports nothing
+    assert torch.equal(again, good)

@@ -134,6 +134,7 @@ struct __align__(16) AttnBars {
   uint64_t v_full, s_full, p_full, o_full;
   uint64_t recv;         // push form: the peers' partial rows of the query rows this CTA merges have arrived
   uint64_t recv_stat;    // push form: the statistics of those rows have arrived (sent ahead, while P.V runs)
+  uint64_t mma_done;     // every tensor-core instruction of this CTA has retired (awaited before the tensor memory is freed)
   uint32_t tmem_base;
   volatile int abort;
   uint32_t valid[4];     // key-validity bits of this CTA's 128 keys
@@ -204,6 +205,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     mbar_init(&bars.s_full, 1);
     mbar_init(&bars.p_full, 8);
     mbar_init(&bars.o_full, 1);
+    mbar_init(&bars.mma_done, 1);
     bars.abort = 0;
     if (PUSH) {
       mbar_init(&bars.recv, 1);
@@ -299,6 +301,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       bars.abort = 1;
       if (p.status) atomicCAS(p.status, 0, TYBOK_DEV_TIMEOUT_MMA);
     }
+    // This warp frees the tensor memory at the end, whatever the other warps decide: it first sees
+    // every instruction it issued retire (on the normal path this completes together with o_full).
+    if (leader) tc_commit(&bars.mma_done);
+    __syncwarp();
+    mbar_wait(&bars.mma_done, 0);
   } else {
     // ------------------------------------------------------------ softmax, two threads per row
     const int q = warp & 3;          // tensor-memory lane quadrant of this warp
@@ -704,6 +711,7 @@ struct __align__(8) PrefillBars {
   uint64_t o_done;    // one phase per P.V product.  S_j is issued after P.V of block j-2, so a thread that
                       // holds S_j and waits for phase j-1 is never more than one phase behind
   uint64_t all_done;  // the last P.V product has landed
+  uint64_t mma_done;  // unwinding: whatever was issued before a failed wait has retired
   uint32_t tmem_base;
   volatile int abort;
   uint32_t valid[PF_MAX_KEYS / 32];
@@ -750,6 +758,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
     }
     mbar_init(&bars.o_done, 1);
     mbar_init(&bars.all_done, 1);
+    mbar_init(&bars.mma_done, 1);
     bars.abort = 0;
     fence_barrier_init();
   }
@@ -843,9 +852,15 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
     }
     // nothing of this CTA's tensor work may be in flight when it gives up its tensor memory
     ok = ok && __all_sync(0xffffffffu, at_wait(&bars.all_done, 0, &bars.abort));
-    if (!ok && lane == 0) {
-      bars.abort = 1;
-      if (p.status) atomicCAS(p.status, 0, TYBOK_DEV_TIMEOUT_MMA);
+    if (!ok) {
+      if (lane == 0) {
+        bars.abort = 1;
+        if (p.status) atomicCAS(p.status, 0, TYBOK_DEV_TIMEOUT_MMA);
+      }
+      // a failed wait left the loop early: see what was issued before it retire
+      if (leader) tc_commit(&bars.mma_done);
+      __syncwarp();
+      mbar_wait(&bars.mma_done, 0);
     }
   }
   else {

@@ -23,6 +23,8 @@ bool pdl_enabled();
 void count_launch();
 // Tuning aid: device buffer that kernels fill with per-CTA clock samples (NULL = off).
 long long* trace_buffer();
+// Test aid: SM clocks the GEMM epilogue waits for its accumulator; 0 = the production limit.
+long long epilogue_wait_limit();
 
 // Encode a 2-D tiled tensor map with the 128-byte shared-memory swizzle.
 //   dim0/dim1: extent in elements (dim0 innermost), pitch_bytes: distance between rows,

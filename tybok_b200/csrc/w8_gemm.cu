@@ -104,6 +104,7 @@ struct GemmParams {
   int gate_bf16;
   int* status;
   long long* trace;  // tuning aid: [CTA][16] SM-clock samples, NULL in production
+  long long epi_wait_limit;  // SM clocks the epilogue waits for the accumulator (kWaitLimitCycles in production)
   RopeEpi rope;      // EPI_QKV_ROPE only
 };
 
@@ -111,16 +112,18 @@ struct __align__(8) Barriers {
   uint64_t full[MAX_STAGES];
   uint64_t empty[MAX_STAGES];
   uint64_t tmem_full;
+  uint64_t mma_done;  // every tensor-core instruction this CTA (or its pair) issued has retired
   uint32_t tmem_base;
   volatile int abort;
 };
 
-__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                              long long limit = kWaitLimitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitLimitCycles) return false;
+    if (clock64() - t0 > limit) return false;
   }
   return true;
 }
@@ -169,6 +172,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
       mbar_init(&bars.empty[i], 1);
     }
     mbar_init(&bars.tmem_full, 1);
+    mbar_init(&bars.mma_done, 1);
     bars.abort = 0;
     fence_barrier_init();
     // Weights depend on nothing that runs before this kernel: request the first stages now,
@@ -249,14 +253,21 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
         for (int i = 0; i < pre; ++i) pair_stage(i, true, false);
         if (p.pdl) pdl_wait();
         for (int i = 0; i < pre; ++i) pair_stage(i, false, true);
+        int armed = pre;
         for (int i = pre; i < nkb; ++i) {
           if (!wait_or_abort(&bars.empty[i % ns], ((i / ns) & 1) ^ 1, &bars.abort)) {
             fail(&bars, p.status, TYBOK_DEV_TIMEOUT_PRODUCER);
             break;
           }
           pair_stage(i, true, true);
+          armed = i + 1;
         }
-        issued = 0;  // completion is observed through the issuing CTA's barriers only
+        // Unwinding (completion is observed through the issuing CTA's barriers only): the even CTA
+        // waits for the newest copy of every stage it armed; the pair leaves together at the
+        // closing cluster barrier.
+        if (bars.abort && pair_rank == 0)
+          for (int i = max(0, armed - ns); i < armed; ++i) mbar_wait(&bars.full[i % ns], (i / ns) & 1);
+        issued = 0;
         ok = true;
       } else {
       // The weight tiles of the first stages were requested during set-up; the activation planes
@@ -350,6 +361,16 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
       else tc_commit(&bars.tmem_full);
     }
     if (tr && leader) tr[3] = clock64();
+    // Whatever happened above, and whatever the other warps decide: this warp frees the tensor
+    // memory at the end, so it first sees every instruction it issued retire (in a pair the even
+    // CTA's commit arrives in both CTAs).  On the normal path this completes together with
+    // tmem_full; the warp has nothing else to do until the CTA meets.
+    if (leader && (!PAIR || pair_rank == 0)) {
+      if (PAIR) tc_commit_pair(&bars.mma_done, 3);
+      else tc_commit(&bars.mma_done);
+    }
+    __syncwarp();
+    if (!mbar_wait(&bars.mma_done, 0) && lane == 0) fail(&bars, p.status, TYBOK_DEV_TIMEOUT_MMA);
   } else {
     // ------------------------------------------------------------ epilogue, phase A
     // Accumulator (lane = channel, column = token) -> fp32 staging tile [w][token][128 channels]
@@ -414,7 +435,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
         }
       }
     }
-    bool ok = __all_sync(0xffffffffu, wait_or_abort(&bars.tmem_full, 0, &bars.abort));
+    bool ok = __all_sync(0xffffffffu, wait_or_abort(&bars.tmem_full, 0, &bars.abort, p.epi_wait_limit));
     if (!ok && lane == 0) fail(&bars, p.status, TYBOK_DEV_TIMEOUT_EPILOGUE);
     if (tr && ew == 0 && lane == 0) tr[4] = clock64();
     if (ok) {
@@ -836,6 +857,7 @@ static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, co
   p.gate = gate; p.ldgate = ldgate; p.rows_per_gate = rows_per_gate > 0 ? rows_per_gate : 1; p.gate_bf16 = gate_bf16;
   p.status = status;
   p.trace = host::trace_buffer();
+  p.epi_wait_limit = host::epilogue_wait_limit() > 0 ? host::epilogue_wait_limit() : kWaitLimitCycles;
   if (rope) p.rope = *rope;
 
   static bool attr_set[64] = {};
