@@ -1,20 +1,34 @@
-"""Benchmark of the fp8 hot path: pi0.5-shaped action-chunk latency on B200 (BASELINE config 2).
+"""Benchmark of the fp8 hot path on B200: pi0.5-shaped action-chunk latency, and the W8 GEMM
+against its roofline.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--batch B]
     torchrun --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-One "step" = one action chunk (prefix prefill + 10 denoise steps) of the pi0.5-shaped random-init
-fp8 policy on synthetic inputs.  ``value`` is the p50 of K CUDA-event-timed graph replays with
-inputs resident in HBM; ``e2e`` is the same chunk through ``engine.predict_action_chunk`` from
-host frames (pinned H2D of images/tokens/noise and D2H of the chunk inside the timed region).
-With N > 1 every rank runs an independent replica (no data-path collective); the time is the
-max over ranks.  ``--impl reference`` times the CPU oracle (the reference's eager torch path on
-dequantised weights) on the host cores.  Prints one JSON line on rank 0.
+Default workload (``pi05_chunk``): one "step" = one action chunk (SigLIP-So400m on two 224x224
+cameras, 18-layer Gemma-2B-shaped prefix over 544 tokens, 18-layer Gemma-300M-shaped expert, chunk
+50, 10 flow steps) of the random-init fp8 policy on synthetic inputs.  ``value`` is the p50 of K
+CUDA-event-timed graph replays with inputs resident in HBM; ``e2e`` is the same chunk through
+``engine.predict_action_chunk`` from pinned host frames (H2D of images / tokens / noise and D2H of the
+chunk inside the timed region).  With N > 1 every rank runs an independent replica (no data-path
+collective); the time is the max over ranks.  The line also carries
+
+* ``parity``: the chunk the timed engine returns for a zero-noise request against the CPU oracle on
+  the same weights and inputs;
+* ``roofline``: the dominant kernel (``w8_gemm_kernel``) timed live, per call signature of the model
+  and over the whole W8 linear sweep (5 projection shapes x M in {1, 50, 256, 800});
+* ``cpu_baseline``: the oracle (the reference's eager torch path on dequantised weights) on the host cores;
+* ``extra.batch_sweep`` (N = 1): chunks/s at 8 / 32 / 64 requests per replica;
+  ``extra.dit_ffn_tp`` (N > 1): the tensor-parallel DiT FFN over the N ranks with its all-reduce timed.
+
+``--impl reference`` times the CPU oracle alone (rank 0 only under torchrun).  Other workloads:
+``dit_ffn`` (one DiT block's FFN tail), ``gemm`` / ``attention`` (small fixed cases for profiler
+captures).  One JSON line on rank 0.
 """
 
 from __future__ import annotations
 
 import argparse
+import hashlib
 import json
 import os
 import statistics
@@ -29,6 +43,15 @@ sys.path.insert(0, ROOT)
 
 METRIC = "pi05_fp8_action_chunk_p50_ms"
 WORKLOAD = "pi05_full: SigLIP-So400m 2x224^2 + Gemma-2B prefix (544 tok) + Gemma-300M expert, chunk 50, 10 steps"
+DTYPE = "e4m3 weights x bf16 activations, fp32 accumulate"
+TRAFFIC_FILE = os.path.join(ROOT, "profiles", "w8_gemm_m50_n1024_k4096.json")
+TRAFFIC_SOURCES = ("tybok_b200/csrc/w8_gemm.cu", "tybok_b200/csrc/ptx.cuh")
+
+
+def _config(batch: int, replicas: int) -> dict:
+    """The workload description both arms print (identical keys and values)."""
+    return {"workload": WORKLOAD, "batch_per_gpu": batch, "replicas": replicas,
+            "l2": "weights streamed per chunk (3.4 GB) exceed the 126 MB L2"}
 
 
 def _peaks() -> tuple[dict, str]:
@@ -36,6 +59,16 @@ def _peaks() -> tuple[dict, str]:
     if os.path.exists(path):
         return json.load(open(path)), "measured"
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+def _all_host_threads() -> int:
+    """Every host thread this process may use (a torchrun launch sets OMP_NUM_THREADS=1 for its ranks)."""
+    try:
+        n = max(1, len(os.sched_getaffinity(0)))
+    except (AttributeError, OSError):
+        n = max(1, os.cpu_count() or 1)
+    torch.set_num_threads(n)
+    return n
 
 
 class ClockSampler(threading.Thread):
@@ -71,33 +104,122 @@ class ClockSampler(threading.Thread):
         return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
 
 
-def _synthetic_frame(engine, seed: int):
-    spec = engine.describe()
+# ------------------------------------------------------------------------------------ inputs
+def _synthetic_frame(shape, cameras, seed: int, pin: bool = True) -> dict:
+    """One seeded request: camera frames in [0, 1] at the model's resolution, a state vector, prompt
+    token ids (no tokenizer files exist for a random-init policy) with an all-ones mask."""
     g = torch.Generator().manual_seed(seed)
-    images = {c: torch.rand(3, spec["resize"][1], spec["resize"][0], generator=g).pin_memory() for c in spec["cameras"]}
-    frame = engine.make_frame(images, torch.randn(8, generator=g), "pick up the red block")
-    s = engine.config.shape
-    frame["observation.language.tokens"] = torch.randint(0, s.vocab, (s.lang_len,), generator=g)
-    frame["observation.language.attention_mask"] = torch.ones(s.lang_len, dtype=torch.bool)
+    res = shape.vision.image
+    frame = {}
+    for c in cameras:
+        img = torch.rand(3, res, res, generator=g)
+        frame[f"observation.images.{c}"] = img.pin_memory() if pin else img
+    frame["observation.state"] = torch.randn(8, generator=g)
+    frame["task"] = "pick up the red block"
+    frame["observation.language.tokens"] = torch.randint(0, shape.vocab, (shape.lang_len,), generator=g)
+    frame["observation.language.attention_mask"] = torch.ones(shape.lang_len, dtype=torch.bool)
     return frame
 
 
-NCU_TRAFFIC_DOWN_PROJ = 4859136  # bytes per launch, from the committed ncu summary
+def _oracle_inputs(frames, cameras):
+    images = [torch.stack([fr[f"observation.images.{c}"] for fr in frames]).float() * 2.0 - 1.0 for c in cameras]
+    img_masks = [torch.ones(len(frames), dtype=torch.bool) for _ in cameras]
+    tokens = torch.stack([fr["observation.language.tokens"] for fr in frames])
+    masks = torch.stack([fr["observation.language.attention_mask"] for fr in frames])
+    return images, img_masks, tokens, masks
 
 
-def _gemm_roofline(engine, peaks, peaks_kind) -> dict:
+def _oracle_weights(seed: int, device: str):
+    """Seeded weights of the full configuration in the oracle's form: quantised with the reference
+    recipe, dequantised to bf16 once (what the reference's loader does), on the CPU."""
+    from oracle import w8_ref
+    from tybok_b200.shapes import PI05_FULL
+    from tybok_b200.weights import quantize_hot_linears, random_pi05_params
+
+    params = quantize_hot_linears(random_pi05_params(PI05_FULL, seed=seed, device=device), PI05_FULL)
+    params = {k: v.cpu() for k, v in params.items()}
+    if device != "cpu":
+        torch.cuda.empty_cache()
+    deq = {}
+    for k, v in params.items():
+        if k.endswith(".scale_weight"):
+            continue
+        deq[k] = w8_ref.dequant_w8(v, params[k[: -len("weight")] + "scale_weight"]) if v.dtype == torch.float8_e4m3fn else v
+    return deq
+
+
+def _cpu_chunks(deq, frames_list, cameras, noise, warmup: int, reps: int):
+    """Warm-up and timed oracle chunks; returns (times in ms, last output)."""
+    from oracle import pi05_ref
+    from tybok_b200.shapes import PI05_FULL
+
+    times, out = [], None
+    for i in range(warmup + reps):
+        inputs = _oracle_inputs(frames_list[i % len(frames_list)], cameras)
+        t0 = time.perf_counter()
+        out = pi05_ref.sample_actions(deq, PI05_FULL, *inputs, noise)
+        if i >= warmup:
+            times.append((time.perf_counter() - t0) * 1e3)
+    return times, out
+
+
+# ------------------------------------------------------------------------------------ GEMM timing
+def _time_graph(call, iters: int) -> float:
+    """Microseconds per call of ``call(i)``, ``iters`` calls captured back to back in one CUDA graph,
+    best of three replays timed with CUDA events on the launching stream."""
+    for i in range(3):
+        call(i)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(iters):
+            call(i)
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    best = float("inf")
+    for _ in range(3):
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1) / iters * 1e3)
+    del graph
+    return best
+
+
+def _rotating_weights(n: int, k: int, dev, budget: float = 400e6):
+    """Weight copies whose total exceeds 3x L2, so that every launch streams its weights from HBM
+    as it does inside a chunk."""
+    nbuf = min(48, max(4, int(budget // (n * k)) + 1))
+    return [torch.randint(0, 120, (n, k), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn) for _ in range(nbuf)]
+
+
+def _traffic() -> tuple[int | None, str]:
+    """DRAM bytes of one captured launch of the expert down projection, from the machine-readable
+    record beside the ncu summary; ``None`` (with the reason) when the kernel sources have changed
+    since the capture."""
+    if not os.path.exists(TRAFFIC_FILE):
+        return None, "no ncu record (profiles/w8_gemm_m50_n1024_k4096.json missing)"
+    rec = json.load(open(TRAFFIC_FILE))
+    for rel in TRAFFIC_SOURCES:
+        digest = hashlib.sha256(open(os.path.join(ROOT, rel), "rb").read()).hexdigest()
+        if rec.get("source_sha256", {}).get(rel) != digest:
+            return None, f"stale: {rel} changed after the ncu capture ({rec.get('captured', '?')})"
+    return int(rec["dram_bytes_per_launch"]), (f"M=50 N=1024 K=4096: {rec['dram_bytes_per_launch']} B measured (ncu, "
+                                               f"{rec.get('captured', '?')}) vs {rec['algorithmic_bytes']} B algorithmic per launch")
+
+
+def _gemm_roofline(shape, batch: int, dev, peaks, peaks_kind, sweep: bool) -> dict:
     """Roofline of the dominant kernel (``w8_gemm_kernel``), measured live: every GEMM call
     signature of one chunk is replayed as a CUDA graph of back-to-back launches over rotating
-    weight copies (> 3x L2, so weights stream from HBM as they do inside the chunk) and timed
-    with CUDA events on the launching stream.  Algorithmic bytes per launch =
+    weight copies and timed with CUDA events.  Algorithmic bytes per launch =
     nw*(N*K + 4N) + 2*M*K + 2*M*N (nw = 2 for the gated form), flops = 2*nw*M*N*K.
     ``achieved`` aggregates the action-expert launches (M = 50*batch, HBM-bound, 720 of the 792
     launches of a chunk); the prefix launches (M = 544*batch, tensor-bound) are reported beside."""
     from tybok_b200 import ops
 
-    s = engine.config.shape
-    dev = engine.device
-    b = engine.batch_size
+    s = shape
 
     def shapes(spec, m, layers, reps):
         hd, kvd = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim
@@ -105,16 +227,14 @@ def _gemm_roofline(engine, peaks, peaks_kind) -> dict:
                 ("geglu", m, spec.mlp_dim, spec.width, 2, layers * reps),
                 ("down", m, spec.width, spec.mlp_dim, 1, layers * reps)]
 
-    groups = {"expert": shapes(s.expert, b * s.chunk, s.expert.depth, s.steps),
-              "prefix": shapes(s.vlm, b * s.prefix_len, s.vlm.depth, 1)}
+    groups = {"expert": shapes(s.expert, batch * s.chunk, s.expert.depth, s.steps),
+              "prefix": shapes(s.vlm, batch * s.prefix_len, s.vlm.depth, 1)}
     out = {}
     for gname, lst in groups.items():
         rows = []
         for name, m, n, k, nw, count in lst:
-            nbuf = min(48, max(4, int(400e6 // (nw * n * k)) + 1))
-            # the gated form streams gate and up as one interleaved [2N, K] matrix
-            ws = [[torch.randint(0, 120, (nw * n, k), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)]
-                  for _ in range(nbuf)]
+            ws = _rotating_weights(nw * n, k, dev)  # the gated form streams gate and up as one interleaved [2N, K] matrix
+            nbuf = len(ws)
             sc = torch.rand(nw * n, device=dev)
             xp = ops.split3(torch.randn(m, k, device=dev).to(torch.bfloat16), 4)
             res = torch.randn(m, n, device=dev).to(torch.bfloat16)
@@ -122,34 +242,17 @@ def _gemm_roofline(engine, peaks, peaks_kind) -> dict:
             def call(i):
                 w = ws[i % nbuf]
                 if nw == 2:
-                    return ops.w8x3_geglu_packed(xp, 4, w[0], sc, out_bf16=False, out_planes=True)
+                    return ops.w8x3_geglu_packed(xp, 4, w, sc, out_bf16=False, out_planes=True)
                 if name == "qkv":
-                    return ops.w8x3_linear(xp, 4, w[0], sc)
-                return ops.w8x3_linear(xp, 4, w[0], sc, epilogue=ops.EPI_RESIDUAL, residual=res)
+                    return ops.w8x3_linear(xp, 4, w, sc)
+                return ops.w8x3_linear(xp, 4, w, sc, epilogue=ops.EPI_RESIDUAL, residual=res)
 
-            for i in range(3):
-                call(i)
-            torch.cuda.synchronize()
-            iters = 2 * nbuf
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                for i in range(iters):
-                    call(i)
-            graph.replay()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            best = float("inf")
-            for _ in range(3):
-                e0.record()
-                graph.replay()
-                e1.record()
-                torch.cuda.synchronize()
-                best = min(best, e0.elapsed_time(e1) / iters * 1e3)
+            us = _time_graph(call, 2 * nbuf)
             byts = nw * (n * k + 4 * n) + 2 * m * k + 2 * m * n
-            rows.append({"gemm": name, "M": m, "N": n, "K": k, "nw": nw, "us": round(best, 2), "count": count,
-                         "GBps": round(byts / best / 1e3, 1), "TFps": round(2.0 * nw * m * n * k / best / 1e6, 1),
+            rows.append({"gemm": name, "M": m, "N": n, "K": k, "nw": nw, "us": round(us, 2), "count": count,
+                         "GBps": round(byts / us / 1e3, 1), "TFps": round(2.0 * nw * m * n * k / us / 1e6, 1),
                          "bytes": byts, "flops": 2.0 * nw * m * n * k})
-            del ws, graph
+            del ws
         out[gname] = rows
     torch.cuda.empty_cache()
 
@@ -159,77 +262,154 @@ def _gemm_roofline(engine, peaks, peaks_kind) -> dict:
     hbm = agg(out["expert"], "bytes") / 1e3  # bytes/us -> GB/s
     tc = agg(out["prefix"], "flops") / 1e6  # flops/us -> TFLOP/s
     strip = lambda rows: [{k: v for k, v in r.items() if k not in ("bytes", "flops")} for r in rows]  # noqa: E731
-    return {
-        "bound": "hbm", "kernel": "w8_gemm_kernel (action-expert launches, M=%d)" % (b * s.chunk),
+    traffic, traffic_note = _traffic()
+    if (batch * s.chunk, s.expert.width, s.expert.mlp_dim) != (50, 1024, 4096):
+        traffic, traffic_note = None, "the ncu record covers M=50 N=1024 K=4096 only"
+    roof = {
+        "bound": "hbm", "kernel": "w8_gemm_kernel (action-expert launches, M=%d)" % (batch * s.chunk),
         "achieved": round(hbm, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(hbm / peaks["hbm_gbs"], 4),
-        # dram__bytes_read + write of one captured launch of the expert down projection (M=50, N=1024,
-        # K=4096; profiles/w8_gemm_m50_n1024_k4096.md) against its 4,710,400 algorithmic bytes
-        "traffic": NCU_TRAFFIC_DOWN_PROJ if (b * s.chunk, s.expert.width, s.expert.mlp_dim) == (50, 1024, 4096) else None,
-        "traffic_case": "M=50 N=1024 K=4096: 4859136 B measured (ncu) vs 4710400 B algorithmic per launch",
-        "peak_source": peaks_kind, "per_shape": strip(out["expert"]),
+        "traffic": traffic, "traffic_case": traffic_note, "peak_source": peaks_kind, "per_shape": strip(out["expert"]),
         "prefix": {"bound": "tensor", "achieved": round(tc, 1), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                    "frac": round(tc / peaks["bf16_tflops"], 4), "per_shape": strip(out["prefix"])},
     }
+    if sweep:
+        roof["sweep"] = _w8_sweep(dev, peaks)
+    return roof
 
 
-def _cpu_chunk_times(reps: int, seed: int = 0) -> tuple[list[float], dict]:
-    """Time the CPU oracle (reference eager path on dequantised weights) on the full config."""
-    from oracle import pi05_ref
-    from tybok_b200.shapes import PI05_FULL
-    from tybok_b200.weights import quantize_hot_linears, random_pi05_params
+def _w8_sweep(dev, peaks) -> list[dict]:
+    """The W8 linear sweep: the Gemma-2B and Gemma-300M-expert projection shapes at M in {1, 50, 256, 800}
+    (bf16 activations ~N(0,1), e4m3 weights, fp32 accumulation).  ``us`` times the GEMM kernel on
+    activation planes (the form the fused producers feed); ``us_bf16_in`` the two-launch bf16 entry
+    point (plane split + GEMM).  Each case is held against both rooflines -- HBM (measured copy
+    bandwidth) and tensor (measured dense bf16) -- and ``binds`` names the slower of the two floors."""
+    from tybok_b200 import ops
+    from tybok_b200.shapes import W8_SWEEP_M, W8_SWEEP_NK
 
-    # every host thread this process may use (a torchrun launch sets OMP_NUM_THREADS=1 for its ranks)
-    try:
-        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
-    except (AttributeError, RuntimeError):
-        torch.set_num_threads(max(1, os.cpu_count() or 1))
-    dev = "cuda" if torch.cuda.is_available() else "cpu"  # weights are generated where it is fast
-    params = quantize_hot_linears(random_pi05_params(PI05_FULL, seed=seed, device=dev), PI05_FULL)
-    params = {k: v.cpu() for k, v in params.items()}
-    if dev == "cuda":
-        torch.cuda.empty_cache()
-    s = PI05_FULL
-    g = torch.Generator().manual_seed(seed)
-    images = [torch.rand(1, 3, 224, 224, generator=g) * 2 - 1 for _ in range(s.n_cams)]
-    img_masks = [torch.ones(1, dtype=torch.bool) for _ in range(s.n_cams)]
-    tokens = torch.randint(0, s.vocab, (1, s.lang_len), generator=g)
-    masks = torch.ones(1, s.lang_len, dtype=torch.bool)
-    noise = torch.randn(1, s.chunk, s.max_action_dim, generator=g)
-    # dequantise once (what the reference's loader does), then time the unmodified eager math
-    from oracle import w8_ref
-    deq = {}
-    for k, v in params.items():
-        if k.endswith(".scale_weight"):
-            continue
-        deq[k] = w8_ref.dequant_w8(v, params[k[: -len("weight")] + "scale_weight"]) if v.dtype == torch.float8_e4m3fn else v
-    del params
-    times = []
-    pi05_ref.sample_actions(deq, s, images, img_masks, tokens, masks, noise)  # warm-up
-    for _ in range(reps):
-        t0 = time.perf_counter()
-        pi05_ref.sample_actions(deq, s, images, img_masks, tokens, masks, noise)
-        times.append((time.perf_counter() - t0) * 1e3)
-    info = {"cores": torch.get_num_threads(), "nproc": os.cpu_count(), "torch": torch.__version__}
-    return times, info
+    rows = []
+    for n, k in W8_SWEEP_NK:
+        ws = _rotating_weights(n, k, dev)
+        nbuf = len(ws)
+        sc = torch.rand(n, device=dev)
+        for m in W8_SWEEP_M:
+            x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+            xp = ops.split3(x, 4)
+            us = _time_graph(lambda i: ops.w8x3_linear(xp, 4, ws[i % nbuf], sc), 2 * nbuf)
+            us2 = _time_graph(lambda i: ops.w8a16_linear(x, ws[i % nbuf], sc), 2 * nbuf)
+            byts = n * k + 4 * n + 2 * m * k + 2 * m * n
+            flops = 2.0 * m * n * k
+            t_hbm, t_tc = byts / peaks["hbm_gbs"] / 1e3, flops / peaks["bf16_tflops"] / 1e6  # us
+            rows.append({"N": n, "K": k, "M": m, "us": round(us, 2), "us_bf16_in": round(us2, 2),
+                         "GBps": round(byts / us / 1e3, 1), "TFps": round(flops / us / 1e6, 1),
+                         "frac_hbm": round(t_hbm / us, 4), "frac_tensor": round(t_tc / us, 4),
+                         "binds": "hbm" if t_hbm >= t_tc else "tensor", "frac_of_binding": round(max(t_hbm, t_tc) / us, 4)})
+        del ws
+    torch.cuda.empty_cache()
+    return rows
 
 
+# ------------------------------------------------------------------------------------ arms
 def run_reference(args, rank: int) -> None:
+    """The reference arm: the CPU oracle on the host cores, rank 0 only, nothing on a GPU."""
     if rank != 0:
         return
-    times, info = _cpu_chunk_times(max(1, args.steps))
+    from tybok_b200.shapes import PI05_FULL as S
+
+    cores = _all_host_threads()
+    deq = _oracle_weights(seed=0, device="cpu")
+    cams = [f"camera{i + 1}" for i in range(S.n_cams)]
+    frames = [[_synthetic_frame(S, cams, 100 + i, pin=False) for _ in range(args.batch)] for i in range(4)]
+    noise = torch.randn(args.batch, S.chunk, S.max_action_dim, generator=torch.Generator().manual_seed(1))
+    times, _ = _cpu_chunks(deq, frames, cams, noise, max(1, args.warmup), max(1, args.steps))
     p50 = statistics.median(times)
     line = {
         "impl": "reference", "metric": METRIC, "value": round(p50, 2), "unit": "ms", "n_gpus": args.gpus,
-        "steps": len(times), "warmup": 1, "ms_per_step": round(sum(times) / len(times), 2), "higher_is_better": False,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16 activations x e4m3 weights dequantised to bf16, fp32 accumulate",
-        "data": "synthetic", "config": {"workload": WORKLOAD, "batch": 1},
-        "cpu_baseline": {"value": round(p50, 2), "unit": "ms", "cores": info["cores"], "kind": "port",
-                         "sample": f"{len(times)} full chunks of the config (oracle/pi05_ref.py, torch {info['torch']}, "
-                                   f"{info['nproc']} logical CPUs)"},
+        "steps": len(times), "warmup": max(1, args.warmup), "ms_per_step": round(sum(times) / len(times), 2),
+        "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+        "dtype": DTYPE + " (weights dequantised to bf16, the reference's loader path)", "data": "synthetic",
+        "config": _config(args.batch, args.gpus),
+        "cpu_baseline": {"value": round(p50, 2), "unit": "ms", "cores": cores, "kind": "port",
+                         "min": round(min(times), 2), "max": round(max(times), 2),
+                         "sample": f"{len(times)} full chunks of the config after {max(1, args.warmup)} warm-up "
+                                   f"(oracle/pi05_ref.py, torch {torch.__version__}, {os.cpu_count()} logical CPUs)"},
         "e2e": {"value": round(p50, 2), "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def _batch_sweep(rank: int, local: int, overlap: bool, batches=(8, 32, 64)) -> list[dict]:
+    """Batched throughput of one replica: ``b`` requests per graph replay (the data-parallel serving
+    configuration at batch {8, 32, 64} per GPU); chunks/s from 5 event-timed replays."""
+    from tybok_b200.engine import PI05B200Engine
+
+    rows = []
+    for b in batches:
+        eng = PI05B200Engine(f"synthetic:pi05_full@{rank}", device=f"cuda:{local}", graph=True, warmup=True, seed=rank,
+                             batch_size=b, overlap=overlap)
+        for _ in range(2):
+            eng._graph.replay()
+        torch.cuda.synchronize()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(5)]
+        for e0, e1 in evs:
+            e0.record()
+            eng._graph.replay()
+            e1.record()
+        torch.cuda.synchronize()
+        ms = statistics.median(a.elapsed_time(c) for a, c in evs)
+        rows.append({"batch": b, "ms_per_batch": round(ms, 3), "chunks_per_s": round(b / ms * 1e3, 1),
+                     "ms_per_chunk": round(ms / b, 3)})
+        del eng
+        torch.cuda.empty_cache()
+    return rows
+
+
+def _dit_ffn_tp(rank: int, world: int, local: int, peaks, steps: int = 10) -> dict:
+    """The tensor-parallel DiT FFN tail (hidden 3072, ffn 14336, 4146 tokens) over the ranks of this
+    run: ms per block, the all-reduce's own share from CUDA events around it, and the result
+    against the single-GPU form computed on rank 0 (rel-L2 <= 1e-2)."""
+    import torch.distributed as dist
+
+    from oracle import w8_ref
+    from tybok_b200.dit import DiTFFN, finish_after_reduce
+    from tybok_b200.shapes import DIT_FULL as S
+
+    g = torch.Generator(device="cuda").manual_seed(0)  # same weights and inputs on every rank
+    rn = lambda *sh, std=1.0: torch.empty(*sh, device="cuda").normal_(0, std, generator=g)  # noqa: E731
+    raw = [(rn(S.ffn, S.hidden, std=0.02), rn(S.ffn, std=0.1), rn(S.hidden, S.ffn, std=0.02), rn(S.hidden, std=0.1))
+           for _ in range(3)]  # 3 x 88 MB of e4m3 weights (per-rank shards still exceed L2 together with activations)
+    blocks = [DiTFFN(*w, device=f"cuda:{local}", rank=rank, world=world) for w in raw]
+    x = rn(S.seq, S.hidden).to(torch.bfloat16)
+    shift, scale, gate = (rn(S.hidden, std=0.5).to(torch.bfloat16) for _ in range(3))
+    for i in range(3):
+        y = blocks[i % 3](x, shift, scale, gate)
+    torch.cuda.synchronize()
+    dist.barrier()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3 * steps + 1)]
+    ev[0].record()
+    for i in range(steps):
+        blk = blocks[i % 3]
+        part = blk.partial(x, shift, scale)
+        ev[3 * i + 1].record()
+        dist.all_reduce(part, group=blk.group)
+        ev[3 * i + 2].record()
+        y = finish_after_reduce(x, part, blk.down[2], gate)
+        ev[3 * i + 3].record()
+    torch.cuda.synchronize()
+    total = ev[0].elapsed_time(ev[-1]) / steps
+    reduce_ms = statistics.median(ev[3 * i + 1].elapsed_time(ev[3 * i + 2]) for i in range(steps))
+    t = torch.tensor([total, reduce_ms], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    out = {"ranks": world, "ms_per_block": round(float(t[0]), 4), "allreduce_ms": round(float(t[1]), 4),
+           "allreduce_bytes": S.seq * S.hidden * 2,
+           "TFps": round(4.0 * S.seq * S.hidden * S.ffn / float(t[0]) / 1e9, 1),
+           "frac_of_bf16_peak_x_ranks": round(4.0 * S.seq * S.hidden * S.ffn / float(t[0]) / 1e9 / (peaks["bf16_tflops"] * world), 4)}
+    if rank == 0:
+        last = (steps - 1) % 3
+        single = DiTFFN(*raw[last], device=f"cuda:{local}", rank=0, world=1)(x, shift, scale, gate)
+        out["rel_l2_vs_single_gpu"] = round(w8_ref.rel_l2(y.float().cpu(), single.float().cpu()), 6)
+        out["parity_ok"] = out["rel_l2_vs_single_gpu"] <= 1e-2
+    return out
 
 
 def run_ours(args, rank: int, world: int) -> None:
@@ -244,14 +424,11 @@ def run_ours(args, rank: int, world: int) -> None:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     peaks, peaks_kind = _peaks()
 
-    l0 = ops.launch_count()
     engine = PI05B200Engine(f"synthetic:pi05_full@{rank}", device=f"cuda:{local}", graph=False, warmup=True,
                             seed=rank, batch_size=args.batch, overlap=not args.no_overlap)
     l1 = ops.launch_count()
     engine._capture()
-    launches_per_chunk = ops.launch_count() - l1
-    launches_per_chunk //= 3  # two warm-up passes + the captured pass
-    del l0
+    launches_per_chunk = (ops.launch_count() - l1) // 3  # two warm-up passes + the captured pass
 
     def barrier():
         if world > 1:
@@ -282,47 +459,75 @@ def run_ours(args, rank: int, world: int) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         p50, total_ms = float(t[0]), float(t[1])
 
-    # end to end through the public call: host frame -> numpy chunk
-    frames = [_synthetic_frame(engine, 100 + i) for i in range(4)]
+    # end to end through the public call: host frames -> numpy chunk(s)
+    s = engine.config.shape
+    cams = engine.describe()["cameras"]
+    frames = [[_synthetic_frame(s, cams, 100 + 10 * i + j) for j in range(args.batch)] for i in range(4)]
+    call = (lambda fr: engine.predict_action_chunk(fr[0])) if args.batch == 1 else engine.predict_action_chunks
     for i in range(3):
-        engine.predict_action_chunk(frames[i % 4])
+        call(frames[i % 4])
     barrier()
     e2e = []
     for i in range(args.steps):
         t0 = time.perf_counter()
-        engine.predict_action_chunk(frames[i % 4])
+        call(frames[i % 4])
         e2e.append((time.perf_counter() - t0) * 1e3)
     e2e_p50 = statistics.median(e2e)
     if world > 1:
         t = torch.tensor([e2e_p50], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_p50 = float(t[0])
-    s = engine.config.shape
-    h2d = s.n_cams * 3 * 224 * 224 * 4 + s.n_cams + s.lang_len * 9 + s.chunk * s.max_action_dim * 4
-    d2h = s.chunk * engine.config.action_dim * 4
+    res = s.vision.image
+    h2d = args.batch * (s.n_cams * 3 * res * res * 4 + s.n_cams + s.lang_len * 9 + s.chunk * s.max_action_dim * 4)
+    d2h = args.batch * s.chunk * engine.config.action_dim * 4
 
+    extra: dict = {}
+    if world > 1 and not args.no_extras:
+        extra["dit_ffn_tp"] = _dit_ffn_tp(rank, world, local, peaks)
     line = None
     if rank == 0:
-        roof = _gemm_roofline(engine, peaks, peaks_kind) if world == 1 else None
+        # parity of the timed engine: a zero-noise request against the CPU oracle (computed below)
+        zero = torch.zeros(args.batch, s.chunk, s.max_action_dim)
+        gpu_chunk = None
+        if not args.no_cpu_baseline:
+            got = engine.predict_action_chunk(frames[0][0], noise=zero) if args.batch == 1 else \
+                engine.predict_action_chunks(frames[0], noise=zero)
+            gpu_chunk = torch.from_numpy(got).reshape(args.batch, s.chunk, -1)
+        roof = _gemm_roofline(s, args.batch, torch.device("cuda", local), peaks, peaks_kind,
+                              sweep=world == 1 and not args.no_extras)
         ops.check_status()
-        cpu = None
-        if world == 1 and not args.no_cpu_baseline:
-            del engine
-            torch.cuda.empty_cache()
-            times, info = _cpu_chunk_times(2)
-            cpu = {"value": round(statistics.median(times), 1), "unit": "ms", "cores": info["cores"], "kind": "port",
-                   "sample": f"2 full chunks of the same config after 1 warm-up (oracle/pi05_ref.py, {info['nproc']} logical CPUs)"}
+        del engine, graph
+        torch.cuda.empty_cache()
+        if world == 1 and args.batch == 1 and not args.no_extras:
+            extra["batch_sweep"] = _batch_sweep(rank, local, not args.no_overlap)
+        cpu = parity = None
+        if not args.no_cpu_baseline:
+            cores = _all_host_threads()
+            deq = _oracle_weights(seed=rank, device="cuda")
+            unpinned = [[{k: (v.clone() if isinstance(v, torch.Tensor) else v) for k, v in fr.items()} for fr in fl]
+                        for fl in frames[:1]]
+            reps = 5 if world == 1 else 1
+            times, ref = _cpu_chunks(deq, unpinned, cams, zero, 1, reps)
+            cpu = {"value": round(statistics.median(times), 1), "unit": "ms", "cores": cores, "kind": "port",
+                   "min": round(min(times), 1), "max": round(max(times), 1),
+                   "sample": f"{reps} full chunks of the same config (batch {args.batch}) after 1 warm-up "
+                             f"(oracle/pi05_ref.py, {os.cpu_count()} logical CPUs)"}
+            from oracle import w8_ref
+            ref = ref[:, :, : gpu_chunk.shape[-1]]
+            parity = {"max_abs": round(float((gpu_chunk - ref).abs().max()), 6), "rel_l2": round(w8_ref.rel_l2(gpu_chunk, ref), 6),
+                      "tolerance_max_abs": 2e-2, "config": "pi05_full", "batch": args.batch,
+                      "what": "engine.predict_action_chunk (graph replay, bf16 tower, step-0 overlap) vs "
+                              "oracle/pi05_ref.sample_actions on the same seeded weights and request, zero noise"}
         line = {
             "metric": METRIC, "value": round(p50, 4), "unit": "ms", "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": round(total_ms / args.steps, 4), "higher_is_better": False,
-            "scaling": "weak", "vs_baseline": None, "dtype": "e4m3 weights x bf16 activations (3 exact e5m2 planes), fp32 accumulate",
-            "data": "synthetic",
-            "config": {"workload": WORKLOAD, "batch_per_gpu": args.batch, "replicas": world, "cuda_graph": True, "overlap_step0": not args.no_overlap,
-                       "l2": "weights streamed per chunk (3.4 GB) exceed the 126 MB L2"},
+            "scaling": "weak", "vs_baseline": None, "dtype": DTYPE + " (activations as 3 exact e5m2 planes)",
+            "data": "synthetic", "config": _config(args.batch, world),
+            "run": {"cuda_graph": True, "overlap_step0": not args.no_overlap},
             "chunks_per_s": round(world * args.batch / (total_ms / args.steps) * 1e3, 2),
             "clocks": clocks, "gpu_launches": launches_per_chunk * args.steps,
             "e2e": {"value": round(e2e_p50, 4), "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "roofline": roof, "cpu_baseline": cpu,
+            "parity": parity, "roofline": roof, "cpu_baseline": cpu, "extra": extra,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -331,9 +536,9 @@ def run_ours(args, rank: int, world: int) -> None:
 
 
 def run_dit_ffn(args, rank: int, world: int) -> None:
-    """Secondary workload (BASELINE config 3): the FFN tail of one fastWAM-class DiT block
-    (hidden 3072, ffn 14336, 4096+50 tokens), tensor-parallel over N GPUs with one NCCL
-    all-reduce per call (strong scaling: the work is fixed, the weights are sharded)."""
+    """Secondary workload: the FFN tail of one fastWAM-class DiT block (hidden 3072, ffn 14336,
+    4096 + 50 tokens), tensor-parallel over N GPUs with one NCCL all-reduce per call (strong
+    scaling: the work is fixed, the weights are sharded)."""
     import torch.distributed as dist
 
     from tybok_b200 import ops
@@ -379,7 +584,7 @@ def run_dit_ffn(args, rank: int, world: int) -> None:
         print(json.dumps({
             "metric": "dit_ffn_tail_ms_per_block", "value": round(ms, 4), "unit": "ms", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": round(ms, 4), "higher_is_better": False,
-            "scaling": "strong", "vs_baseline": None, "dtype": "e4m3 weights x bf16 activations, fp32 accumulate",
+            "scaling": "strong", "vs_baseline": None, "dtype": DTYPE,
             "data": "synthetic", "config": {"workload": "dit_ffn: hidden 3072, ffn 14336, 4146 tokens, TP over N GPUs",
                                             "l2": "6 rotating blocks (528 MB of weights) exceed L2"},
             "clocks": clocks, "gpu_launches": 3 * args.steps,
@@ -392,6 +597,43 @@ def run_dit_ffn(args, rank: int, world: int) -> None:
         dist.destroy_process_group()
 
 
+def run_profile_case(args) -> None:
+    """Small fixed workloads for profiler captures: a few launches over a few hundred MB.
+
+    ``--workload gemm --m 50 --n 1024 --k 4096 [--launches 6] [--gated]``: the W8 GEMM over rotating
+    weight copies whose total exceeds the 126 MB L2, so the DRAM counters of a captured launch mean
+    what they mean inside a chunk.  ``--workload attention --tokens 50 --prefix 544 [--head-dim 256]``:
+    six launches of the attention kernel."""
+    from tybok_b200 import ops
+
+    dev = torch.device("cuda")
+    if args.workload == "gemm":
+        n = 2 * args.n if args.gated else args.n
+        nbuf = max(2, int(260e6 // (n * args.k)) + 1)
+        ws = [torch.randint(0, 120, (n, args.k), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn) for _ in range(nbuf)]
+        sc = torch.rand(n, device=dev)
+        xp = ops.split3(torch.randn(args.m, args.k, device=dev).to(torch.bfloat16), 4)
+        for i in range(nbuf + args.launches):
+            if args.gated:
+                ops.w8x3_geglu_packed(xp, 4, ws[i % nbuf], sc, out_bf16=False, out_planes=True)
+            else:
+                ops.w8x3_linear(xp, 4, ws[i % nbuf], sc)
+        launches = nbuf + args.launches + 1
+        what = {"workload": f"gemm M={args.m} N={args.n} K={args.k} gated={args.gated}", "weight_copies": nbuf}
+    else:
+        d, lk, heads = args.head_dim, args.prefix + args.tokens, args.heads
+        kv_heads = heads if args.mha else 1
+        kc = torch.randn(1, kv_heads, lk + 8, d, device=dev).to(torch.bfloat16)
+        vc = torch.randn(1, kv_heads, lk + 8, d, device=dev).to(torch.bfloat16)
+        q = torch.randn(args.tokens, heads * d, device=dev).to(torch.bfloat16)
+        for _ in range(args.launches):
+            ops.attention(q, kc, vc, None, tokens=args.tokens, keys=lk, scale=d**-0.5, out_bf16=False, out_planes=True)
+        launches = args.launches
+        what = {"workload": f"attention tokens={args.tokens} keys={lk} heads={heads} kv_heads={kv_heads} head_dim={d}"}
+    ops.check_status()
+    print(json.dumps({"metric": "profile_case", "config": what, "gpu_launches": launches}), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -399,9 +641,15 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=1)
-    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle leg (and with it the parity field)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the W8 sweep, the batch sweep and the tensor-parallel extra")
     ap.add_argument("--no-overlap", action="store_true", help="run the first denoise step after the prefix, not behind it")
-    ap.add_argument("--workload", default="pi05_chunk", choices=["pi05_chunk", "dit_ffn"])
+    ap.add_argument("--workload", default="pi05_chunk", choices=["pi05_chunk", "dit_ffn", "gemm", "attention"])
+    for name, default in (("m", 50), ("n", 16384), ("k", 2048), ("launches", 6), ("tokens", 50), ("prefix", 544),
+                          ("head-dim", 256), ("heads", 8)):
+        ap.add_argument(f"--{name}", type=int, default=default)
+    ap.add_argument("--gated", action="store_true")
+    ap.add_argument("--mha", action="store_true")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -411,10 +659,12 @@ def main() -> None:
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device -- the product path has no CPU fallback (use --impl reference "
                          "for the CPU oracle timing)")
-    if args.workload == "dit_ffn":
+    if args.workload in ("gemm", "attention"):
+        run_profile_case(args)
+    elif args.workload == "dit_ffn":
         run_dit_ffn(args, rank, world)
-        return
-    run_ours(args, rank, world)
+    else:
+        run_ours(args, rank, world)
 
 
 if __name__ == "__main__":
