@@ -338,7 +338,7 @@ def run_reference(args, rank: int) -> None:
     print(json.dumps(line), flush=True)
 
 
-def _batch_sweep(rank: int, local: int, overlap: bool, batches=(8, 32, 64)) -> list[dict]:
+def _batch_sweep(rank: int, local: int, overlap: bool, vision: str, batches=(8, 32, 64)) -> list[dict]:
     """Batched throughput of one replica: ``b`` requests per graph replay (the data-parallel serving
     configuration at batch {8, 32, 64} per GPU); chunks/s from 5 event-timed replays."""
     from tybok_b200.engine import PI05B200Engine
@@ -346,7 +346,7 @@ def _batch_sweep(rank: int, local: int, overlap: bool, batches=(8, 32, 64)) -> l
     rows = []
     for b in batches:
         eng = PI05B200Engine(f"synthetic:pi05_full@{rank}", device=f"cuda:{local}", graph=True, warmup=True, seed=rank,
-                             batch_size=b, overlap=overlap)
+                             batch_size=b, overlap=overlap, vision_precision=vision)
         for _ in range(2):
             eng._graph.replay()
         torch.cuda.synchronize()
@@ -425,7 +425,8 @@ def run_ours(args, rank: int, world: int) -> None:
     peaks, peaks_kind = _peaks()
 
     engine = PI05B200Engine(f"synthetic:pi05_full@{rank}", device=f"cuda:{local}", graph=False, warmup=True,
-                            seed=rank, batch_size=args.batch, overlap=not args.no_overlap)
+                            seed=rank, batch_size=args.batch, overlap=not args.no_overlap,
+                            vision_precision=args.vision_precision)
     l1 = ops.launch_count()
     engine._capture()
     launches_per_chunk = (ops.launch_count() - l1) // 3  # two warm-up passes + the captured pass
@@ -499,7 +500,7 @@ def run_ours(args, rank: int, world: int) -> None:
         del engine, graph
         torch.cuda.empty_cache()
         if world == 1 and args.batch == 1 and not args.no_extras:
-            extra["batch_sweep"] = _batch_sweep(rank, local, not args.no_overlap)
+            extra["batch_sweep"] = _batch_sweep(rank, local, not args.no_overlap, args.vision_precision)
         cpu = parity = None
         if not args.no_cpu_baseline:
             cores = _all_host_threads()
@@ -516,14 +517,14 @@ def run_ours(args, rank: int, world: int) -> None:
             ref = ref[:, :, : gpu_chunk.shape[-1]]
             parity = {"max_abs": round(float((gpu_chunk - ref).abs().max()), 6), "rel_l2": round(w8_ref.rel_l2(gpu_chunk, ref), 6),
                       "tolerance_max_abs": 2e-2, "config": "pi05_full", "batch": args.batch,
-                      "what": "engine.predict_action_chunk (graph replay, bf16 tower, step-0 overlap) vs "
+                      "what": f"engine.predict_action_chunk (graph replay, {args.vision_precision} tower, step-0 overlap) vs "
                               "oracle/pi05_ref.sample_actions on the same seeded weights and request, zero noise"}
         line = {
             "metric": METRIC, "value": round(p50, 4), "unit": "ms", "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": round(total_ms / args.steps, 4), "higher_is_better": False,
             "scaling": "weak", "vs_baseline": None, "dtype": DTYPE + " (activations as 3 exact e5m2 planes)",
             "data": "synthetic", "config": _config(args.batch, world),
-            "run": {"cuda_graph": True, "overlap_step0": not args.no_overlap},
+            "run": {"cuda_graph": True, "overlap_step0": not args.no_overlap, "vision_tower": args.vision_precision},
             "chunks_per_s": round(world * args.batch / (total_ms / args.steps) * 1e3, 2),
             "clocks": clocks, "gpu_launches": launches_per_chunk * args.steps,
             "e2e": {"value": round(e2e_p50, 4), "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -644,6 +645,8 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle leg (and with it the parity field)")
     ap.add_argument("--no-extras", action="store_true", help="skip the W8 sweep, the batch sweep and the tensor-parallel extra")
     ap.add_argument("--no-overlap", action="store_true", help="run the first denoise step after the prefix, not behind it")
+    ap.add_argument("--vision-precision", default="tf32", choices=["tf32", "bf16", "fp32"],
+                    help="SigLIP tower: fp32 activations with TF32 GEMMs (default), all bf16, or plain fp32")
     ap.add_argument("--workload", default="pi05_chunk", choices=["pi05_chunk", "dit_ffn", "gemm", "attention"])
     for name, default in (("m", 50), ("n", 16384), ("k", 2048), ("launches", 6), ("tokens", 50), ("prefix", 544),
                           ("head-dim", 256), ("heads", 8)):

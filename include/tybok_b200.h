@@ -158,6 +158,31 @@ int tybok_action_tail(const void* x, int64_t ldx, const float* mod, int64_t ldmo
 int tybok_add_layernorm(const void* x, const void* y, const void* weight, const void* bias, int M, int W, float eps,
                         void* x_out, void* h, void* stream);
 
+/* The same in fp32 (all six tensors fp32; W % 4 == 0, W <= 2048), for a tower run in fp32 / TF32. */
+int tybok_add_layernorm_f32(const float* x, const float* y, const float* weight, const float* bias, int M, int W,
+                            float eps, float* x_out, float* h, void* stream);
+
+/* LayerNorm with affine weight / bias (bf16 [W]) and fp32 statistics, one rounding at the end:
+ * y = bf16(LN(x) * weight + bias), as apply_norm3 of a DiT block
+ * (tybok/policies/fastwam/models/dit_block.py:236-237, wan_base.py:141-148).  Outputs as tybok_rmsnorm. */
+int tybok_layernorm_affine(const void* x, int64_t ldx, const void* weight, const void* bias, int M, int W, float eps,
+                           void* y, int64_t ldy, void* y_planes, int out_shift, void* stream);
+
+/* qk-norm + rotary embedding + KV store of a DiT attention (one launch, one CTA per token row).
+ * A source row (bf16, row stride ld) holds q at column q_off, k at k_off, v at v_off, each H*D wide;
+ * a negative offset means "absent".  q and k are RMS-normalised over all H*D channels of the row
+ * (fp32 statistics, bf16(x * rstd) * bf16 weight -> bf16), then rotated pair-wise by the per-token
+ * table cos/sin fp32 [L, D/2] ((x[2i], x[2i+1]) times (cos + i sin), fp32, rounded to bf16; NULL
+ * tables = no rotation); q goes to q_out [B*L, H*D], k and the untouched v head-major into the
+ * caches [B, H, Lcap, D] at key offset key_off.  H*D <= 4096, D % 8 == 0.
+ * Replaces norm_q / norm_k / apply_dense_rope and the K/V concatenation of
+ * tybok/policies/fastwam/models/dit_block.py:246-273,255-266 and wan_base.py:97-128 (the reference's fused
+ * form: phases P2 of tybok/policies/fastwam/kernels/adit_attn_self.cu:87-783 and adit_attn_cross.cu:77-813). */
+int tybok_qknorm_rope_store(const void* src, int64_t ld, int q_off, int k_off, int v_off, const void* norm_q_weight,
+                            const void* norm_k_weight, float eps, const float* cos_table, const float* sin_table,
+                            void* q_out, void* k_cache, void* v_cache, int B, int L, int H, int D, int Lcap, int key_off,
+                            void* stream);
+
 /* RoPE + KV store.  qkv is the packed projection output [B*L, (H+2G)*D] (row stride ldq); q and
  * k are rotated (rotate-half form, bf16 cos/sin tables [max_pos, D], bf16 arithmetic with the
  * reference's rounding points) at positions pos[B*L]; q goes to q_out [B*L, H*D], k and v to the
@@ -179,7 +204,8 @@ int tybok_w8x3_qkv_rope(const void* x_planes, int x_shift, const void* w8_paired
                         int splits, int* status_word, void* stream);
 
 /* GQA/MQA attention of L query tokens per batch element over the first Lk keys of the caches
- * (head_dim 256; Lk <= 1024 for L <= 128, Lk <= 4096 for longer query sequences):
+ * (head_dim 256: Lk <= 1024 for L <= 128, Lk <= 8192 for longer query sequences; head_dim 128: any L,
+ * Lk <= 8192):
  * softmax(q k^T * scale + mask) v with fp32 softmax, bf16 P.
  *   q          [B*L, H*D] bf16 (already rotated);  k_cache / v_cache  [B, G, Lcap, D] bf16, finite
  *   key_valid  NULL or uint8 [B, Lk]: 0 masks a key for every query of that batch element
@@ -187,8 +213,8 @@ int tybok_w8x3_qkv_rope(const void* x_planes, int x_shift, const void* w8_paired
  *   workspace  >= tybok_attention_workspace_bytes(B, L, H, Lk) bytes, 16-byte aligned (0 bytes, and
  *              NULL allowed, when Lk <= 128 or L > 128): where the key blocks of a query tile are
  *              spread over a cluster and the partial outputs do not fit the exchange through
- *              shared memory, they pass through it (L2) and merge in block order.  L > 128 runs
- *              one CTA per query tile and head over all keys and exchanges nothing.
+ *              shared memory, they pass through it (L2) and merge in block order.  L > 128, and every
+ *              head_dim 128 call, runs one CTA per query tile and head over all keys and exchanges nothing.
  * Replaces GemmaAttention._forward_eager (tybok/policies/pi05/models/layers.py:166-191) and the
  * split-K flash kernels of tybok/policies/pi05/models/triton_expert_fused_qkv_rope_attn.py:322-433. */
 int tybok_attention(const void* q, const void* k_cache, const void* v_cache, const void* key_valid, void* out,

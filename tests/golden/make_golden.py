@@ -68,6 +68,28 @@ def dit_case(seed=4, m=70, h=256, f=512):
     return x, mods, ws
 
 
+def dit_block_case(shape, seed=8, video_prefix=0):
+    """Seeded inputs of the whole-DiT-block fixtures: tokens, context with a padded tail, the
+    per-step modulation table, the dense rotary table (complex, ``[S, 1, d/2]``) and, optionally,
+    keys / values of ``video_prefix`` earlier tokens."""
+    g = torch.Generator().manual_seed(seed)
+    s, h, c = shape.seq, shape.hidden, shape.context_len
+    x = torch.empty(1, s, h).normal_(0, 1, generator=g).to(torch.bfloat16)
+    context = torch.empty(1, c, h).normal_(0, 1, generator=g).to(torch.bfloat16)
+    context_mask = torch.ones(1, c, dtype=torch.bool)
+    context_mask[:, c - 4:] = False
+    t_mod = torch.empty(1, 6, h).normal_(0, 0.5, generator=g).to(torch.bfloat16)
+    pos = torch.arange(video_prefix, video_prefix + s, dtype=torch.float64)
+    inv = 1.0 / torch.pow(10000, torch.arange(0, shape.head_dim, 2, dtype=torch.float64) / shape.head_dim)
+    ang = torch.outer(pos, inv)
+    freqs = torch.polar(torch.ones_like(ang), ang)[:, None, :]
+    video_kv = None
+    if video_prefix:
+        video_kv = tuple(torch.empty(1, video_prefix, shape.heads * shape.head_dim).normal_(0, 1, generator=g).to(torch.bfloat16)
+                         for _ in range(2))
+    return x, context, context_mask, t_mod, freqs, video_kv
+
+
 def request_case(seed=6):
     """Seeded inputs of the request-path fixture: a state vector with its statistics, an action
     chunk with its statistics, and two non-square camera frames."""
@@ -138,6 +160,29 @@ def main() -> None:
     with torch.no_grad():
         y = x + gate * blk.ffn(modulate(blk.apply_norm2(x), shift, scale))
     out["dit_ffn"] = {"in_sum": checksum(x, *mods, *[t for pair in ws for t in pair]), "y": y}
+
+    # ---- a9 / a12: a whole DiT block on dequantised weights -------------------------------
+    from tybok_b200.shapes import DIT_TINY
+    from tybok_b200.weights import DIT_HOT_LINEARS, quantize_dit_block, random_dit_block_params
+
+    bp = quantize_dit_block(random_dit_block_params(DIT_TINY, seed=0))
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        blk = FastWAMAttentionBlock(DIT_TINY.hidden, DIT_TINY.head_dim, DIT_TINY.heads, DIT_TINY.ffn)
+    finally:
+        torch.set_default_dtype(torch.float32)
+    sd = {k: v for k, v in bp.items() if not k.endswith(".scale_weight")}
+    for lin in DIT_HOT_LINEARS:
+        sd[f"{lin}.weight"] = _dequant_fp8_weight(bp[f"{lin}.weight"], bp[f"{lin}.scale_weight"])
+    missing, unexpected = blk.load_state_dict(sd, strict=False)
+    assert not unexpected and not missing, (missing, unexpected)
+    blk.eval()
+    for tag, prefix in (("dit_block", 0), ("dit_block_video_kv", 40)):
+        x, context, context_mask, t_mod, freqs, video_kv = dit_block_case(DIT_TINY, video_prefix=prefix)
+        with torch.no_grad():
+            y, (k, v) = blk(x, context, t_mod, freqs, context_mask=context_mask, video_kv=video_kv, return_kv=True)
+        out[tag] = {"in_sum": checksum(x, context, t_mod, torch.view_as_real(freqs), *[t for t in bp.values()]),
+                    "y": y.clone(), "k": k.clone(), "v": v.clone()}
 
     # ---- request path: normaliser, prompt text, centred-padding resize -------------------
     from tybok.policies.pi05.models.flow_matching import resize_with_pad_torch

@@ -83,3 +83,22 @@ def test_pi05_tiny_batch2_matches_reference(golden):
     images, img_masks, tokens, masks, noise = tiny_inputs(PI05_TINY, seed=3, batch=2)
     actions = pi05_ref.sample_actions(params, PI05_TINY, images, img_masks, tokens, masks, noise)
     assert torch.equal(actions, golden["pi05_tiny_b2"]["actions"])
+
+
+@pytest.mark.parametrize("tag,prefix", [("dit_block", 0), ("dit_block_video_kv", 40)])
+def test_dit_block_matches_reference(golden, tag, prefix):
+    """``FastWAMAttentionBlock.forward`` (self-attention with qk-norm and dense RoPE, masked
+    cross-attention, modulated FFN), without and with keys / values of earlier tokens."""
+    from make_golden import dit_block_case
+
+    from oracle import dit_ref
+    from tybok_b200.shapes import DIT_TINY
+    from tybok_b200.weights import quantize_dit_block, random_dit_block_params
+
+    bp = quantize_dit_block(random_dit_block_params(DIT_TINY, seed=0))
+    x, context, context_mask, t_mod, freqs, video_kv = dit_block_case(DIT_TINY, video_prefix=prefix)
+    g = golden[tag]
+    assert checksum(x, context, t_mod, torch.view_as_real(freqs), *bp.values()) == g["in_sum"]
+    y, (k, v) = dit_ref.block_forward(bp, DIT_TINY.heads, x, context, t_mod, freqs, context_mask, video_kv, return_kv=True)
+    assert torch.equal(k, g["k"]) and torch.equal(v, g["v"])
+    assert torch.equal(y, g["y"])

@@ -2,7 +2,7 @@
 
 The pi0.5-shaped policy at full size (SigLIP-So400m on two 224x224 cameras, 18-layer Gemma-2B-shaped
 prefix over 544 tokens, 18-layer Gemma-300M-shaped expert, chunk 50, 10 flow steps), built exactly
-as ``bench.py`` builds it -- bf16 vision tower, first denoise step overlapped with the prefix, whole
+as ``bench.py`` builds it -- vision tower in fp32 with TF32 GEMMs, first denoise step overlapped with the prefix, whole
 chunk replayed from one CUDA graph, request through ``predict_action_chunk`` -- compared with
 ``oracle/pi05_ref.sample_actions`` (fp32 vision tower, bf16 dequantised decoders; the reference's
 eager path, tybok/policies/pi05/models/flow_matching.py:761-838) on the same seeded weights and
@@ -62,7 +62,7 @@ def test_benchmarked_configuration_matches_oracle(full_oracle_params):
 
     torch.set_num_threads(max(1, len(__import__("os").sched_getaffinity(0))))
     eng = PI05B200Engine("synthetic:pi05_full@0", device="cuda", graph=True, overlap=True, seed=0)
-    assert eng.graph_enabled and eng.model.overlap and eng.model.vision_dtype == torch.bfloat16
+    assert eng.graph_enabled and eng.model.overlap and eng.model.vision_tf32
     frames = _frames(eng, 1, seed=100)
     noise = torch.zeros(1, PI05_FULL.chunk, PI05_FULL.max_action_dim)
     assert eng._predict_chunk_static(frames[0], noise) is not None  # the path bench.py's e2e leg times

@@ -56,6 +56,13 @@ SIGNATURES = {
     ),
     "tybok_add_layernorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, ctypes.c_float, c_void_p,
                                     c_void_p, c_void_p]),
+    "tybok_add_layernorm_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, ctypes.c_float, c_void_p,
+                                        c_void_p, c_void_p]),
+    "tybok_layernorm_affine": (c_int, [c_void_p, c_i64, c_void_p, c_void_p, c_int, c_int, ctypes.c_float, c_void_p,
+                                       c_i64, c_void_p, c_int, c_void_p]),
+    "tybok_qknorm_rope_store": (c_int, [c_void_p, c_i64, c_int, c_int, c_int, c_void_p, c_void_p, ctypes.c_float,
+                                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                        c_int, c_int, c_void_p]),
     "tybok_w8a16_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "tybok_w8a16_linear": (
         c_int,

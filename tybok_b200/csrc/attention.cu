@@ -112,6 +112,104 @@ __global__ void rope_store_kernel(const RopeParams p) {
   }
 }
 
+// qk-norm + rotary embedding + KV store of a DiT block (tybok/policies/fastwam/models/dit_block.py:
+// 246-273, wan_base.py:97-128): per token row, q and k are RMS-normalised over ALL heads' channels
+// together (fp32 statistics, the normalised value rounded to bf16, then times a bf16 weight), rotated
+// pair-wise ((x[2i], x[2i+1]) times a complex table entry, fp32, rounded to bf16) and stored: q as
+// rows [M, H*D], k and the untouched v head-major into the caches [B, H, Lcap, D] at key_off.
+// One CTA per row, eight channels per thread.
+struct QkNormParams {
+  const __nv_bfloat16* src;
+  long long ld;
+  int q_off, k_off, v_off;     // column of q / k / v inside a source row; negative = absent
+  const __nv_bfloat16* wq;     // [H*D] norm weights
+  const __nv_bfloat16* wk;
+  const float* cos;            // [L][D/2] or NULL (no rotation)
+  const float* sin;
+  __nv_bfloat16* q_out;        // [M][H*D]
+  __nv_bfloat16* kcache;       // [B][H][Lcap][D]
+  __nv_bfloat16* vcache;
+  int M, L, H, D, Lcap, key_off;
+  float eps;
+  int pdl;
+};
+
+__global__ void __launch_bounds__(512) qknorm_rope_store_kernel(const QkNormParams p) {
+  __shared__ float red[2][16];
+  if (p.pdl) pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int m = blockIdx.x, c = threadIdx.x * 8, A = p.H * p.D;
+  const bool live = c < A;
+  const int b = m / p.L, t = m - b * p.L;
+  const int head = live ? c / p.D : 0, d0 = live ? c - head * p.D : 0;
+  // norm weights and rotary table entries are constants: fetch them before waiting for the producer
+  uint4 wq = {}, wk = {};
+  float4 cs = make_float4(1.f, 1.f, 1.f, 1.f), sn = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (live) {
+    if (p.q_off >= 0) wq = *reinterpret_cast<const uint4*>(p.wq + c);
+    if (p.k_off >= 0) wk = *reinterpret_cast<const uint4*>(p.wk + c);
+    if (p.cos) {
+      cs = *reinterpret_cast<const float4*>(p.cos + static_cast<long long>(t) * (p.D >> 1) + (d0 >> 1));
+      sn = *reinterpret_cast<const float4*>(p.sin + static_cast<long long>(t) * (p.D >> 1) + (d0 >> 1));
+    }
+  }
+  if (p.pdl) pdl_wait();
+  const __nv_bfloat16* row = p.src + static_cast<long long>(m) * p.ld;
+  uint4 rq = {}, rk = {}, rv = {};
+  float ssq = 0.f, ssk = 0.f;
+  if (live) {
+    if (p.q_off >= 0) rq = *reinterpret_cast<const uint4*>(row + p.q_off + c);
+    if (p.k_off >= 0) rk = *reinterpret_cast<const uint4*>(row + p.k_off + c);
+    if (p.v_off >= 0) rv = *reinterpret_cast<const uint4*>(row + p.v_off + c);
+    const __nv_bfloat16* hq = reinterpret_cast<const __nv_bfloat16*>(&rq);
+    const __nv_bfloat16* hk = reinterpret_cast<const __nv_bfloat16*>(&rk);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float a = __bfloat162float(hq[e]), kk = __bfloat162float(hk[e]);
+      ssq += a * a;
+      ssk += kk * kk;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+    ssk += __shfl_xor_sync(0xffffffffu, ssk, o);
+  }
+  if (lane == 0) {
+    red[0][warp] = ssq;
+    red[1][warp] = ssk;
+  }
+  __syncthreads();
+  float tq = 0.f, tk = 0.f;
+  for (int w = 0; w < nwarps; ++w) {
+    tq += red[0][w];
+    tk += red[1][w];
+  }
+  if (!live) return;
+  const float cosv[4] = {cs.x, cs.y, cs.z, cs.w}, sinv[4] = {sn.x, sn.y, sn.z, sn.w};
+  auto finish = [&](const uint4& raw, const uint4& wraw, float total) {
+    const float rstd = rsqrtf(total / static_cast<float>(A) + p.eps);
+    const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&raw);
+    const __nv_bfloat16* w = reinterpret_cast<const __nv_bfloat16*>(&wraw);
+    float n[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) n[e] = bf16_round(bf16_round(__bfloat162float(h[e]) * rstd) * __bfloat162float(w[e]));
+    uint4 out;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float a = n[2 * j], bb = n[2 * j + 1];
+      o2[j] = p.cos ? __floats2bfloat162_rn(a * cosv[j] - bb * sinv[j], a * sinv[j] + bb * cosv[j])
+                    : __floats2bfloat162_rn(a, bb);
+    }
+    return out;
+  };
+  const long long crow = ((static_cast<long long>(b) * p.H + head) * p.Lcap + p.key_off + t) * p.D + d0;
+  if (p.q_off >= 0) *reinterpret_cast<uint4*>(p.q_out + static_cast<long long>(m) * A + c) = finish(rq, wq, tq);
+  if (p.k_off >= 0) *reinterpret_cast<uint4*>(p.kcache + crow) = finish(rk, wk, tk);
+  if (p.v_off >= 0) *reinterpret_cast<uint4*>(p.vcache + crow) = rv;
+}
+
 struct AttnParams {
   int B, L, H, G, Lk, Lcap;
   int nsplit;
@@ -1085,6 +1183,47 @@ int tybok_rope_store(const void* qkv, int64_t ldq, const int* pos, const void* c
   cfg.attrs = attr;
   cfg.numAttrs = p.pdl;
   if (cudaLaunchKernelEx(&cfg, rope_store_kernel, p) != cudaSuccess) return host::fail_cuda("launch rope_store_kernel");
+  host::count_launch();
+  return TYBOK_OK;
+}
+
+int tybok_qknorm_rope_store(const void* src, int64_t ld, int q_off, int k_off, int v_off, const void* norm_q_weight,
+                            const void* norm_k_weight, float eps, const float* cos_table, const float* sin_table,
+                            void* q_out, void* k_cache, void* v_cache, int B, int L, int H, int D, int Lcap, int key_off,
+                            void* stream) {
+  using namespace tb;
+  if (!src || (q_off < 0 && k_off < 0)) return host::fail(TYBOK_ERR_ARG, "qknorm_rope_store: nothing to do (no q and no k)");
+  if ((q_off >= 0 && (!q_out || !norm_q_weight)) || (k_off >= 0 && (!k_cache || !norm_k_weight)) || (v_off >= 0 && !v_cache))
+    return host::fail(TYBOK_ERR_ARG, "qknorm_rope_store: null pointer for a requested output");
+  if ((cos_table == nullptr) != (sin_table == nullptr)) return host::fail(TYBOK_ERR_ARG, "qknorm_rope_store: cos and sin come together");
+  if (B <= 0 || L <= 0 || H <= 0 || D <= 0 || D % 8 != 0 || H * D > 4096 || key_off < 0 ||
+      ((k_off >= 0 || v_off >= 0) && key_off + L > Lcap))
+    return host::fail(TYBOK_ERR_ARG, "qknorm_rope_store: bad shape (D % 8 == 0, H*D <= 4096, key_off + L <= Lcap)");
+  if (ld % 8 != 0 || (q_off >= 0 && q_off % 8) || (k_off >= 0 && k_off % 8) || (v_off >= 0 && v_off % 8))
+    return host::fail(TYBOK_ERR_ARG, "qknorm_rope_store: row stride and column offsets must be multiples of 8");
+  if ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_cache) |
+       reinterpret_cast<uintptr_t>(v_cache) | reinterpret_cast<uintptr_t>(norm_q_weight) |
+       reinterpret_cast<uintptr_t>(norm_k_weight) | reinterpret_cast<uintptr_t>(cos_table) |
+       reinterpret_cast<uintptr_t>(sin_table)) & 15)
+    return host::fail(TYBOK_ERR_ARG, "qknorm_rope_store: tensors must be 16-byte aligned");
+  if (int rc = host::require_sm100()) return rc;
+  QkNormParams p{};
+  p.src = static_cast<const __nv_bfloat16*>(src); p.ld = ld; p.q_off = q_off; p.k_off = k_off; p.v_off = v_off;
+  p.wq = static_cast<const __nv_bfloat16*>(norm_q_weight); p.wk = static_cast<const __nv_bfloat16*>(norm_k_weight);
+  p.cos = cos_table; p.sin = sin_table; p.q_out = static_cast<__nv_bfloat16*>(q_out);
+  p.kcache = static_cast<__nv_bfloat16*>(k_cache); p.vcache = static_cast<__nv_bfloat16*>(v_cache);
+  p.M = B * L; p.L = L; p.H = H; p.D = D; p.Lcap = Lcap; p.key_off = key_off; p.eps = eps;
+  p.pdl = host::pdl_enabled() ? 1 : 0;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(p.M));
+  cfg.blockDim = dim3(static_cast<unsigned>(((H * D / 8) + 31) / 32 * 32));
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = p.pdl;
+  if (cudaLaunchKernelEx(&cfg, qknorm_rope_store_kernel, p) != cudaSuccess) return host::fail_cuda("launch qknorm_rope_store_kernel");
   host::count_launch();
   return TYBOK_OK;
 }

@@ -26,6 +26,7 @@ struct NormParams {
   const float* mod;     // [groups, ldmod] or NULL; scale at [0,W), shift at [W,2W)
   const __nv_bfloat16* ln_scale;  // [W] bf16: LayerNorm + modulate form when set
   const __nv_bfloat16* ln_shift;  // [W] bf16
+  int ln_affine;  // 1: ln_scale / ln_shift are an affine LayerNorm's weight / bias, y = bf16(LN(x) * w + b) in fp32
   long long ldmod;
   int rows_per_group;
   int M, W;
@@ -124,11 +125,16 @@ __global__ void __launch_bounds__(128) rmsnorm_kernel(const NormParams p) {
           const uint4 rh = *reinterpret_cast<const uint4*>(p.ln_shift + c * 8);
           const __nv_bfloat16* ps = reinterpret_cast<const __nv_bfloat16*>(&rs);
           const __nv_bfloat16* ph = reinterpret_cast<const __nv_bfloat16*>(&rh);
+          if (p.ln_affine) {  // fp32 statistics and fp32 affine, one rounding (wan_base.py:141-148)
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const float nrm = bf16_round(v[i][e] * rstd);
-            const float t = bf16_round(1.0f + __bfloat162float(ps[e]));
-            o[e] = bf16_round(nrm * t) + __bfloat162float(ph[e]);
+            for (int e = 0; e < 8; ++e) o[e] = v[i][e] * rstd * __bfloat162float(ps[e]) + __bfloat162float(ph[e]);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const float nrm = bf16_round(v[i][e] * rstd);
+              const float t = bf16_round(1.0f + __bfloat162float(ps[e]));
+              o[e] = bf16_round(nrm * t) + __bfloat162float(ph[e]);
+            }
           }
         } else {
         // x * rstd is formed in fp32 (the bf16 x promotes), as in the reference's _norm
@@ -412,12 +418,67 @@ __global__ void __launch_bounds__(256) add_layernorm_row_kernel(const AddLnParam
   }
 }
 
+// fp32 form of add_layernorm_row_kernel for the tower run in fp32 / TF32: x, y, weight, bias,
+// x_out and h are fp32; one CTA per row, four elements per thread.
+struct AddLnF32Params {
+  const float* x;
+  const float* y;  // or NULL
+  const float* w;
+  const float* b;
+  float* x_out;    // or NULL
+  float* h;
+  int M, W;
+  float eps;
+};
+
+__global__ void __launch_bounds__(512) add_layernorm_f32_kernel(const AddLnF32Params p) {
+  __shared__ float red[2][16];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int c = threadIdx.x * 4;
+  const bool live = c < p.W;
+  const long long base = static_cast<long long>(blockIdx.x) * p.W;
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f), rw = v, rb = v;
+  if (live) {
+    rw = *reinterpret_cast<const float4*>(p.w + c);
+    rb = *reinterpret_cast<const float4*>(p.b + c);
+    v = *reinterpret_cast<const float4*>(p.x + base + c);
+    if (p.y) {
+      const float4 u = *reinterpret_cast<const float4*>(p.y + base + c);
+      v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
+      if (p.x_out) *reinterpret_cast<float4*>(p.x_out + base + c) = v;
+    }
+  }
+  float sm = v.x + v.y + v.z + v.w;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sm += __shfl_xor_sync(0xffffffffu, sm, o);
+  if (lane == 0) red[0][warp] = sm;
+  __syncthreads();
+  float tot = 0.f;
+  for (int w = 0; w < nwarps; ++w) tot += red[0][w];
+  const float mean = tot / static_cast<float>(p.W);
+  float ss = 0.f;
+  if (live) {
+    v.x -= mean; v.y -= mean; v.z -= mean; v.w -= mean;
+    ss = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (lane == 0) red[1][warp] = ss;
+  __syncthreads();
+  tot = 0.f;
+  for (int w = 0; w < nwarps; ++w) tot += red[1][w];
+  const float rstd = rsqrtf(tot / static_cast<float>(p.W) + p.eps);
+  if (live)
+    *reinterpret_cast<float4*>(p.h + base + c) = make_float4(v.x * rstd * rw.x + rb.x, v.y * rstd * rw.y + rb.y,
+                                                              v.z * rstd * rw.z + rb.z, v.w * rstd * rw.w + rb.w);
+}
+
 }  // namespace tb
 
 namespace tb {
 static int launch_norm(const void* x, int64_t ldx, const float* weight, const float* mod, int64_t ldmod,
                        int rows_per_group, const void* ln_scale, const void* ln_shift, int M, int W, float eps, void* y,
-                       int64_t ldy, void* y_planes, int out_shift, void* stream) {
+                       int64_t ldy, void* y_planes, int out_shift, void* stream, int ln_affine = 0) {
   if (!x || (!y && !y_planes) || (!weight && !mod && !ln_scale)) return host::fail(TYBOK_ERR_ARG, "rmsnorm: null pointer argument");
   if (M <= 0 || W <= 0 || W % 8 != 0 || W > NORM_MAX_VEC * 256)
     return host::fail(TYBOK_ERR_ARG, "rmsnorm: W must be a multiple of 8 and <= 4096");
@@ -431,6 +492,7 @@ static int launch_norm(const void* x, int64_t ldx, const float* weight, const fl
   NormParams p{};
   p.x = static_cast<const __nv_bfloat16*>(x); p.ldx = ldx; p.weight = weight; p.mod = mod; p.ldmod = ldmod;
   p.ln_scale = static_cast<const __nv_bfloat16*>(ln_scale); p.ln_shift = static_cast<const __nv_bfloat16*>(ln_shift);
+  p.ln_affine = ln_affine;
   p.rows_per_group = rows_per_group > 0 ? rows_per_group : 1; p.M = M; p.W = W; p.eps = eps;
   p.plane_scale = ldexpf(1.0f, out_shift); p.planes = static_cast<uint8_t*>(y_planes);
   p.y = static_cast<__nv_bfloat16*>(y); p.ldy = ldy; p.pdl = host::pdl_enabled() ? 1 : 0;
@@ -510,12 +572,37 @@ int tybok_add_layernorm(const void* x, const void* y, const void* weight, const 
   return TYBOK_OK;
 }
 
+int tybok_add_layernorm_f32(const float* x, const float* y, const float* weight, const float* bias, int M, int W,
+                            float eps, float* x_out, float* h, void* stream) {
+  using namespace tb;
+  if (!x || !weight || !bias || !h) return host::fail(TYBOK_ERR_ARG, "add_layernorm_f32: null pointer argument");
+  if (M <= 0 || W <= 0 || W % 4 != 0 || W > 2048) return host::fail(TYBOK_ERR_ARG, "add_layernorm_f32: W must be a multiple of 4 and <= 2048");
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(weight) |
+       reinterpret_cast<uintptr_t>(bias) | reinterpret_cast<uintptr_t>(x_out) | reinterpret_cast<uintptr_t>(h)) & 15)
+    return host::fail(TYBOK_ERR_ARG, "add_layernorm_f32: tensors must be 16-byte aligned");
+  if (int rc = host::require_sm100()) return rc;
+  AddLnF32Params p{x, y, weight, bias, x_out, h, M, W, eps};
+  add_layernorm_f32_kernel<<<M, ((W / 4) + 31) / 32 * 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  if (cudaGetLastError() != cudaSuccess) return host::fail_cuda("launch add_layernorm_f32_kernel");
+  host::count_launch();
+  return TYBOK_OK;
+}
+
 int tybok_layernorm_modulate(const void* x, int64_t ldx, const void* shift, const void* scale, int M, int W, float eps,
                              void* y, int64_t ldy, void* y_planes, int out_shift, void* stream) {
   if (!shift || !scale) return tb::host::fail(TYBOK_ERR_ARG, "layernorm_modulate: null shift/scale");
   if ((reinterpret_cast<uintptr_t>(shift) | reinterpret_cast<uintptr_t>(scale)) & 15)
     return tb::host::fail(TYBOK_ERR_ARG, "layernorm_modulate: shift/scale must be 16-byte aligned");
   return tb::launch_norm(x, ldx, nullptr, nullptr, 0, 1, scale, shift, M, W, eps, y, ldy, y_planes, out_shift, stream);
+}
+
+
+int tybok_layernorm_affine(const void* x, int64_t ldx, const void* weight, const void* bias, int M, int W, float eps,
+                           void* y, int64_t ldy, void* y_planes, int out_shift, void* stream) {
+  if (!weight || !bias) return tb::host::fail(TYBOK_ERR_ARG, "layernorm_affine: null weight/bias");
+  if ((reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(bias)) & 15)
+    return tb::host::fail(TYBOK_ERR_ARG, "layernorm_affine: weight/bias must be 16-byte aligned");
+  return tb::launch_norm(x, ldx, nullptr, nullptr, 0, 1, weight, bias, M, W, eps, y, ldy, y_planes, out_shift, stream, 1);
 }
 
 }  // extern "C"

@@ -54,6 +54,12 @@ _L.define("w8x3_qkv_rope(Tensor planes, int shift, Tensor w8_paired, Tensor scal
 
 _L.define("add_layernorm(Tensor x, Tensor? y, Tensor weight, Tensor bias, float eps) -> (Tensor, Tensor)")
 
+_L.define("layernorm_affine(Tensor x, Tensor weight, Tensor bias, float eps, bool out_bf16, bool out_planes, "
+          "int out_shift) -> (Tensor, Tensor)")
+_L.define("qknorm_rope_store(Tensor src, int q_off, int k_off, int v_off, Tensor? norm_q, Tensor? norm_k, float eps, "
+          "Tensor? cos, Tensor? sin, Tensor(a!)? k_cache, Tensor(b!)? v_cache, int batch, int heads, int head_dim, "
+          "int key_off) -> Tensor")
+
 _status: dict[int, torch.Tensor] = {}
 
 
@@ -350,7 +356,77 @@ def _add_layernorm_cuda(x, y, weight, bias, eps):
     return x_out, h
 
 
-_L.impl("add_layernorm", _add_layernorm_cuda, "CUDA")
+def _add_layernorm_any(x, y, weight, bias, eps):
+    """bf16 or fp32 (every tensor of one dtype)."""
+    if x.dtype != torch.float32:
+        return _add_layernorm_cuda(x, y, weight, bias, eps)
+    lib = _lib.load()
+    w = x.shape[-1]
+    for t in (x, y, weight, bias):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+            raise TypeError("add_layernorm: tensors must be contiguous and of one dtype (bf16 or fp32)")
+    if (y is not None and y.shape != x.shape) or weight.numel() != w or bias.numel() != w:
+        raise ValueError("add_layernorm: shapes disagree")
+    m = x.numel() // w
+    x_out = torch.empty_like(x) if y is not None else x.new_empty(0)
+    h = torch.empty_like(x)
+    rc = lib.tybok_add_layernorm_f32(x.data_ptr(), _ptr(y), weight.data_ptr(), bias.data_ptr(), m, w, float(eps),
+                                     x_out.data_ptr() if y is not None else None, h.data_ptr(), _stream(x))
+    _lib.check(rc, "tybok_add_layernorm_f32")
+    return x_out, h
+
+
+def _layernorm_affine_cuda(x, weight, bias, eps, out_bf16, out_planes, out_shift):
+    lib = _lib.load()
+    if x.dtype != torch.bfloat16:
+        raise TypeError(f"layernorm_affine: x must be bf16, got {x.dtype}")
+    x2 = _rows(x)
+    m, w = x2.shape
+    for t in (weight, bias):
+        if t.dtype != torch.bfloat16 or t.numel() != w or not t.is_contiguous():
+            raise TypeError("layernorm_affine: weight/bias must be contiguous bf16 with W elements")
+    y, yp = _outputs(m, w, x.device, out_bf16, out_planes)
+    rc = lib.tybok_layernorm_affine(x2.data_ptr(), x2.stride(0), weight.data_ptr(), bias.data_ptr(), m, w, float(eps),
+                                    y.data_ptr() if out_bf16 else None, w, yp.data_ptr() if out_planes else None,
+                                    int(out_shift), _stream(x))
+    _lib.check(rc, "tybok_layernorm_affine")
+    return y, yp
+
+
+def _qknorm_rope_store_cuda(src, q_off, k_off, v_off, norm_q, norm_k, eps, cos, sin, k_cache, v_cache, batch, heads,
+                            head_dim, key_off):
+    lib = _lib.load()
+    if src.dtype != torch.bfloat16 or src.dim() != 2 or src.stride(1) != 1:
+        raise TypeError("qknorm_rope_store: src must be bf16 [B*L, C] with unit inner stride")
+    m, a = src.shape[0], heads * head_dim
+    if m % batch != 0:
+        raise ValueError("qknorm_rope_store: rows must be a multiple of the batch size")
+    l = m // batch
+    for t in (norm_q, norm_k):
+        if t is not None and (t.dtype != torch.bfloat16 or t.numel() != a or not t.is_contiguous()):
+            raise TypeError("qknorm_rope_store: norm weights must be contiguous bf16 [H*D]")
+    for t in (cos, sin):
+        if t is not None and (t.dtype != torch.float32 or tuple(t.shape) != (l, head_dim // 2) or not t.is_contiguous()):
+            raise TypeError("qknorm_rope_store: cos/sin must be contiguous fp32 [L, D/2]")
+    lcap = 0
+    for t in (k_cache, v_cache):
+        if t is not None:
+            if t.dtype != torch.bfloat16 or not t.is_contiguous() or t.dim() != 4 or t.shape[0] != batch \
+                    or t.shape[1] != heads or t.shape[3] != head_dim:
+                raise TypeError("qknorm_rope_store: caches must be contiguous bf16 [B, H, Lcap, D]")
+            lcap = t.shape[2]
+    q = torch.empty((m, a) if q_off >= 0 else (0,), dtype=torch.bfloat16, device=src.device)
+    rc = lib.tybok_qknorm_rope_store(src.data_ptr(), src.stride(0), int(q_off), int(k_off), int(v_off), _ptr(norm_q),
+                                     _ptr(norm_k), float(eps), _ptr(cos), _ptr(sin), q.data_ptr() if q_off >= 0 else None,
+                                     _ptr(k_cache), _ptr(v_cache), batch, l, heads, head_dim, lcap, int(key_off),
+                                     _stream(src))
+    _lib.check(rc, "tybok_qknorm_rope_store")
+    return q
+
+
+_L.impl("layernorm_affine", _layernorm_affine_cuda, "CUDA")
+_L.impl("qknorm_rope_store", _qknorm_rope_store_cuda, "CUDA")
+_L.impl("add_layernorm", _add_layernorm_any, "CUDA")
 _L.impl("split3", _split3_cuda, "CUDA")
 _L.impl("w8x3_linear", _w8x3_linear_cuda, "CUDA")
 _L.impl("w8x3_geglu", _w8x3_geglu_cuda, "CUDA")
@@ -467,10 +543,24 @@ def action_tail(x, mod, w_out, b_out, x_t, dt, w_in, b_in, *, rows_per_group=1, 
 
 
 def add_layernorm(x, y, weight, bias, *, eps=1e-6):
-    """``x_new = x + y`` (``y=None``: ``x``) and ``LayerNorm(x_new) * weight + bias``, bf16, one kernel;
-    returns ``(x_new, h)``; see ``tybok_add_layernorm``."""
+    """``x_new = x + y`` (``y=None``: ``x``) and ``LayerNorm(x_new) * weight + bias``, one kernel, all
+    tensors bf16 or all fp32; returns ``(x_new, h)``; see ``tybok_add_layernorm`` / ``_f32``."""
     x_new, h = torch.ops.tybok_b200.add_layernorm(x, y, weight, bias, eps)
     return (x if y is None else x_new), h
+
+
+def layernorm_affine(x, weight, bias, *, eps=1e-6, out_bf16=False, out_planes=True, out_shift=DEFAULT_SHIFT):
+    """``LayerNorm(x) * weight + bias`` (fp32 statistics and affine, one bf16 rounding); returns
+    ``(y_bf16, y_planes)``; see ``tybok_layernorm_affine``."""
+    return torch.ops.tybok_b200.layernorm_affine(x, weight, bias, eps, out_bf16, out_planes, out_shift)
+
+
+def qknorm_rope_store(src, *, q_off=-1, k_off=-1, v_off=-1, norm_q=None, norm_k=None, eps=1e-6, cos=None, sin=None,
+                      k_cache=None, v_cache=None, batch=1, heads, head_dim, key_off=0):
+    """Full-row RMS qk-norm + pair-wise rotary embedding + KV store of a DiT attention; returns the
+    finished q ``[B*L, H*D]`` (empty when ``q_off < 0``); see ``tybok_qknorm_rope_store``."""
+    return torch.ops.tybok_b200.qknorm_rope_store(src, q_off, k_off, v_off, norm_q, norm_k, eps, cos, sin, k_cache,
+                                                  v_cache, batch, heads, head_dim, key_off)
 
 
 def launch_count() -> int:

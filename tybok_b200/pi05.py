@@ -94,7 +94,7 @@ class PI05Model:
     """Weights + forward of a pi0.5-shaped policy on one GPU (inference only)."""
 
     def __init__(self, params: dict[str, torch.Tensor], shape: PI05Shape, device: str = "cuda",
-                 vision_dtype: torch.dtype = torch.bfloat16, overlap: bool = False):
+                 vision_dtype: torch.dtype = torch.bfloat16, overlap: bool = False, vision_tf32: bool = False):
         if not str(device).startswith("cuda"):
             raise RuntimeError("tybok_b200 has no CPU path: PI05Model needs a CUDA (sm_100) device")
         hd = shape.vlm.head_dim
@@ -111,8 +111,12 @@ class PI05Model:
         self.device = torch.device(device)
         dev = self.device
         self.vision_dtype = vision_dtype
+        #: fp32 tower with TF32 tensor-core GEMMs (10-bit mantissa operands, fp32 accumulation): the
+        #: prefix embeddings then agree with an fp32 tower to ~2e-3 rel-L2 where a bf16 tower is at 1.4e-2
+        self.vision_tf32 = bool(vision_tf32) and vision_dtype == torch.float32
         self.vision = {k: v.to(dev, vision_dtype) for k, v in params.items() if k.startswith(VISION)}
-        self.vis_layers = self._pack_vision() if vision_dtype == torch.bfloat16 else None
+        # the 7-kernel-per-layer form: bf16, or fp32 with TF32 GEMMs; plain fp32 keeps the unfused torch chain
+        self.vis_layers = self._pack_vision() if (vision_dtype == torch.bfloat16 or self.vision_tf32) else None
         self.proj_w = params[f"{PROJECTOR}.weight"].to(dev, vision_dtype)
         self.proj_b = params[f"{PROJECTOR}.bias"].to(dev, vision_dtype)
         self.embed = params[f"{VLM}.embed_tokens.weight"].to(dev)
@@ -182,14 +186,15 @@ class PI05Model:
         return layers
 
     def _embed_image_fused(self, image: torch.Tensor) -> torch.Tensor:
-        """The bf16 tower with 7 kernels per encoder layer instead of 14: each residual add runs
-        inside the LayerNorm kernel that follows it, q/k/v are one GEMM, GELU is the epilogue of
-        fc1 (same layer math as ``embed_image``; vision.py:200-289)."""
-        v, p = self.shape.vision, self.vision
+        """The tower with 7 kernels per encoder layer instead of 14: each residual add runs inside
+        the LayerNorm kernel that follows it, q/k/v are one GEMM, GELU is the epilogue of fc1 (same
+        layer math as ``embed_image``; vision.py:200-289).  bf16 throughout, or fp32 activations
+        with TF32 GEMMs."""
+        v, p, dt = self.shape.vision, self.vision, self.vision_dtype
         # Patch embedding as a GEMM over flattened patches (the stride == kernel convolution of
         # vision.py; cuDNN runs it as an fp32 direct convolution that takes longer than 20 layers' GEMMs).
         b, side = image.shape[0], v.image // v.patch
-        patches = image.to(torch.bfloat16).view(b, 3, side, v.patch, side, v.patch).permute(0, 2, 4, 1, 3, 5)
+        patches = image.to(dt).view(b, 3, side, v.patch, side, v.patch).permute(0, 2, 4, 1, 3, 5)
         patches = patches.reshape(b, side * side, 3 * v.patch * v.patch)
         wp = p[f"{VISION}.embeddings.patch_embedding.weight"]
         x = F.linear(patches, wp.view(wp.shape[0], -1), p[f"{VISION}.embeddings.patch_embedding.bias"])
@@ -214,7 +219,14 @@ class PI05Model:
         """SigLIP tower + projector (tybok/policies/pi05/models/vision.py:200-289); plain torch ops
         unless the tower is bf16."""
         if self.vis_layers is not None:
-            return self._embed_image_fused(image)
+            if not self.vision_tf32:
+                return self._embed_image_fused(image)
+            prev = torch.backends.cuda.matmul.allow_tf32
+            torch.backends.cuda.matmul.allow_tf32 = True
+            try:
+                return self._embed_image_fused(image)
+            finally:
+                torch.backends.cuda.matmul.allow_tf32 = prev
         v, p, dt = self.shape.vision, self.vision, self.vision_dtype
         x = F.conv2d(image.to(dt), p[f"{VISION}.embeddings.patch_embedding.weight"],
                      p[f"{VISION}.embeddings.patch_embedding.bias"], stride=v.patch)

@@ -161,3 +161,21 @@ def random_dit_block_params(shape: DiTShape, seed: int = 0, device: str = "cpu")
     p["ffn.2.bias"] = _normal(gen, (h,), bf16, device)
     p["modulation"] = _normal(gen, (1, 6, h), bf16, device, std=1.0 / h**0.5)
     return p
+
+
+#: Linear sub-modules of one DiT block that run as W8 GEMMs.
+DIT_HOT_LINEARS = ("self_attn.q", "self_attn.k", "self_attn.v", "self_attn.o", "cross_attn.q", "cross_attn.k",
+                   "cross_attn.v", "cross_attn.o", "ffn.0", "ffn.2")
+
+
+def quantize_dit_block(params: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+    """The on-disk fp8 form of one DiT block: every projection and FFN matrix as e4m3 ``<lin>.weight``
+    + fp32 ``<lin>.scale_weight`` (docs/fastWAM_weight_quantization.md:14-24); biases, norm weights and
+    the modulation table stay bf16.  Weights that are already e4m3 are kept."""
+    out = dict(params)
+    for lin in DIT_HOT_LINEARS:
+        w = out[f"{lin}.weight"]
+        if w.dtype == torch.float8_e4m3fn:
+            continue
+        out[f"{lin}.weight"], out[f"{lin}.scale_weight"] = quantize_w8(w)
+    return out
