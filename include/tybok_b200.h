@@ -158,6 +158,10 @@ int tybok_action_tail(const void* x, int64_t ldx, const float* mod, int64_t ldmo
 int tybok_add_layernorm(const void* x, const void* y, const void* weight, const void* bias, int M, int W, float eps,
                         void* x_out, void* h, void* stream);
 
+/* The same with the residual stream kept in fp32: x and x_out fp32, y / weight / bias / h bf16
+ * (W % 8 == 0, W <= 2048).  A bf16 tower run this way never rounds its stream to bf16. */
+int tybok_add_layernorm_mixed(const float* x, const void* y, const void* weight, const void* bias, int M, int W, float eps,
+                              float* x_out, void* h, void* stream);
 /* The same in fp32 (all six tensors fp32; W % 4 == 0, W <= 2048), for a tower run in fp32 / TF32. */
 int tybok_add_layernorm_f32(const float* x, const float* y, const float* weight, const float* bias, int M, int W,
                             float eps, float* x_out, float* h, void* stream);

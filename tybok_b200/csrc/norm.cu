@@ -418,6 +418,83 @@ __global__ void __launch_bounds__(256) add_layernorm_row_kernel(const AddLnParam
   }
 }
 
+// Mixed form for a bf16 tower whose residual stream stays in fp32: x and x_out fp32, the sublayer
+// output y, weight, bias and the normalised h bf16.  The stream is then never rounded to bf16
+// (only the GEMM inputs are), which is where a bf16 tower loses most of its accuracy: the stream is
+// several times larger than what a sublayer adds to it.  One CTA per row, eight elements per thread.
+struct AddLnMixedParams {
+  const float* x;
+  const __nv_bfloat16* y;  // or NULL
+  const __nv_bfloat16* w;
+  const __nv_bfloat16* b;
+  float* x_out;            // or NULL
+  __nv_bfloat16* h;
+  int M, W;
+  float eps;
+};
+
+__global__ void __launch_bounds__(256) add_layernorm_mixed_kernel(const AddLnMixedParams p) {
+  __shared__ float red[2][8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int c = threadIdx.x * 8;
+  const bool live = c < p.W;
+  const long long base = static_cast<long long>(blockIdx.x) * p.W;
+  uint4 rw = {}, rb = {};
+  float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  float sm = 0.f;
+  if (live) {
+    rw = *reinterpret_cast<const uint4*>(p.w + c);
+    rb = *reinterpret_cast<const uint4*>(p.b + c);
+    const float4 a0 = *reinterpret_cast<const float4*>(p.x + base + c);
+    const float4 a1 = *reinterpret_cast<const float4*>(p.x + base + c + 4);
+    v[0] = a0.x; v[1] = a0.y; v[2] = a0.z; v[3] = a0.w; v[4] = a1.x; v[5] = a1.y; v[6] = a1.z; v[7] = a1.w;
+    if (p.y) {
+      const uint4 ry = *reinterpret_cast<const uint4*>(p.y + base + c);
+      const __nv_bfloat16* hy = reinterpret_cast<const __nv_bfloat16*>(&ry);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] += __bfloat162float(hy[e]);
+      if (p.x_out) {
+        *reinterpret_cast<float4*>(p.x_out + base + c) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(p.x_out + base + c + 4) = make_float4(v[4], v[5], v[6], v[7]);
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) sm += v[e];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sm += __shfl_xor_sync(0xffffffffu, sm, o);
+  if (lane == 0) red[0][warp] = sm;
+  __syncthreads();
+  float tot = 0.f;
+  for (int w = 0; w < nwarps; ++w) tot += red[0][w];
+  const float mean = tot / static_cast<float>(p.W);
+  float ss = 0.f;
+  if (live) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      v[e] -= mean;
+      ss += v[e] * v[e];
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (lane == 0) red[1][warp] = ss;
+  __syncthreads();
+  tot = 0.f;
+  for (int w = 0; w < nwarps; ++w) tot += red[1][w];
+  const float rstd = rsqrtf(tot / static_cast<float>(p.W) + p.eps);
+  if (live) {
+    const __nv_bfloat16* pw = reinterpret_cast<const __nv_bfloat16*>(&rw);
+    const __nv_bfloat16* pb = reinterpret_cast<const __nv_bfloat16*>(&rb);
+    __nv_bfloat162 o[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      o[e] = __floats2bfloat162_rn(v[2 * e] * rstd * __bfloat162float(pw[2 * e]) + __bfloat162float(pb[2 * e]),
+                                   v[2 * e + 1] * rstd * __bfloat162float(pw[2 * e + 1]) + __bfloat162float(pb[2 * e + 1]));
+    *reinterpret_cast<uint4*>(p.h + base + c) = *reinterpret_cast<const uint4*>(o);
+  }
+}
+
 // fp32 form of add_layernorm_row_kernel for the tower run in fp32 / TF32: x, y, weight, bias,
 // x_out and h are fp32; one CTA per row, four elements per thread.
 struct AddLnF32Params {
@@ -568,6 +645,23 @@ int tybok_add_layernorm(const void* x, const void* y, const void* weight, const 
   else if (per_lane <= 5) e = cudaLaunchKernelEx(&cfg, add_layernorm_kernel<5>, p);
   else e = cudaLaunchKernelEx(&cfg, add_layernorm_kernel<8>, p);
   if (e != cudaSuccess) return host::fail_cuda("launch add_layernorm_kernel");
+  host::count_launch();
+  return TYBOK_OK;
+}
+
+int tybok_add_layernorm_mixed(const float* x, const void* y, const void* weight, const void* bias, int M, int W, float eps,
+                              float* x_out, void* h, void* stream) {
+  using namespace tb;
+  if (!x || !weight || !bias || !h) return host::fail(TYBOK_ERR_ARG, "add_layernorm_mixed: null pointer argument");
+  if (M <= 0 || W <= 0 || W % 8 != 0 || W > 2048) return host::fail(TYBOK_ERR_ARG, "add_layernorm_mixed: W must be a multiple of 8 and <= 2048");
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(weight) |
+       reinterpret_cast<uintptr_t>(bias) | reinterpret_cast<uintptr_t>(x_out) | reinterpret_cast<uintptr_t>(h)) & 15)
+    return host::fail(TYBOK_ERR_ARG, "add_layernorm_mixed: tensors must be 16-byte aligned");
+  if (int rc = host::require_sm100()) return rc;
+  AddLnMixedParams p{x, static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(weight),
+                     static_cast<const __nv_bfloat16*>(bias), x_out, static_cast<__nv_bfloat16*>(h), M, W, eps};
+  add_layernorm_mixed_kernel<<<M, ((W / 8) + 31) / 32 * 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  if (cudaGetLastError() != cudaSuccess) return host::fail_cuda("launch add_layernorm_mixed_kernel");
   host::count_launch();
   return TYBOK_OK;
 }

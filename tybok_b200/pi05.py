@@ -117,6 +117,7 @@ class PI05Model:
         self.vision = {k: v.to(dev, vision_dtype) for k, v in params.items() if k.startswith(VISION)}
         # the 7-kernel-per-layer form: bf16, or fp32 with TF32 GEMMs; plain fp32 keeps the unfused torch chain
         self.vis_layers = self._pack_vision() if (vision_dtype == torch.bfloat16 or self.vision_tf32) else None
+        self.pos_embed_f32 = params[f"{VISION}.embeddings.position_embedding.weight"].to(dev).float()
         self.proj_w = params[f"{PROJECTOR}.weight"].to(dev, vision_dtype)
         self.proj_b = params[f"{PROJECTOR}.bias"].to(dev, vision_dtype)
         self.embed = params[f"{VLM}.embed_tokens.weight"].to(dev)
@@ -198,16 +199,22 @@ class PI05Model:
         patches = patches.reshape(b, side * side, 3 * v.patch * v.patch)
         wp = p[f"{VISION}.embeddings.patch_embedding.weight"]
         x = F.linear(patches, wp.view(wp.shape[0], -1), p[f"{VISION}.embeddings.patch_embedding.bias"])
-        x = x + p[f"{VISION}.embeddings.position_embedding.weight"][None]
+        # The residual stream is fp32 whatever the GEMM precision (the LayerNorm kernel adds the bf16
+        # sublayer output to it): a stream rounded to bf16 after each of the 54 adds is where a bf16
+        # tower loses most of its accuracy, and the fp32 stream costs a few bytes per element.
+        x = x.float() + self.pos_embed_f32[None]
         b, l, hid = x.shape
         hd = hid // v.heads
         y = None
         for lay in self.vis_layers:
             x, h = ops.add_layernorm(x, y, *lay["ln1"])
-            qkv = F.linear(h, lay["qkv_w"], lay["qkv_b"]).view(b, l, 3, v.heads, hd)
+            # attention itself always runs on bf16 operands (the flash kernel; an fp32 tower would take
+            # a three times slower one): what it rounds is per-token noise that the 256-token averages
+            # after it wash out, unlike a rounded weight, which errs the same way for every token
+            qkv = F.linear(h, lay["qkv_w"], lay["qkv_b"]).to(torch.bfloat16).view(b, l, 3, v.heads, hd)
             q, k, val = (qkv[:, :, j].transpose(1, 2) for j in range(3))
             a = F.scaled_dot_product_attention(q, k, val, scale=hd**-0.5).transpose(1, 2).reshape(b, l, hid)
-            y = F.linear(a, *lay["o"])
+            y = F.linear(a.to(dt), *lay["o"])
             x, h = ops.add_layernorm(x, y, *lay["ln2"])
             h = torch._addmm_activation(lay["fc1_b"], h.view(b * l, hid), lay["fc1_wt"], use_gelu=True)  # tanh GELU
             y = F.linear(h, *lay["fc2"]).view(b, l, hid)
