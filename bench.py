@@ -21,8 +21,9 @@ collective); the time is the max over ranks.  The line also carries
   ``extra.dit_ffn_tp`` (N > 1): the tensor-parallel DiT FFN over the N ranks with its all-reduce timed.
 
 ``--impl reference`` times the CPU oracle alone (rank 0 only under torchrun).  Other workloads:
-``dit_ffn`` (one DiT block's FFN tail), ``gemm`` / ``attention`` (small fixed cases for profiler
-captures).  One JSON line on rank 0.
+``dit`` (the fastWAM-class DiT denoiser, 30 blocks x 4 steps over 4146 tokens, its FFN tensor-parallel
+over the N ranks), ``dit_ffn`` (one block's FFN tail), ``gemm`` / ``attention`` (small fixed cases
+for profiler captures).  One JSON line on rank 0.
 """
 
 from __future__ import annotations
@@ -598,6 +599,203 @@ def run_dit_ffn(args, rank: int, world: int) -> None:
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------------ DiT denoiser
+DIT_METRIC = "dit_fp8_denoise_ms"
+DIT_WORKLOAD = ("fastWAM-class DiT denoiser: 30 blocks, hidden 3072, 24 heads x 128, FFN 14336; 4096 latent-video + 50 "
+                "action tokens, 129-token context (128 text embeddings + 1 proprio token from a 14-dim state), 4 steps")
+
+
+def _dit_inputs(S, device, seed: int = 0):
+    """Seeded inputs of the denoiser: tokens ~N(0,1), a context of 128 text embeddings plus one
+    proprio token ``Linear(14 -> hidden)(state)`` with the last four text tokens masked, per-step
+    modulation tables, the dense rotary table, the shifted flow schedule's step sizes."""
+    from oracle.dit_ref import sampling_deltas  # schedule arithmetic only (a few floats)
+
+    g = torch.Generator().manual_seed(seed)
+    x = torch.empty(S.seq, S.hidden).normal_(0, 1, generator=g).to(torch.bfloat16)
+    text = torch.empty(S.context_len - 1, S.hidden).normal_(0, 1, generator=g)
+    state = torch.empty(S.state_dim).normal_(0, 1, generator=g)
+    proprio = torch.empty(S.hidden, S.state_dim).normal_(0, 0.3, generator=g) @ state
+    context = torch.cat([text, proprio[None]]).to(torch.bfloat16)
+    mask = torch.ones(S.context_len, dtype=torch.bool)
+    mask[S.context_len - 5 : S.context_len - 1] = False
+    t_mods = torch.empty(S.steps, 6, S.hidden).normal_(0, 0.5, generator=g).to(torch.bfloat16)
+    ang = torch.outer(torch.arange(S.seq, dtype=torch.float64),
+                      1.0 / torch.pow(10000, torch.arange(0, S.head_dim, 2, dtype=torch.float64) / S.head_dim))
+    freqs = torch.polar(torch.ones_like(ang), ang)[:, None, :]
+    return {"x": x, "context": context, "mask": mask, "t_mods": t_mods, "freqs": freqs, "deltas": sampling_deltas(S.steps)}
+
+
+def _dit_flops(S) -> float:
+    """Dense flops of one pass (all steps): projections + FFN + self-attention + cross-attention."""
+    a = S.heads * S.head_dim
+    lin = 2.0 * S.seq * (3 * a * S.hidden + a * S.hidden + 2 * a * S.hidden + 2 * S.hidden * S.ffn)
+    attn = 4.0 * S.seq * S.seq * S.head_dim * S.heads + 4.0 * S.seq * S.context_len * S.head_dim * S.heads
+    return S.steps * S.blocks * (lin + attn)
+
+
+def _dit_cpu_block(S, inp, bp_cpu, reps: int):
+    """One block of the denoiser on the CPU oracle at the full sequence length; returns (times ms, output)."""
+    from oracle import dit_ref
+
+    times, y = [], None
+    for i in range(1 + reps):
+        t0 = time.perf_counter()
+        y = dit_ref.block_forward(bp_cpu, S.heads, inp["x"][None], inp["context"][None], inp["t_mods"][0][None], inp["freqs"],
+                                  inp["mask"][None])
+        if i:
+            times.append((time.perf_counter() - t0) * 1e3)
+    return times, y
+
+
+def run_dit_reference(args, rank: int) -> None:
+    """Reference arm of the DiT workload: the CPU oracle on ONE block at the full sequence length
+    (a bounded sample), extrapolated to blocks x steps; rank 0 only, nothing on a GPU."""
+    if rank != 0:
+        return
+    from tybok_b200.shapes import DIT_FULL as S
+    from tybok_b200.weights import quantize_dit_block, random_dit_block_params
+
+    cores = _all_host_threads()
+    bp = quantize_dit_block(random_dit_block_params(S, seed=0, device="cpu"))
+    inp = _dit_inputs(S, "cpu")
+    times, _ = _dit_cpu_block(S, inp, bp, max(1, min(args.steps, 5)))
+    blk = statistics.median(times)
+    value = blk * S.blocks * S.steps
+    print(json.dumps({
+        "impl": "reference", "metric": DIT_METRIC, "value": round(value, 1), "unit": "ms", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(value, 1), "higher_is_better": False,
+        "scaling": "strong", "vs_baseline": None, "dtype": DTYPE + " (weights dequantised to bf16, fp32 attention)",
+        "data": "synthetic", "config": {"workload": DIT_WORKLOAD, "tensor_parallel_ffn": args.gpus},
+        "cpu_baseline": {"value": round(value, 1), "unit": "ms", "cores": cores, "kind": "port",
+                         "sample": f"one block at 4146 tokens timed {len(times)}x after 1 warm-up ({blk:.0f} ms median, "
+                                   f"oracle/dit_ref.py), extrapolated x {S.blocks} blocks x {S.steps} steps"},
+        "e2e": {"value": round(value, 1), "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0}), flush=True)
+
+
+def run_dit(args, rank: int, world: int) -> None:
+    """The whole DiT denoiser: one "step" of this workload is one denoise pass (4 flow steps x 30
+    blocks) over one 4146-token sequence.  With N > 1 the FFN of every block is tensor-parallel over
+    the ranks (one NCCL all-reduce per block and step); attention and projections are replicated.
+    Strong scaling: the work is fixed."""
+    import torch.distributed as dist
+
+    from tybok_b200 import ops
+    from tybok_b200.dit import DiTDenoiser, rotary_parts
+    from tybok_b200.shapes import DIT_FULL as S
+    from tybok_b200.weights import quantize_dit_block, random_dit_block_params
+
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = f"cuda:{local}"
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    peaks, peaks_kind = _peaks()
+    l0 = ops.launch_count()
+    den = DiTDenoiser([], S, device=dev, rank=rank, world=world)
+    from tybok_b200.dit import DiTBlock
+
+    bp0 = None
+    for i in range(S.blocks):  # the same seeded weights on every rank; bf16 masters are dropped block by block
+        bp = quantize_dit_block(random_dit_block_params(S, seed=i, device=dev))
+        if i == 0 and rank == 0 and not args.no_cpu_baseline:
+            bp0 = {k: v.cpu() for k, v in bp.items()}
+        den.blocks.append(DiTBlock(bp, S, device=dev, rank=rank, world=world))
+        del bp
+    torch.cuda.empty_cache()
+    inp = _dit_inputs(S, dev)
+    pinned = {k: inp[k].pin_memory() for k in ("x", "context", "t_mods")}
+    cos, sin = rotary_parts(inp["freqs"], dev)
+    den.prepare_context(inp["context"].to(dev), inp["mask"])
+    x_d, tm_d = inp["x"].to(dev), inp["t_mods"].to(dev)
+
+    def one_pass(x):
+        return den.denoise(x, tm_d, cos, sin, inp["deltas"])
+
+    for _ in range(max(1, min(args.warmup, 3))):
+        one_pass(x_d)
+    torch.cuda.synchronize()
+    launches_per_pass = None
+    n0 = ops.launch_count()
+    one_pass(x_d)
+    launches_per_pass = ops.launch_count() - n0
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    steps = max(1, min(args.steps, 10))
+    sampler = ClockSampler(local)
+    sampler.start()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for e0, e1 in evs:
+        e0.record()
+        out = one_pass(x_d)
+        e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    clocks = sampler.stop()
+    ms = statistics.median(a.elapsed_time(b) for a, b in evs)
+    # end to end from host buffers: tokens, context and modulation tables up, the denoised tokens down
+    e2e = []
+    host_out = torch.empty(inp["x"].shape, dtype=torch.bfloat16).pin_memory()
+    for _ in range(min(3, steps)):
+        t0 = time.perf_counter()
+        xd = pinned["x"].to(dev, non_blocking=True)
+        den.prepare_context(pinned["context"].to(dev, non_blocking=True), inp["mask"])
+        tm = pinned["t_mods"].to(dev, non_blocking=True)
+        host_out.copy_(den.denoise(xd, tm, cos, sin, inp["deltas"]), non_blocking=True)
+        torch.cuda.synchronize()
+        e2e.append((time.perf_counter() - t0) * 1e3)
+    e2e_ms = statistics.median(e2e)
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), float(t[1])
+    ops.check_status()
+    flops = _dit_flops(S)
+    if rank == 0:
+        cpu = parity = None
+        if bp0 is not None:
+            from oracle import w8_ref
+
+            cores = _all_host_threads()
+            times, ref = _dit_cpu_block(S, inp, bp0, 2)
+            got = den.blocks[0].forward(x_d, den.blocks[0].modulations(tm_d[0]), cos, sin, den._cache(S.seq), 0,
+                                        den._cross[0], den._ctx_valid)
+            if world > 1:
+                parity = None  # block 0's FFN is sharded: its all-reduce needs every rank (checked by the N = 1 run)
+            else:
+                parity = {"rel_l2": round(w8_ref.rel_l2(got.float().cpu()[None], ref.float()), 6), "tolerance_rel_l2": 1e-2,
+                          "what": "block 0 at 4146 tokens on the GPU vs oracle/dit_ref.block_forward, same weights and inputs"}
+            blk = statistics.median(times)
+            cpu = {"value": round(blk * S.blocks * S.steps, 1), "unit": "ms", "cores": cores, "kind": "port",
+                   "sample": f"one block at 4146 tokens timed {len(times)}x after 1 warm-up ({blk:.0f} ms median), "
+                             f"extrapolated x {S.blocks} blocks x {S.steps} steps"}
+        tf = flops / ms / 1e9
+        peak = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]) * world
+        print(json.dumps({
+            "metric": DIT_METRIC, "value": round(ms, 3), "unit": "ms", "n_gpus": world, "steps": steps,
+            "warmup": max(1, min(args.warmup, 3)), "ms_per_step": round(ms, 3), "higher_is_better": False,
+            "scaling": "strong", "vs_baseline": None, "dtype": DTYPE + " (activations as 3 exact e5m2 planes), bf16 attention",
+            "data": "synthetic", "config": {"workload": DIT_WORKLOAD, "tensor_parallel_ffn": world},
+            "run": {"cuda_graph": False, "l2": "4.3 GB of e4m3 weights per step exceed the 126 MB L2"},
+            "clocks": clocks, "gpu_launches": launches_per_pass * steps,
+            "e2e": {"value": round(e2e_ms, 3), "unit": "ms", "h2d_bytes_per_step": sum(v.numel() * 2 for v in pinned.values()),
+                    "d2h_bytes_per_step": host_out.numel() * 2},
+            "parity": parity,
+            "roofline": {"bound": "tensor", "kernel": "whole pass (w8_gemm_kernel pairs + attention_prefill_kernel<128>)",
+                         "achieved": round(tf, 1), "peak": peak, "unit": "TFLOP/s", "frac": round(tf / peak, 4),
+                         "traffic": None, "peak_source": peaks_kind + " (sustained bf16 x ranks; only the FFN is sharded)",
+                         "flops_per_pass": flops},
+            "cpu_baseline": cpu, "finite": bool(torch.isfinite(out.float()).all()),
+        }), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+
 def run_profile_case(args) -> None:
     """Small fixed workloads for profiler captures: a few launches over a few hundred MB.
 
@@ -647,7 +845,7 @@ def main() -> None:
     ap.add_argument("--no-overlap", action="store_true", help="run the first denoise step after the prefix, not behind it")
     ap.add_argument("--vision-precision", default="tf32", choices=["tf32", "bf16", "fp32"],
                     help="SigLIP tower: fp32 activations with TF32 GEMMs (default), all bf16, or plain fp32")
-    ap.add_argument("--workload", default="pi05_chunk", choices=["pi05_chunk", "dit_ffn", "gemm", "attention"])
+    ap.add_argument("--workload", default="pi05_chunk", choices=["pi05_chunk", "dit", "dit_ffn", "gemm", "attention"])
     for name, default in (("m", 50), ("n", 16384), ("k", 2048), ("launches", 6), ("tokens", 50), ("prefix", 544),
                           ("head-dim", 256), ("heads", 8)):
         ap.add_argument(f"--{name}", type=int, default=default)
@@ -657,7 +855,7 @@ def main() -> None:
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     if args.impl == "reference":
-        run_reference(args, rank)
+        (run_dit_reference if args.workload == "dit" else run_reference)(args, rank)
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device -- the product path has no CPU fallback (use --impl reference "
@@ -666,6 +864,8 @@ def main() -> None:
         run_profile_case(args)
     elif args.workload == "dit_ffn":
         run_dit_ffn(args, rank, world)
+    elif args.workload == "dit":
+        run_dit(args, rank, world)
     else:
         run_ours(args, rank, world)
 
