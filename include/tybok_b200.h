@@ -244,6 +244,13 @@ void tybok_set_pdl(int enabled);
  * kernels record SM clock samples at their phase boundaries into it.  NULL (default) = off. */
 void tybok_debug_set_trace(void* device_buffer);
 
+/* Debugging aid: with a zeroed device buffer of 128 ints, every CTA of the following launches bumps
+ * counter [kernel * 8 + stage] at its stage boundaries (stage 0 entered, 1 set-up done / tensor memory
+ * held, 2 predecessor awaited, 3 main loop done, 4 leaving; kernels: 0-2 w8_gemm_kernel (8 warps, 16
+ * warps, pair), 5 / 6 attention_prefill_kernel<256> / <128>, 7 qknorm_rope_store_kernel, 8 norm
+ * kernels).  Read from another stream, it tells where a stalled chain stands.  NULL (default) = off. */
+void tybok_debug_set_counters(void* device_buffer);
+
 /* Test aid: how many SM clocks the epilogue warps of the following GEMM launches wait for their
  * accumulator before they give up, record TYBOK_DEV_TIMEOUT_EPILOGUE in the status word and skip
  * their stores (the producer, the MMA warp and the unwinding keep the production limit of about a

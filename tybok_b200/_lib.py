@@ -21,6 +21,7 @@ SIGNATURES = {
     "tybok_launch_count": (ctypes.c_longlong, []),
     "tybok_set_pdl": (None, [c_int]),
     "tybok_debug_set_trace": (None, [c_void_p]),
+    "tybok_debug_set_counters": (None, [c_void_p]),
     "tybok_debug_set_epilogue_wait_limit": (None, [ctypes.c_longlong]),
     "tybok_split3": (c_int, [c_void_p, c_i64, c_void_p, c_int, c_int, c_int, c_void_p]),
     "tybok_w8x3_linear": (

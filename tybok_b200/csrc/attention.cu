@@ -132,11 +132,13 @@ struct QkNormParams {
   int M, L, H, D, Lcap, key_off;
   float eps;
   int pdl;
+  int* dbg;
 };
 
 __global__ void __launch_bounds__(512) qknorm_rope_store_kernel(const QkNormParams p) {
   __shared__ float red[2][16];
   if (p.pdl) pdl_launch_dependents();
+  if (threadIdx.x == 0) dbg_stage(p.dbg, 7, 0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int m = blockIdx.x, c = threadIdx.x * 8, A = p.H * p.D;
   const bool live = c < A;
@@ -154,6 +156,7 @@ __global__ void __launch_bounds__(512) qknorm_rope_store_kernel(const QkNormPara
     }
   }
   if (p.pdl) pdl_wait();
+  if (threadIdx.x == 0) dbg_stage(p.dbg, 7, 2);
   const __nv_bfloat16* row = p.src + static_cast<long long>(m) * p.ld;
   uint4 rq = {}, rk = {}, rv = {};
   float ssq = 0.f, ssk = 0.f;
@@ -208,6 +211,7 @@ __global__ void __launch_bounds__(512) qknorm_rope_store_kernel(const QkNormPara
   if (p.q_off >= 0) *reinterpret_cast<uint4*>(p.q_out + static_cast<long long>(m) * A + c) = finish(rq, wq, tq);
   if (p.k_off >= 0) *reinterpret_cast<uint4*>(p.kcache + crow) = finish(rk, wk, tk);
   if (p.v_off >= 0) *reinterpret_cast<uint4*>(p.vcache + crow) = rv;
+  if (threadIdx.x == 0) dbg_stage(p.dbg, 7, 4);
 }
 
 struct AttnParams {
@@ -224,6 +228,7 @@ struct AttnParams {
   int q_rows;        // query rows per bulk copy: 128, or 64 when all real rows fit (the rest of the tile is never read back)
   int dsplit;        // 1, or 2: two CTAs per (query tile, key block), each producing half of the output columns
   long long* trace;  // tuning aid: [CTA][16] SM-clock samples, NULL in production
+  int* dbg;          // debugging aid: stage counters, NULL in production
 };
 
 struct __align__(16) AttnBars {
@@ -817,20 +822,26 @@ struct __align__(8) PrefillBars {
   float hsum[2][AT_BQ];     // [half][row]: sum of that half's probabilities over all blocks
 };
 
-// HD = head dimension, 128 or 256.  With 128 two CTAs share an SM (96 KB of shared memory and 256
-// tensor-memory columns each), so one tile's softmax runs under the other's products.
+// HD = head dimension, 128 or 256.  Either way a CTA takes ALL 512 tensor-memory columns of its SM
+// and therefore has the SM's tensor memory to itself.  (At HD = 128 two CTAs of 256 columns each
+// would fit, and ran, but chains that alternate this kernel with the CTA-pair GEMM -- whose two CTAs
+// allocate 256 columns collectively on two SMs -- then stalled once in some 10^5 launches with one
+// GEMM pair waiting for tensor memory on an otherwise idle device.  Whole-SM allocations next to
+// the pair GEMM are the combination that has run the pi0.5 prefix 10^6 launches without a stall.)
 template <int HD>
-__global__ void __launch_bounds__(AT_THREADS, HD == 128 ? 2 : 1)
+__global__ void __launch_bounds__(AT_THREADS, 1)
 attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                          const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ PrefillBars bars;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int KID = HD == 256 ? 5 : 6;
+  if (tid == 0) dbg_stage(p.dbg, KID, 0);
   constexpr int NCH = HD / 64;              // 64-column chunks of a Q, K or V row
   constexpr int PF_KV = NCH * PF_KCHUNK;    // one K or V block: 64 keys x HD
   constexpr int Q_TILE = NCH * AT_CHUNK;    // 128 query rows x HD
-  constexpr int T_COLS = HD == 256 ? 512 : 256;  // tensor memory: S / P at columns 0 and 64, O behind them
+  constexpr int T_COLS = 512;               // tensor memory: S / P at columns 0 and 64, O behind them
   constexpr int OCH = HD / 64;              // 32-column chunks of O per thread (its half of the row)
   uint8_t* sq = smem;
   uint8_t* sk = smem + Q_TILE;               // two K blocks
@@ -879,6 +890,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
   tc_fence_after();
   const uint32_t tmem = bars.tmem_base;
   const uint32_t t_o = tmem + (HD == 256 ? 256 : 128);  // S_j (and P_j over it) at columns 64 * (j & 1)
+  if (tid == 0) dbg_stage(p.dbg, KID, 1);
   long long* tr = p.trace ? p.trace + 16ll * ((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) : nullptr;
   const long long t_start = clock64();
   if (tr && tid == 0) tr[0] = t_start;
@@ -887,6 +899,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
     if (lane == 0) {
       if (p.pdl) pdl_launch_dependents();
       if (p.pdl) pdl_wait();
+      dbg_stage(p.dbg, KID, 2);
       mbar_arrive_expect_tx(&bars.q_full, Q_TILE);
       for (int c = 0; c < NCH; ++c) tma_load_2d(sq + c * AT_CHUNK, &tm_q, &bars.q_full, h * HD + c * 64, b * p.L + qt * AT_BQ);
       for (int j = 0; j < nkb; ++j) {
@@ -1077,6 +1090,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
     // bytes and three plane rows of 256 bytes, each padded by 16 bytes against bank conflicts,
     // then one warp per row, so that global memory sees whole rows.
     if (tr && tid == 128) tr[13] = clock64();
+    if (tid == 64) dbg_stage(p.dbg, KID, 3);
     tc_fence_before();
     asm volatile("bar.sync 1, 256;" ::: "memory");
     constexpr int OB = HD * 2 + 16, OP = HD + 16;  // padded row pitches
@@ -1149,6 +1163,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
     tc_fence_after();
     tmem_dealloc(tmem, T_COLS);
   }
+  if (tid == 0) dbg_stage(p.dbg, KID, 4);
 }
 
 }  // namespace tb
@@ -1214,6 +1229,7 @@ int tybok_qknorm_rope_store(const void* src, int64_t ld, int q_off, int k_off, i
   p.kcache = static_cast<__nv_bfloat16*>(k_cache); p.vcache = static_cast<__nv_bfloat16*>(v_cache);
   p.M = B * L; p.L = L; p.H = H; p.D = D; p.Lcap = Lcap; p.key_off = key_off; p.eps = eps;
   p.pdl = host::pdl_enabled() ? 1 : 0;
+  p.dbg = host::counter_buffer();
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<unsigned>(p.M));
   cfg.blockDim = dim3(static_cast<unsigned>(((H * D / 8) + 31) / 32 * 32));
@@ -1284,6 +1300,7 @@ int tybok_attention(const void* q, const void* k_cache, const void* v_cache, con
   const int n_qt = (L + AT_BQ - 1) / AT_BQ;
   p.dsplit = (nsplit > 1 && 2 * nsplit * H * n_qt * B <= host::sm_count()) ? 2 : 1;
   p.trace = host::trace_buffer();
+  p.dbg = host::counter_buffer();
   const int rows_per_rank = (std::min(L, AT_BQ) + nsplit - 1) / nsplit;
   const bool push = p.dsplit == 2 && n_qt == 1 && nsplit * rows_per_rank <= AT_PUSH_MAX_ROWS;
 

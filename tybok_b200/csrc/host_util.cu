@@ -14,6 +14,7 @@ static std::atomic<int> g_pdl{1};
 static std::atomic<long long> g_launches{0};
 static std::atomic<long long*> g_trace{nullptr};
 static std::atomic<long long> g_epi_limit{0};
+static std::atomic<int*> g_counters{nullptr};
 
 int fail(int code, const char* msg) {
   std::snprintf(g_err, sizeof(g_err), "%s", msg);
@@ -70,6 +71,7 @@ int require_sm100() {
 
 bool pdl_enabled() { return g_pdl.load(std::memory_order_relaxed) != 0; }
 long long* trace_buffer() { return g_trace.load(std::memory_order_relaxed); }
+int* counter_buffer() { return g_counters.load(std::memory_order_relaxed); }
 long long epilogue_wait_limit() { return g_epi_limit.load(std::memory_order_relaxed); }
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
@@ -145,6 +147,7 @@ int tybok_version(void) { return 100; }
 const char* tybok_last_error(void) { return tb::host::last_error(); }
 void tybok_set_pdl(int enabled) { tb::host::g_pdl.store(enabled ? 1 : 0); }
 void tybok_debug_set_trace(void* device_buffer) { tb::host::g_trace.store(static_cast<long long*>(device_buffer)); }
+void tybok_debug_set_counters(void* device_buffer) { tb::host::g_counters.store(static_cast<int*>(device_buffer)); }
 void tybok_debug_set_epilogue_wait_limit(long long sm_clocks) { tb::host::g_epi_limit.store(sm_clocks > 0 ? sm_clocks : 0); }
 long long tybok_launch_count(void) { return tb::host::g_launches.load(); }
 }

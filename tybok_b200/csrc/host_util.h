@@ -23,6 +23,8 @@ bool pdl_enabled();
 void count_launch();
 // Tuning aid: device buffer that kernels fill with per-CTA clock samples (NULL = off).
 long long* trace_buffer();
+// Debugging aid: device int array [16 kernels][8 stages] that kernels bump at their stage boundaries (NULL = off).
+int* counter_buffer();
 // Test aid: SM clocks the GEMM epilogue waits for its accumulator; 0 = the production limit.
 long long epilogue_wait_limit();
 

@@ -36,6 +36,7 @@ struct NormParams {
   __nv_bfloat16* y;      // [M, ldy] or NULL
   long long ldy;
   int pdl;
+  int* dbg;  // debugging aid: stage counters, NULL in production
 };
 
 // VEC = 8-element vectors per lane; FULL = every lane owns exactly VEC vectors (W == 256 * VEC),
@@ -45,6 +46,7 @@ __global__ void __launch_bounds__(128) rmsnorm_kernel(const NormParams p) {
   // Let the next kernel in the stream start its preamble (weight prefetch) right away; it still
   // waits for this grid to finish before it reads what is written here.
   if (p.pdl) pdl_launch_dependents();
+  if (threadIdx.x == 0) dbg_stage(p.dbg, 8, 0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m = blockIdx.x * 4 + warp;
   const int nvec = p.W / 8;  // 8-element vectors per row
@@ -68,6 +70,7 @@ __global__ void __launch_bounds__(128) rmsnorm_kernel(const NormParams p) {
     }
   }
   if (p.pdl) pdl_wait();
+  if (threadIdx.x == 0) dbg_stage(p.dbg, 8, 2);
   if (m < p.M) {
     const __nv_bfloat16* row = p.x + m * p.ldx;
     float v[VEC][8];
@@ -573,6 +576,7 @@ static int launch_norm(const void* x, int64_t ldx, const float* weight, const fl
   p.rows_per_group = rows_per_group > 0 ? rows_per_group : 1; p.M = M; p.W = W; p.eps = eps;
   p.plane_scale = ldexpf(1.0f, out_shift); p.planes = static_cast<uint8_t*>(y_planes);
   p.y = static_cast<__nv_bfloat16*>(y); p.ldy = ldy; p.pdl = host::pdl_enabled() ? 1 : 0;
+  p.dbg = host::counter_buffer();
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3((M + 3) / 4);
   cfg.blockDim = dim3(128);

@@ -30,6 +30,11 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// Debugging aid: bump counter [kernel][stage] once per CTA (see tybok_debug_set_counters).
+__device__ __forceinline__ void dbg_stage(int* counters, int kernel, int stage) {
+  if (counters) atomicAdd(counters + kernel * 8 + stage, 1);
+}
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");

@@ -104,6 +104,7 @@ struct GemmParams {
   int gate_bf16;
   int* status;
   long long* trace;  // tuning aid: [CTA][16] SM-clock samples, NULL in production
+  int* dbg;          // debugging aid: stage counters, NULL in production
   long long epi_wait_limit;  // SM clocks the epilogue waits for the accumulator (kWaitLimitCycles in production)
   RopeEpi rope;      // EPI_QKV_ROPE only
 };
@@ -151,6 +152,8 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
   const int warp = tid >> 5;
   const int lane = tid & 31;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int KID = PAIR ? 2 : (EW == EPI_WARPS ? 0 : 1);
+  if (tid == 0) dbg_stage(p.dbg, KID, 0);
 
   const int ns = p.nstages;
   const int x_bytes = PAIR ? 3 * p.bt * 64 : 3 * p.bt * 128;  // three planes of bt rows x 128 bytes (a pair: half each)
@@ -206,6 +209,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     __syncthreads();
   }
   tc_fence_after();
+  if (tid == 0) dbg_stage(p.dbg, KID, 1);
   const uint32_t tmem = bars.tmem_base;
   // Per-thread epilogue constants (4 consecutive channels), fetched while the main loop runs.
   float s0[4] = {0, 0, 0, 0}, s1[4] = {0, 0, 0, 0}, b0[4] = {0, 0, 0, 0};
@@ -252,6 +256,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
         };
         for (int i = 0; i < pre; ++i) pair_stage(i, true, false);
         if (p.pdl) pdl_wait();
+        dbg_stage(p.dbg, KID, 2);
         for (int i = 0; i < pre; ++i) pair_stage(i, false, true);
         int armed = pre;
         for (int i = pre; i < nkb; ++i) {
@@ -273,6 +278,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
       // The weight tiles of the first stages were requested during set-up; the activation planes
       // are requested once the programmatic dependency has resolved.
       if (p.pdl) pdl_wait();
+      dbg_stage(p.dbg, KID, 2);
       for (int i = 0; i < pre; ++i)
         tma_load_3d(smem + i * stage_bytes + x_off, &tm_x, &bars.full[i], (kb0 + i) * BK, t_tile * p.bt, 0);
       issued = pre;
@@ -503,6 +509,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
   }
 
   if (tr && tid == 64) tr[6] = clock64();
+  if (tid == 0) dbg_stage(p.dbg, KID, 3);
   if (warp >= 2 && !bars.abort) {
     // ---------------------------------------------------------- epilogue, phase B
     // 4 consecutive channels per thread, 8 token rows per pass; with split-K, rank r owns token
@@ -659,6 +666,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     if (PAIR) tmem_dealloc_pair(tmem, p.tmem_cols);
     else tmem_dealloc(tmem, p.tmem_cols);
   }
+  if (tid == 0) dbg_stage(p.dbg, KID, 4);
 }
 
 // ------------------------------------------------------------------------------------ split kernel
@@ -857,6 +865,7 @@ static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, co
   p.gate = gate; p.ldgate = ldgate; p.rows_per_gate = rows_per_gate > 0 ? rows_per_gate : 1; p.gate_bf16 = gate_bf16;
   p.status = status;
   p.trace = host::trace_buffer();
+  p.dbg = host::counter_buffer();
   p.epi_wait_limit = host::epilogue_wait_limit() > 0 ? host::epilogue_wait_limit() : kWaitLimitCycles;
   if (rope) p.rope = *rope;
 
