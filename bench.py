@@ -761,11 +761,11 @@ def run_dit(args, rank: int, world: int) -> None:
 
             cores = _all_host_threads()
             times, ref = _dit_cpu_block(S, inp, bp0, 2)
-            got = den.blocks[0].forward(x_d, den.blocks[0].modulations(tm_d[0]), cos, sin, den._cache(S.seq), 0,
-                                        den._cross[0], den._ctx_valid)
-            if world > 1:
-                parity = None  # block 0's FFN is sharded: its all-reduce needs every rank (checked by the N = 1 run)
-            else:
+            # Only rank 0 is in this branch: with a sharded FFN a block's forward holds an all-reduce
+            # that every rank must enter, so the block-level parity is computed by the N = 1 run only.
+            if world == 1:
+                got = den.blocks[0].forward(x_d, den.blocks[0].modulations(tm_d[0]), cos, sin, den._cache(S.seq), 0,
+                                            den._cross[0], den._ctx_valid)
                 parity = {"rel_l2": round(w8_ref.rel_l2(got.float().cpu()[None], ref.float()), 6), "tolerance_rel_l2": 1e-2,
                           "what": "block 0 at 4146 tokens on the GPU vs oracle/dit_ref.block_forward, same weights and inputs"}
             blk = statistics.median(times)
