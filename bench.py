@@ -789,6 +789,8 @@ def run_dit(args, rank: int, world: int) -> None:
                          "traffic": None, "peak_source": peaks_kind + " (sustained bf16 x ranks; only the FFN is sharded)",
                          "flops_per_pass": flops},
             "cpu_baseline": cpu, "finite": bool(torch.isfinite(out.float()).all()),
+            # the denoised tokens' mean magnitude: equal across N up to the all-reduce's summation order
+            "out_abs_mean": round(float(out.float().abs().mean()), 6),
         }), flush=True)
     if world > 1:
         dist.barrier()
