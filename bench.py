@@ -72,37 +72,62 @@ def _all_host_threads() -> int:
     return n
 
 
-class ClockSampler(threading.Thread):
-    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+class ClockSampler:
+    """SM clock and throttle reasons of one GPU while the timed region runs, sampled by an
+    ``nvidia-smi`` child process (every 50 ms), not through NVML inside this process: an in-process
+    NVML poll running beside NCCL collectives stalled both ranks of the tensor-parallel workload.
+    ``start()`` spawns the child (early, it needs a moment to come up), ``mark()`` opens the window
+    whose samples count, ``stop()`` closes it and returns the summary."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
     def __init__(self, index: int):
-        super().__init__(daemon=True)
-        self.index, self.samples, self.reasons, self.max_mhz, self._halt = index, [], set(), None, threading.Event()
+        self.index, self.rows, self.t0, self.proc, self.note = index, [], None, None, None
 
-    def run(self):
-        try:
-            import pynvml as nv
+    def start(self):
+        import shutil
+        import subprocess
 
-            nv.nvmlInit()
-            h = nv.nvmlDeviceGetHandleByIndex(self.index)
-            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
-            names = {nv.nvmlClocksEventReasonHwSlowdown: "hw_slowdown",
-                     nv.nvmlClocksEventReasonHwThermalSlowdown: "hw_thermal_slowdown",
-                     nv.nvmlClocksEventReasonSwThermalSlowdown: "sw_thermal_slowdown",
-                     nv.nvmlClocksEventReasonSwPowerCap: "sw_power_cap"}
-            while not self._halt.is_set():
-                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
-                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
-                self.reasons |= {n for bit, n in names.items() if mask & bit}
-                time.sleep(0.02)
-        except Exception as e:  # NVML missing: report that instead of clocks
-            self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
+        if os.environ.get("TYBOK_BENCH_NO_CLOCKS") or not shutil.which("nvidia-smi"):
+            self.note = "sampling_disabled" if os.environ.get("TYBOK_BENCH_NO_CLOCKS") else "nvidia-smi_unavailable"
+            return
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        gpu = visible.split(",")[self.index] if visible else str(self.index)
+        self.proc = subprocess.Popen(["nvidia-smi", "-i", gpu, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                      "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+
+        def pump():
+            for line in self.proc.stdout:
+                self.rows.append((time.time(), line))
+
+        threading.Thread(target=pump, daemon=True).start()
+
+    def mark(self):
+        self.t0 = time.time()
 
     def stop(self) -> dict:
-        self._halt.set()
-        self.join(timeout=2)
-        med = statistics.median(self.samples) if self.samples else None
-        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+        t1 = time.time()
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [self.note]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        t0 = self.t0 if self.t0 is not None else 0.0
+        inside = [ln for t, ln in self.rows if t0 <= t <= t1 + 0.06] or [ln for _, ln in self.rows[-3:]]
+        mhz, reasons, mx = [], set(), None
+        for ln in inside:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 6 or not f[0].isdigit():
+                continue
+            mhz.append(int(f[0]))
+            mx = int(f[1]) if f[1].isdigit() else mx
+            reasons |= {n for n, v in zip(self.NAMES, f[2:6]) if v.lower().startswith("active")}
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(mhz)}
 
 
 # ------------------------------------------------------------------------------------ inputs
@@ -438,11 +463,12 @@ def run_ours(args, rank: int, world: int) -> None:
         torch.cuda.synchronize()
 
     graph = engine._graph
+    sampler = ClockSampler(local)
+    sampler.start()
     for _ in range(max(3, args.warmup)):
         graph.replay()
     barrier()
-    sampler = ClockSampler(local)
-    sampler.start()
+    sampler.mark()
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     t_all0, t_all1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_all0.record()
@@ -452,7 +478,6 @@ def run_ours(args, rank: int, world: int) -> None:
         e1.record()
     t_all1.record()
     barrier()
-    clocks = sampler.stop()
     per = sorted(a.elapsed_time(b) for a, b in evs)
     p50 = statistics.median(per)
     total_ms = t_all0.elapsed_time(t_all1)
@@ -474,6 +499,7 @@ def run_ours(args, rank: int, world: int) -> None:
         t0 = time.perf_counter()
         call(frames[i % 4])
         e2e.append((time.perf_counter() - t0) * 1e3)
+    clocks = sampler.stop()  # the window covers the device-timed replays and the end-to-end calls after them
     e2e_p50 = statistics.median(e2e)
     if world > 1:
         t = torch.tensor([e2e_p50], device="cuda", dtype=torch.float64)
@@ -561,11 +587,14 @@ def run_dit_ffn(args, rank: int, world: int) -> None:
     shift, scale, gate = (rn(S.hidden, std=0.5).to(torch.bfloat16) for _ in range(3))
     for i in range(max(3, args.warmup)):
         blocks[i % nblk](x, shift, scale, gate)
+    sampler = ClockSampler(local)
+    sampler.start()
+    for i in range(30):  # keeps the device busy while the sampling child comes up
+        blocks[i % nblk](x, shift, scale, gate)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    sampler = ClockSampler(local)
-    sampler.start()
+    sampler.mark()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(args.steps):
@@ -692,7 +721,21 @@ def run_dit(args, rank: int, world: int) -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     peaks, peaks_kind = _peaks()
-    l0 = ops.launch_count()
+    if os.environ.get("TYBOK_BENCH_DUMP_AFTER"):  # debugging aid: where do this rank's kernels stand after N seconds
+        counters = torch.zeros(128, dtype=torch.int32, device=dev)
+        ops._lib.load().tybok_debug_set_counters(counters.data_ptr())
+        side = torch.cuda.Stream(device=dev)
+
+        def _watch():
+            time.sleep(int(os.environ["TYBOK_BENCH_DUMP_AFTER"]) + 2)
+            with torch.cuda.stream(side):
+                c = counters.cpu().view(16, 8)
+            names = {0: "gemm8", 1: "gemm16", 2: "gemm_pair", 6: "prefill128", 7: "qknorm", 8: "norm"}
+            print(f"rank {rank} launches {ops.launch_count()} status {int(ops.status_word(torch.device(dev)).cpu().item())} " +
+                  " | ".join(f"{n}: in {c[k][0]} setup {c[k][1]} awaited {c[k][2]} main {c[k][3]} out {c[k][4]}"
+                             for k, n in names.items()), file=sys.stderr, flush=True)
+
+        threading.Thread(target=_watch, daemon=True).start()
     den = DiTDenoiser([], S, device=dev, rank=rank, world=world)
     from tybok_b200.dit import DiTBlock
 
@@ -713,6 +756,8 @@ def run_dit(args, rank: int, world: int) -> None:
     def one_pass(x):
         return den.denoise(x, tm_d, cos, sin, inp["deltas"])
 
+    sampler = ClockSampler(local)
+    sampler.start()
     for _ in range(max(1, min(args.warmup, 3))):
         one_pass(x_d)
     torch.cuda.synchronize()
@@ -724,8 +769,7 @@ def run_dit(args, rank: int, world: int) -> None:
     if world > 1:
         dist.barrier()
     steps = max(1, min(args.steps, 10))
-    sampler = ClockSampler(local)
-    sampler.start()
+    sampler.mark()
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
     for e0, e1 in evs:
         e0.record()
@@ -856,6 +900,10 @@ def main() -> None:
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
+    if os.environ.get("TYBOK_BENCH_DUMP_AFTER"):  # debugging aid: python stacks of every thread after N seconds
+        import faulthandler
+
+        faulthandler.dump_traceback_later(int(os.environ["TYBOK_BENCH_DUMP_AFTER"]), exit=False)
     if args.impl == "reference":
         (run_dit_reference if args.workload == "dit" else run_reference)(args, rank)
         return
