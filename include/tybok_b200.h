@@ -121,6 +121,36 @@ int tybok_w8x3_geglu(const void* x_planes, int x_shift, const void* w8_gate, con
                      const float* scale_up, void* h, int64_t ldh, void* h_planes, int out_shift, int M, int I, int K,
                      int token_tile, int splits, int* status_word, void* stream);
 
+/* ---- two-plane activations ---------------------------------------------------------------
+ * A producer that sees a whole activation row (the norm kernels) can hand the GEMM two e4m3 planes
+ * [2][M][K] of x * 2^k(row) plus row_scale[M] = 2^-k(row), k chosen so that the row's largest
+ * magnitude lies in (224, 448]: exact for every element within 2^-10.8 of its row maximum (4e-6 of
+ * the maximum below that), a third less tensor work and operand traffic than three e5m2 planes and
+ * token tiles up to 128.  tybok_norm_planes2 produces the form for the four norms of this library:
+ *   TYBOK_NORM_RMS          a = fp32 weight [W]                       (tybok_rmsnorm, weight form)
+ *   TYBOK_NORM_ADARMS       a = fp32 mod [groups, ldmod], rows_per_group (tybok_rmsnorm, mod form)
+ *   TYBOK_NORM_LN_MODULATE  a = bf16 shift [W], b = bf16 scale [W]    (tybok_layernorm_modulate)
+ *   TYBOK_NORM_LN_AFFINE    a = bf16 weight [W], b = bf16 bias [W]    (tybok_layernorm_affine)
+ * tybok_w8x2_gemm is tybok_w8x3_linear on that form (epilogue TYBOK_EPI_* or
+ * TYBOK_EPI_GEGLU_PACKED: N = 2*I packed gate/up rows in, I columns out, as
+ * tybok_w8x3_geglu_packed); tybok_w8x2_qkv_rope is tybok_w8x3_qkv_rope on it.  Outputs are as in
+ * the three-plane entry points (bf16 and / or three e5m2 planes for the next GEMM). */
+#define TYBOK_NORM_RMS 0
+#define TYBOK_NORM_ADARMS 1
+#define TYBOK_NORM_LN_MODULATE 2
+#define TYBOK_NORM_LN_AFFINE 3
+#define TYBOK_EPI_GEGLU_PACKED 4
+int tybok_norm_planes2(const void* x, int64_t ldx, int mode, const void* a, const void* b, int64_t ldmod, int rows_per_group,
+                       int M, int W, float eps, void* y_planes2, float* row_scale, void* stream);
+int tybok_w8x2_gemm(const void* x_planes2, const float* row_scale, const void* w8, const float* scale, const void* bias,
+                    void* y, int64_t ldy, void* y_planes, int out_shift, int M, int N, int K, int epilogue,
+                    const void* residual, int64_t ldres, const void* gate, int64_t ldgate, int rows_per_gate,
+                    int gate_is_bf16, int token_tile, int splits, int* status_word, void* stream);
+int tybok_w8x2_qkv_rope(const void* x_planes2, const float* row_scale, const void* w8_paired, const float* scale_paired,
+                        const int* pos, const void* cos_table, const void* sin_table, void* q_out, void* k_cache,
+                        void* v_cache, int B, int L, int H, int G, int D, int Lcap, int key_off, int K, int token_tile,
+                        int splits, int* status_word, void* stream);
+
 /* RMS normalisation feeding a W8 GEMM (fp32 statistics, one warp per row).
  *   weight != NULL: plain Gemma norm    y = bf16(x * rsqrt(mean(x^2)+eps) * (1 + weight))
  *   mod    != NULL: AdaRMS norm         y = bf16(x * rsqrt(mean(x^2)+eps) * (1 + scale) + shift),

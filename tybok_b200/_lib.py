@@ -66,6 +66,18 @@ SIGNATURES = {
     "tybok_qknorm_rope_store": (c_int, [c_void_p, c_i64, c_int, c_int, c_int, c_void_p, c_void_p, ctypes.c_float,
                                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                         c_int, c_int, c_void_p]),
+    "tybok_norm_planes2": (c_int, [c_void_p, c_i64, c_int, c_void_p, c_void_p, c_i64, c_int, c_int, c_int, ctypes.c_float,
+                                   c_void_p, c_void_p, c_void_p]),
+    "tybok_w8x2_gemm": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_i64, c_void_p, c_int, c_int, c_int, c_int, c_int,
+         c_void_p, c_i64, c_void_p, c_i64, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    ),
+    "tybok_w8x2_qkv_rope": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    ),
     "tybok_w8a16_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "tybok_w8a16_linear": (
         c_int,

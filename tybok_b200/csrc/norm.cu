@@ -33,6 +33,8 @@ struct NormParams {
   float eps;
   float plane_scale;
   uint8_t* planes;       // [3][M][W] or NULL
+  uint8_t* planes2;      // [2][M][W] e4m3 planes of y * 2^k(row) or NULL, with row_scale[M] = 2^-k(row)
+  float* row_scale;
   __nv_bfloat16* y;      // [M, ldy] or NULL
   long long ldy;
   int pdl;
@@ -116,6 +118,7 @@ __global__ void __launch_bounds__(128) rmsnorm_kernel(const NormParams p) {
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     const float rstd = rsqrtf(ss / static_cast<float>(p.W) + p.eps);
     const long long plane = static_cast<long long>(p.M) * p.W;
+    float amax = 0.f;
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
       const int c = lane + 32 * i;
@@ -176,6 +179,35 @@ __global__ void __launch_bounds__(128) rmsnorm_kernel(const NormParams p) {
           *reinterpret_cast<uint2*>(dst + plane) = w2;
           *reinterpret_cast<uint2*>(dst + 2 * plane) = w3;
         }
+        if (p.planes2) {  // keep the rounded row (over v, which is dead now) until its maximum is known
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            v[i][2 * e] = __bfloat162float(b[e].x);
+            v[i][2 * e + 1] = __bfloat162float(b[e].y);
+            amax = fmaxf(amax, fmaxf(fabsf(v[i][2 * e]), fabsf(v[i][2 * e + 1])));
+          }
+        }
+      }
+    }
+    if (p.planes2) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      float up, down;
+      row_pow2(amax, up, down);
+      if (lane == 0) p.row_scale[m] = down;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        const int c = lane + 32 * i;
+        if (FULL || c < nvec) {
+          const float lo[4] = {v[i][0] * up, v[i][1] * up, v[i][2] * up, v[i][3] * up};
+          const float hi[4] = {v[i][4] * up, v[i][5] * up, v[i][6] * up, v[i][7] * up};
+          uint2 w1, w2;
+          split2_quad(lo, w1.x, w2.x);
+          split2_quad(hi, w1.y, w2.y);
+          uint8_t* dst = p.planes2 + static_cast<long long>(m) * p.W + c * 8;
+          *reinterpret_cast<uint2*>(dst) = w1;
+          *reinterpret_cast<uint2*>(dst + plane) = w2;
+        }
       }
     }
   }
@@ -186,6 +218,7 @@ __global__ void __launch_bounds__(128) rmsnorm_kernel(const NormParams p) {
 // per-thread arithmetic, and the sum of squares crosses the warps through shared memory.
 __global__ void __launch_bounds__(512) rmsnorm_row_kernel(const NormParams p) {
   __shared__ float red[16];
+  __shared__ float red_max[16];
   if (p.pdl) pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int m = blockIdx.x, c = threadIdx.x;
@@ -250,6 +283,37 @@ __global__ void __launch_bounds__(512) rmsnorm_row_kernel(const NormParams p) {
       *reinterpret_cast<uint2*>(dst) = w1;
       *reinterpret_cast<uint2*>(dst + plane) = w2;
       *reinterpret_cast<uint2*>(dst + 2 * plane) = w3;
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {  // the rounded values, for the two-plane form below
+      v[2 * e] = __bfloat162float(b[e].x);
+      v[2 * e + 1] = __bfloat162float(b[e].y);
+    }
+  }
+  if (p.planes2) {  // CTA-uniform: the row maximum crosses the warps like the sum of squares did
+    float amax = 0.f;
+    if (live) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(v[e]));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (lane == 0) red_max[warp] = amax;
+    __syncthreads();
+    amax = 0.f;
+    for (int w = 0; w < nwarps; ++w) amax = fmaxf(amax, red_max[w]);
+    float up, down;
+    row_pow2(amax, up, down);
+    if (threadIdx.x == 0) p.row_scale[m] = down;
+    if (live) {
+      const float lo[4] = {v[0] * up, v[1] * up, v[2] * up, v[3] * up};
+      const float hi[4] = {v[4] * up, v[5] * up, v[6] * up, v[7] * up};
+      uint2 w1, w2;
+      split2_quad(lo, w1.x, w2.x);
+      split2_quad(hi, w1.y, w2.y);
+      uint8_t* dst = p.planes2 + static_cast<long long>(m) * p.W + c * 8;
+      *reinterpret_cast<uint2*>(dst) = w1;
+      *reinterpret_cast<uint2*>(dst + static_cast<long long>(p.M) * p.W) = w2;
     }
   }
 }
@@ -558,8 +622,11 @@ __global__ void __launch_bounds__(512) add_layernorm_f32_kernel(const AddLnF32Pa
 namespace tb {
 static int launch_norm(const void* x, int64_t ldx, const float* weight, const float* mod, int64_t ldmod,
                        int rows_per_group, const void* ln_scale, const void* ln_shift, int M, int W, float eps, void* y,
-                       int64_t ldy, void* y_planes, int out_shift, void* stream, int ln_affine = 0) {
-  if (!x || (!y && !y_planes) || (!weight && !mod && !ln_scale)) return host::fail(TYBOK_ERR_ARG, "rmsnorm: null pointer argument");
+                       int64_t ldy, void* y_planes, int out_shift, void* stream, int ln_affine = 0,
+                       void* y_planes2 = nullptr, float* row_scale = nullptr) {
+  if (!x || (!y && !y_planes && !y_planes2) || (!weight && !mod && !ln_scale)) return host::fail(TYBOK_ERR_ARG, "rmsnorm: null pointer argument");
+  if ((y_planes2 != nullptr) != (row_scale != nullptr) || (reinterpret_cast<uintptr_t>(y_planes2) & 7))
+    return host::fail(TYBOK_ERR_ARG, "norm: two-plane output needs both planes (8-byte aligned) and row_scale");
   if (M <= 0 || W <= 0 || W % 8 != 0 || W > NORM_MAX_VEC * 256)
     return host::fail(TYBOK_ERR_ARG, "rmsnorm: W must be a multiple of 8 and <= 4096");
   if (ldx % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (y && ((reinterpret_cast<uintptr_t>(y) & 15) || ldy % 8 != 0)) ||
@@ -575,6 +642,7 @@ static int launch_norm(const void* x, int64_t ldx, const float* weight, const fl
   p.ln_affine = ln_affine;
   p.rows_per_group = rows_per_group > 0 ? rows_per_group : 1; p.M = M; p.W = W; p.eps = eps;
   p.plane_scale = ldexpf(1.0f, out_shift); p.planes = static_cast<uint8_t*>(y_planes);
+  p.planes2 = static_cast<uint8_t*>(y_planes2); p.row_scale = row_scale;
   p.y = static_cast<__nv_bfloat16*>(y); p.ldy = ldy; p.pdl = host::pdl_enabled() ? 1 : 0;
   p.dbg = host::counter_buffer();
   cudaLaunchConfig_t cfg{};
@@ -701,6 +769,28 @@ int tybok_layernorm_affine(const void* x, int64_t ldx, const void* weight, const
   if ((reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(bias)) & 15)
     return tb::host::fail(TYBOK_ERR_ARG, "layernorm_affine: weight/bias must be 16-byte aligned");
   return tb::launch_norm(x, ldx, nullptr, nullptr, 0, 1, weight, bias, M, W, eps, y, ldy, y_planes, out_shift, stream, 1);
+}
+
+int tybok_norm_planes2(const void* x, int64_t ldx, int mode, const void* a, const void* b, int64_t ldmod, int rows_per_group,
+                       int M, int W, float eps, void* y_planes2, float* row_scale, void* stream) {
+  using namespace tb;
+  switch (mode) {
+    case TYBOK_NORM_RMS:
+      return launch_norm(x, ldx, static_cast<const float*>(a), nullptr, 0, 1, nullptr, nullptr, M, W, eps, nullptr, 0, nullptr,
+                         0, stream, 0, y_planes2, row_scale);
+    case TYBOK_NORM_ADARMS:
+      return launch_norm(x, ldx, nullptr, static_cast<const float*>(a), ldmod, rows_per_group, nullptr, nullptr, M, W, eps,
+                         nullptr, 0, nullptr, 0, stream, 0, y_planes2, row_scale);
+    case TYBOK_NORM_LN_MODULATE:  // a = shift, b = scale (bf16 [W])
+    case TYBOK_NORM_LN_AFFINE:    // a = weight, b = bias (bf16 [W])
+      if (!a || !b || ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15))
+        return host::fail(TYBOK_ERR_ARG, "norm_planes2: the two bf16 vectors must be given, 16-byte aligned");
+      return mode == TYBOK_NORM_LN_MODULATE
+                 ? launch_norm(x, ldx, nullptr, nullptr, 0, 1, b, a, M, W, eps, nullptr, 0, nullptr, 0, stream, 0, y_planes2, row_scale)
+                 : launch_norm(x, ldx, nullptr, nullptr, 0, 1, a, b, M, W, eps, nullptr, 0, nullptr, 0, stream, 1, y_planes2, row_scale);
+    default:
+      return host::fail(TYBOK_ERR_ARG, "norm_planes2: unknown mode");
+  }
 }
 
 }  // extern "C"

@@ -173,6 +173,11 @@ __host__ __device__ constexpr uint32_t idesc_e4m3_e5m2_f32(int m, int n) {
   return (1u << 4) | (0u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
          (static_cast<uint32_t>(m >> 4) << 24);
 }
+// The same with B = e4m3 (format 0): the two-plane activation form.
+__host__ __device__ constexpr uint32_t idesc_e4m3_e4m3_f32(int m, int n) {
+  return (1u << 4) | (0u << 7) | (0u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
+}
 // D[tmem] (+)= A[smem] * B[smem], 8-bit operands, K = 32 per instruction.
 __device__ __forceinline__ void umma_ss_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                            uint32_t accumulate) {

@@ -54,4 +54,45 @@ __device__ __forceinline__ void split3_quad(const float (&x)[4], uint32_t& w1, u
   w3 = a3 | (b3 << 16);
 }
 
+// ------------------------------------------------------------------------------------------
+// Two-term e4m3 decomposition with a per-row power-of-two scale, for producers that see a whole
+// activation row (the norm kernels): x * 2^k = g1 + g2 with g1 = rn(x'), g2 = rn(x' - g1) in e4m3,
+// where k puts the row's largest magnitude into (224, 448].  Two terms of 4 significant bits carry
+// the 8 significant bits of a bf16 value exactly whenever |x'| >= 2^-2, i.e. for every element
+// within 2^-10.8 of the row maximum; smaller elements err by at most 2^-10 in scaled units
+// (4e-6 of the row maximum).  The GEMM multiplies its accumulator column of that token by 2^-k.
+// Two planes instead of three: a third less tensor work and operand traffic, token tiles to 128.
+__device__ __forceinline__ uint32_t e4m3x2_from_f16x2(uint32_t h2) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(r) : "r"(h2));
+  return r;
+}
+__device__ __forceinline__ uint32_t f16x2_from_e4m3x2(uint32_t p) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(static_cast<uint16_t>(p)));
+  return r;
+}
+// Four scaled values -> one 32-bit word per plane (byte i = value i).
+__device__ __forceinline__ void split2_quad(const float (&x)[4], uint32_t& w1, uint32_t& w2) {
+  uint32_t a = f16x2_from_floats(x[0], x[1]), b = f16x2_from_floats(x[2], x[3]);
+  const uint32_t a1 = e4m3x2_from_f16x2(a), b1 = e4m3x2_from_f16x2(b);
+  a = f16x2_sub(a, f16x2_from_e4m3x2(a1));
+  b = f16x2_sub(b, f16x2_from_e4m3x2(b1));
+  w1 = a1 | (b1 << 16);
+  w2 = e4m3x2_from_f16x2(a) | (e4m3x2_from_f16x2(b) << 16);
+}
+// Exponent k with amax * 2^k in (224, 448] (0 for an all-zero row), returned as the two exact
+// powers of two: up = 2^k for the producer, down = 2^-k for the consumer.
+__device__ __forceinline__ void row_pow2(float amax, float& up, float& down) {
+  const uint32_t bits = __float_as_uint(amax);
+  int k = 0;
+  if (amax > 1e-30f && amax < 1e30f) {
+    const int e = static_cast<int>((bits >> 23) & 0xffu) - 127;          // amax = f * 2^e, f in [1, 2)
+    const float f = __uint_as_float((bits & 0x7fffffu) | 0x3f800000u);
+    k = 8 - e - (f > 1.75f ? 1 : 0);                                     // 448 = 1.75 * 2^8
+  }
+  up = __uint_as_float(static_cast<uint32_t>(k + 127) << 23);
+  down = __uint_as_float(static_cast<uint32_t>(127 - k) << 23);
+}
+
 }  // namespace tb

@@ -83,7 +83,9 @@ struct GemmParams {
   int tmem_cols;
   int stage_off;  // byte offset of the epilogue staging tile: 0 (over the idle ring) without split-K,
                   // behind the ring with split-K, because peers write into it while this CTA still streams
-  int merge;     // 1: the three planes are one UMMA of N = 3*bt whose column groups the epilogue adds
+  int np;        // activation planes: 3 (e5m2, fixed exponent shift) or 2 (e4m3, per-token scale row_scale[m])
+  const float* row_scale;  // [M] 2^-k of every token row (two-plane form), else NULL
+  int merge;     // 1: the planes are one UMMA of N = np*bt whose column groups the epilogue adds
   int pair;      // 1: CTA pairs (cluster of 2 along the channel tiles) run one UMMA of M = 256; each CTA
                  // loads its own weight tile and half of the activation planes (tm_w1 = half-tile map)
   int epi;
@@ -156,7 +158,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
   if (tid == 0) dbg_stage(p.dbg, KID, 0);
 
   const int ns = p.nstages;
-  const int x_bytes = PAIR ? 3 * p.bt * 64 : 3 * p.bt * 128;  // three planes of bt rows x 128 bytes (a pair: half each)
+  const int x_bytes = PAIR ? p.np * p.bt * 64 : p.np * p.bt * 128;  // np planes of bt rows x 128 bytes (a pair: half each)
   const int x_off = p.nw * W_TILE_BYTES;              // activation planes follow the weight tile(s)
   const int stage_bytes = x_off + x_bytes;
 
@@ -248,8 +250,8 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
             tma_load_2d_pair(st, &tm_w0, bar, k0, n_tile * BN);
           }
           if (acts) {
-            for (int j = 0; j < 3; ++j) {
-              const int u = static_cast<int>(pair_rank) * 3 + j;  // half-plane index 0..5
+            for (int j = 0; j < p.np; ++j) {
+              const int u = static_cast<int>(pair_rank) * p.np + j;  // half-plane index 0 .. 2 np - 1
               tma_load_3d_pair(st + x_off + j * hrows * 128, &tm_w1, bar, k0, t_tile * p.bt + (u & 1) * hrows, u >> 1);
             }
           }
@@ -312,11 +314,12 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     // with N = 3*bt multiplies a K slice by all of them (one column group per plane) -- 4
     // instead of 12 instructions per weight tile and K block.  Larger tiles issue one UMMA per
     // plane into the same accumulator.
-    const uint32_t idesc = idesc_e4m3_e5m2_f32(PAIR ? 2 * BN : BN, p.merge ? 3 * p.bt : p.bt);
+    const int mma_n = p.merge ? p.np * p.bt : p.bt;
+    const uint32_t idesc = p.np == 2 ? idesc_e4m3_e4m3_f32(PAIR ? 2 * BN : BN, mma_n) : idesc_e4m3_e5m2_f32(PAIR ? 2 * BN : BN, mma_n);
     const int nkb_mma = (PAIR && pair_rank != 0) ? 0 : nkb;  // the odd CTA of a pair issues nothing
     const uint64_t desc_const = smem_desc_sw128(0);
     const uint32_t plane16 = static_cast<uint32_t>(p.bt * 128) >> 4;  // plane pitch in 16-byte units
-    const int acc_cols = p.merge ? 3 * p.bt : p.bt;
+    const int acc_cols = p.merge ? p.np * p.bt : p.bt;
     bool ok = true;
     for (int i = 0; i < nkb_mma; ++i) {
       const int s = i % ns;
@@ -345,8 +348,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
             }
           }
         } else {
-#pragma unroll
-          for (int pl = 0; pl < 3; ++pl) {
+          for (int pl = 0; pl < p.np; ++pl) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const uint64_t a_desc = desc_const | (w16 + j * 2);
@@ -452,13 +454,19 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
       // own shared memory.
       const uint32_t stage_addr = smem_u32(smem + p.stage_off);
       const int ngroups = (nvalid + 15) / 16;
-      const int acc_cols = p.merge ? 3 * p.bt : p.bt;
+      const int acc_cols = p.merge ? p.np * p.bt : p.bt;
       for (int w = 0; w < p.nw; ++w) {
         for (int g = half; g < ngroups; g += EW / 4) {
           uint32_t v[16];
           const uint32_t col = tmem + lane_addr + w * acc_cols + g * 16;
           tmem_ld16(col, v);
-          if (p.merge) {  // add the per-plane column groups in plane order
+          if (p.merge && p.np == 2) {  // add the per-plane column groups in plane order
+            uint32_t v2[16];
+            tmem_ld16(col + p.bt, v2);
+            tc_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 16; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) + __uint_as_float(v2[e]));
+          } else if (p.merge) {
             uint32_t v2[16], v3[16];
             tmem_ld16(col + p.bt, v2);
             tmem_ld16(col + 2 * p.bt, v3);
@@ -543,6 +551,11 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
                                   : *reinterpret_cast<const float4*>(stage + ((sp * p.nw + 1) * rpr + rl) * BN + col0);
           a1.x += g.x; a1.y += g.y; a1.z += g.z; a1.w += g.w;
         }
+      }
+      if (p.row_scale) {  // two-plane form: undo the token's power-of-two pre-scale (exact)
+        const float rs = p.row_scale[m];
+        a0.x *= rs; a0.y *= rs; a0.z *= rs; a0.w *= rs;
+        a1.x *= rs; a1.y *= rs; a1.z *= rs; a1.w *= rs;
       }
       {
       // Every rounding point is the one the reference's bf16 torch modules have: linear output,
@@ -733,7 +746,7 @@ static int max_active_clusters(int splits) {
   return cached[splits];
 }
 
-static bool make_plan(int M, int N, int K, int nw, int force_bt, int force_splits, Plan& pl) {
+static bool make_plan(int M, int N, int K, int nw, int force_bt, int force_splits, Plan& pl, int np = 3) {
   const int max_bt = nw == 2 ? 128 : 256;
   int bt;
   if (force_bt > 0) {
@@ -748,8 +761,12 @@ static bool make_plan(int M, int N, int K, int nw, int force_bt, int force_split
     const int n_tiles = (N + BN - 1) / BN;
     long long best_cost = 0;
     bt = 0;
-    for (int cap : {80, 64}) {
-      if (cap == 64 && M <= 80) break;  // one tile already: do not stream the weights twice
+    // Two planes: np * bt <= 256 allows token tiles up to 128 (caps 128 / 96 / 64).
+    const int caps3[3] = {80, 64, 0}, caps2[3] = {128, 96, 64};
+    for (int ci = 0; ci < 3; ++ci) {
+      const int cap = np == 2 ? caps2[ci] : caps3[ci];
+      if (cap == 0) break;
+      if (ci > 0 && M <= (np == 2 ? 128 : 80)) break;  // one tile already: do not stream the weights twice
       const int tiles = (M + cap - 1) / cap;
       const int cand = round_up((M + tiles - 1) / tiles, 16);
       const long long waves = (static_cast<long long>((M + cand - 1) / cand) * n_tiles + sms - 1) / sms;
@@ -777,9 +794,9 @@ static bool make_plan(int M, int N, int K, int nw, int force_bt, int force_split
   // CTA then loads half of the activation planes, a third less shared-memory fill per MMA and a
   // third stage in the same shared memory (4146 x 3072 x 14336: 503 -> 409 us; 544 x 32768 x 2048:
   // unchanged; single-wave launches lose a microsecond to the pair's set-up, so they stay single).
-  pl.pair = (splits == 1 && nw == 1 && 3 * bt <= 256 && pl.n_tiles % 2 == 0 &&
+  pl.pair = (splits == 1 && nw == 1 && np * bt <= 256 && pl.n_tiles % 2 == 0 &&
              pl.t_tiles * pl.n_tiles >= 2 * host::sm_count()) ? 1 : 0;
-  const int stage_bytes = pl.pair ? W_TILE_BYTES + 3 * bt * 64 : nw * W_TILE_BYTES + 3 * bt * 128;
+  const int stage_bytes = pl.pair ? W_TILE_BYTES + np * bt * 64 : nw * W_TILE_BYTES + np * bt * 128;
   for (;; --splits) {  // fewer splits if the split-K staging tile does not fit beside the ring
     pl.kb_per_split = (pl.kb_total + splits - 1) / splits;
     pl.splits = (pl.kb_total + pl.kb_per_split - 1) / pl.kb_per_split;  // no empty split
@@ -791,7 +808,7 @@ static bool make_plan(int M, int N, int K, int nw, int force_bt, int force_split
     pl.nstages = std::min(pl.nstages, std::max(2, pl.kb_per_split));
     // Several waves of full-K tiles: a shallower ring lets two CTAs share an SM, so one tile's
     // epilogue runs under the other's main loop (measured on 544 x 32768 x 2048: 117 vs 156 us).
-    if (pl.splits == 1 && pl.t_tiles * pl.n_tiles >= 2 * host::sm_count() && nw * 3 * bt <= 256) {
+    if (pl.splits == 1 && pl.t_tiles * pl.n_tiles >= 2 * host::sm_count() && nw * np * bt <= 256) {
       const int shared = (CORESIDENT_SMEM - 1024) / stage_bytes;
       if (shared >= 2) pl.nstages = std::min(pl.nstages, shared);
     }
@@ -801,9 +818,9 @@ static bool make_plan(int M, int N, int K, int nw, int force_bt, int force_split
     if (pl.nstages >= 2 && pl.nstages <= MAX_STAGES && pl.smem_bytes <= DYN_SMEM_MAX) break;
     if (splits == 1) return false;
   }
-  pl.merge = (3 * bt <= 256 && nw * 3 * bt <= 512) ? 1 : 0;
+  pl.merge = (np * bt <= 256 && nw * np * bt <= 512) ? 1 : 0;
   pl.tmem_cols = 32;
-  while (pl.tmem_cols < nw * bt * (pl.merge ? 3 : 1)) pl.tmem_cols *= 2;
+  while (pl.tmem_cols < nw * bt * (pl.merge ? np : 1)) pl.tmem_cols *= 2;
   return true;
 }
 
@@ -811,7 +828,9 @@ static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, co
                        const void* bias, void* y, void* y_planes, int M, int N, int K, long long ldy, int epi,
                        const void* res, long long ldres, const void* gate, long long ldgate, int rows_per_gate,
                        int gate_bf16, int x_shift, int out_shift, int force_bt, int force_splits, int* status,
-                       cudaStream_t stream, const RopeEpi* rope = nullptr, bool check_only = false) {
+                       cudaStream_t stream, const RopeEpi* rope = nullptr, bool check_only = false,
+                       const float* row_scale = nullptr) {
+  const int np = row_scale ? 2 : 3;  // two e4m3 planes with a per-token scale, or three e5m2 planes
   const int nw = w1 ? 2 : 1;
   if (!planes || !w0 || !s0 || (!y && !y_planes && !rope)) return host::fail(TYBOK_ERR_ARG, "w8 gemm: null pointer argument");
   if (M <= 0 || N <= 0 || K <= 0) return host::fail(TYBOK_ERR_ARG, "w8 gemm: M, N, K must be positive");
@@ -834,7 +853,7 @@ static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, co
   if (int rc = host::require_sm100()) return rc;
 
   Plan pl;
-  if (!make_plan(M, N, K, nw, force_bt, force_splits, pl))
+  if (!make_plan(M, N, K, nw, force_bt, force_splits, pl, np))
     return host::fail(TYBOK_ERR_ARG, "w8 gemm: unsupported token tile (multiple of 16, <= 256, <= 128 when gated)");
   if (force_splits > MAX_SPLITS) return host::fail(TYBOK_ERR_ARG, "w8 gemm: at most 8 K splits (cluster size)");
   if ((pl.pair ? pl.t_tiles : pl.n_tiles) > 65535) return host::fail(TYBOK_ERR_ARG, "w8 gemm: grid too large");
@@ -846,18 +865,18 @@ static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, co
   if (nw == 2)
     if (int rc = host::tensor_map_2d(&tm_w1, w1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, N, K, BK, BN)) return rc;
   if (pl.pair)  // half-plane boxes of the activation planes: bt/2 token rows of one plane
-    if (int rc = host::tensor_map_3d(&tm_w1, planes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, M, 3, K,
+    if (int rc = host::tensor_map_3d(&tm_w1, planes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, M, np, K,
                                      static_cast<uint64_t>(M) * K, BK, pl.bt / 2, 1))
       return rc;
-  if (int rc = host::tensor_map_3d(&tm_x, planes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, M, 3, K,
-                                   static_cast<uint64_t>(M) * K, BK, pl.bt, 3))
+  if (int rc = host::tensor_map_3d(&tm_x, planes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, M, np, K,
+                                   static_cast<uint64_t>(M) * K, BK, pl.bt, np))
     return rc;
 
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.n_out = n_out;
   p.bt = pl.bt; p.nw = nw; p.splits = pl.splits; p.kb_total = pl.kb_total; p.kb_per_split = pl.kb_per_split;
   p.nstages = pl.nstages; p.tmem_cols = pl.tmem_cols; p.merge = pl.merge; p.pair = pl.pair; p.stage_off = pl.stage_off; p.epi = epi; p.pdl = host::pdl_enabled() ? 1 : 0;
-  p.out_scale = ldexpf(1.0f, -x_shift);
+  p.out_scale = row_scale ? 1.0f : ldexpf(1.0f, -x_shift);
   p.plane_scale = ldexpf(1.0f, out_shift);
   p.scale0 = s0; p.scale1 = s1; p.bias0 = static_cast<const __nv_bfloat16*>(bias);
   p.y = static_cast<__nv_bfloat16*>(y); p.ldy = ldy; p.y_planes = static_cast<uint8_t*>(y_planes);
@@ -1012,6 +1031,42 @@ int tybok_w8x3_qkv_rope(const void* x_planes, int x_shift, const void* w8_paired
   return tb::launch_gemm(static_cast<const uint8_t*>(x_planes), w8_paired, nullptr, scale_paired, nullptr, nullptr,
                          nullptr, nullptr, B * L, (H + 2 * G) * D, K, 0, tb::EPI_QKV_ROPE, nullptr, 0, nullptr, 0, 1, 0,
                          x_shift, 0, token_tile, splits, status_word, static_cast<cudaStream_t>(stream), &r);
+}
+
+int tybok_w8x2_gemm(const void* x_planes2, const float* row_scale, const void* w8, const float* scale, const void* bias,
+                    void* y, int64_t ldy, void* y_planes, int out_shift, int M, int N, int K, int epilogue,
+                    const void* residual, int64_t ldres, const void* gate, int64_t ldgate, int rows_per_gate,
+                    int gate_is_bf16, int token_tile, int splits, int* status_word, void* stream) {
+  if (!row_scale) return tb::host::fail(TYBOK_ERR_ARG, "w8x2_gemm: null row_scale");
+  if (epilogue != TYBOK_EPI_NONE && epilogue != TYBOK_EPI_GELU && epilogue != TYBOK_EPI_RESIDUAL &&
+      epilogue != TYBOK_EPI_GEGLU_PACKED)
+    return tb::host::fail(TYBOK_ERR_ARG, "w8x2_gemm: unknown epilogue");
+  // the packed gated form takes N = 2*I weight rows and writes I output columns
+  return tb::launch_gemm(static_cast<const uint8_t*>(x_planes2), w8, nullptr, scale, nullptr, bias, y, y_planes, M, N, K,
+                         ldy, epilogue == TYBOK_EPI_GEGLU_PACKED ? tb::EPI_GEGLU_PACKED : epilogue, residual, ldres, gate,
+                         ldgate, rows_per_gate, gate_is_bf16, 0, out_shift, token_tile, splits, status_word,
+                         static_cast<cudaStream_t>(stream), nullptr, false, row_scale);
+}
+
+int tybok_w8x2_qkv_rope(const void* x_planes2, const float* row_scale, const void* w8_paired, const float* scale_paired,
+                        const int* pos, const void* cos_table, const void* sin_table, void* q_out, void* k_cache,
+                        void* v_cache, int B, int L, int H, int G, int D, int Lcap, int key_off, int K, int token_tile,
+                        int splits, int* status_word, void* stream) {
+  if (!row_scale || !pos || !cos_table || !sin_table || !q_out || !k_cache || !v_cache)
+    return tb::host::fail(TYBOK_ERR_ARG, "w8x2_qkv_rope: null pointer argument");
+  if (B <= 0 || L <= 0 || H <= 0 || G <= 0 || D <= 0 || D % 128 != 0 || key_off < 0 || key_off + L > Lcap)
+    return tb::host::fail(TYBOK_ERR_ARG, "w8x2_qkv_rope: needs head_dim % 128 == 0 and key_off + L <= Lcap");
+  if ((reinterpret_cast<uintptr_t>(cos_table) | reinterpret_cast<uintptr_t>(sin_table) |
+       reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 7)
+    return tb::host::fail(TYBOK_ERR_ARG, "w8x2_qkv_rope: tables, q and caches must be 8-byte aligned");
+  tb::RopeEpi r{};
+  r.pos = pos; r.cos = static_cast<const __nv_bfloat16*>(cos_table); r.sin = static_cast<const __nv_bfloat16*>(sin_table);
+  r.q = static_cast<__nv_bfloat16*>(q_out); r.kcache = static_cast<__nv_bfloat16*>(k_cache);
+  r.vcache = static_cast<__nv_bfloat16*>(v_cache);
+  r.L = L; r.H = H; r.G = G; r.D = D; r.Lcap = Lcap; r.key_off = key_off;
+  return tb::launch_gemm(static_cast<const uint8_t*>(x_planes2), w8_paired, nullptr, scale_paired, nullptr, nullptr,
+                         nullptr, nullptr, B * L, (H + 2 * G) * D, K, 0, tb::EPI_QKV_ROPE, nullptr, 0, nullptr, 0, 1, 0, 0,
+                         0, token_tile, splits, status_word, static_cast<cudaStream_t>(stream), &r, false, row_scale);
 }
 
 int tybok_w8a16_linear(const void* x, const void* w8, const float* scale, const void* bias, void* y, int M, int N,

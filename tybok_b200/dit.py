@@ -29,6 +29,23 @@ from .weights import quantize_w8
 SHIFT_IN = 4
 SHIFT_HIDDEN = 4
 SHIFT_ATTN = 6  # attention outputs are convex combinations of value rows
+#: From this many token rows the GEMMs fed by a norm take two e4m3 planes with a per-row scale.
+TWO_PLANE_MIN_TOKENS = 128
+
+
+def _ln_planes(x, shift, scale, eps):
+    """modulate(LayerNorm(x)) as GEMM input: ``(planes, row_scale)`` (two-plane form) or
+    ``(planes, None)`` (three planes at SHIFT_IN)."""
+    if x.shape[0] >= TWO_PLANE_MIN_TOKENS:
+        return ops.norm_planes2(x, ops.NORM_LN_MODULATE, shift, scale, eps=eps)
+    return ops.layernorm_modulate(x, shift, scale, eps=eps, out_shift=SHIFT_IN)[1], None
+
+
+def _gemm(xp, rs, w8, sc, bias=None, **kw):
+    """The W8 linear on either activation form."""
+    if rs is not None:
+        return ops.w8x2_gemm(xp, rs, w8, sc, bias, **kw)
+    return ops.w8x3_linear(xp, SHIFT_IN, w8, sc, bias, **kw)
 
 
 def _as_w8(w: torch.Tensor, scale: torch.Tensor | None):
@@ -78,9 +95,8 @@ class DiTFFN:
 
     def partial(self, x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
         """This rank's un-biased contribution ``[M, H]`` bf16 to ``down(gelu(up(...)))``."""
-        _, xp = ops.layernorm_modulate(x, shift, scale, eps=self.eps, out_shift=SHIFT_IN)
-        _, hp = ops.w8x3_linear(xp, SHIFT_IN, *self.up, epilogue=ops.EPI_GELU, out_bf16=False, out_planes=True,
-                                out_shift=SHIFT_HIDDEN)
+        xp, rs = _ln_planes(x, shift, scale, self.eps)
+        _, hp = _gemm(xp, rs, *self.up, epilogue=ops.EPI_GELU, out_bf16=False, out_planes=True, out_shift=SHIFT_HIDDEN)
         y, _ = ops.w8x3_linear(hp, SHIFT_HIDDEN, self.down[0], self.down[1])
         return y
 
@@ -88,9 +104,8 @@ class DiTFFN:
         """``x [M, H]`` bf16; ``shift``/``scale``/``gate`` bf16 ``[H]``."""
         m = x.shape[0]
         if self.world == 1:
-            _, xp = ops.layernorm_modulate(x, shift, scale, eps=self.eps, out_shift=SHIFT_IN)
-            _, hp = ops.w8x3_linear(xp, SHIFT_IN, *self.up, epilogue=ops.EPI_GELU, out_bf16=False, out_planes=True,
-                                    out_shift=SHIFT_HIDDEN)
+            xp, rs = _ln_planes(x, shift, scale, self.eps)
+            _, hp = _gemm(xp, rs, *self.up, epilogue=ops.EPI_GELU, out_bf16=False, out_planes=True, out_shift=SHIFT_HIDDEN)
             y, _ = ops.w8x3_linear(hp, SHIFT_HIDDEN, *self.down, epilogue=ops.EPI_RESIDUAL, residual=x,
                                    gate=gate.reshape(1, -1), rows_per_gate=m)
             return y
@@ -177,8 +192,8 @@ class DiTBlock:
         ``ctx_valid`` uint8 ``[1, C]`` (``None`` skips the cross-attention, dit_block.py:385-390)."""
         s = x.shape[0]
         a, hd = self.attn_dim, self.hd
-        _, hp = ops.layernorm_modulate(x, mods[0], mods[1], eps=self.eps, out_shift=SHIFT_IN)
-        qkv, _ = ops.w8x3_linear(hp, SHIFT_IN, *self.qkv)
+        hp, rs = _ln_planes(x, mods[0], mods[1], self.eps)
+        qkv, _ = _gemm(hp, rs, *self.qkv)
         q = ops.qknorm_rope_store(qkv, q_off=0, k_off=a, v_off=2 * a, norm_q=self.norm_q, norm_k=self.norm_k, eps=self.eps,
                                   cos=cos, sin=sin, k_cache=self_cache[0], v_cache=self_cache[1], heads=self.heads,
                                   head_dim=hd, key_off=key_off)
@@ -187,8 +202,11 @@ class DiTBlock:
         x, _ = ops.w8x3_linear(ap, SHIFT_ATTN, *self.o, epilogue=ops.EPI_RESIDUAL, residual=x, gate=mods[2:3],
                                rows_per_gate=s)
         if cross_cache is not None:
-            _, cp = ops.layernorm_affine(x, *self.norm3, eps=self.eps, out_shift=SHIFT_IN)
-            qc, _ = ops.w8x3_linear(cp, SHIFT_IN, *self.cross_q)
+            if s >= TWO_PLANE_MIN_TOKENS:
+                cp, rs = ops.norm_planes2(x, ops.NORM_LN_AFFINE, *self.norm3, eps=self.eps)
+            else:
+                cp, rs = ops.layernorm_affine(x, *self.norm3, eps=self.eps, out_shift=SHIFT_IN)[1], None
+            qc, _ = _gemm(cp, rs, *self.cross_q)
             qc = ops.qknorm_rope_store(qc, q_off=0, norm_q=self.cross_norm_q, eps=self.eps, heads=self.heads, head_dim=hd)
             lc = ctx_valid.shape[1] if ctx_valid is not None else cross_cache[0].shape[2]
             _, cap = ops.attention(qc, cross_cache[0], cross_cache[1], ctx_valid, tokens=s, keys=lc, scale=hd**-0.5,

@@ -60,6 +60,16 @@ _L.define("qknorm_rope_store(Tensor src, int q_off, int k_off, int v_off, Tensor
           "Tensor? cos, Tensor? sin, Tensor(a!)? k_cache, Tensor(b!)? v_cache, int batch, int heads, int head_dim, "
           "int key_off) -> Tensor")
 
+_L.define("norm_planes2(Tensor x, int mode, Tensor a, Tensor? b, int rows_per_group, float eps) -> (Tensor, Tensor)")
+_L.define("w8x2_gemm(Tensor planes2, Tensor row_scale, Tensor w8, Tensor scale, Tensor? bias, int epilogue, "
+          "Tensor? residual, Tensor? gate, int rows_per_gate, bool out_bf16, bool out_planes, int out_shift, "
+          "int token_tile, int splits) -> (Tensor, Tensor)")
+_L.define("w8x2_qkv_rope(Tensor planes2, Tensor row_scale, Tensor w8_paired, Tensor scale_paired, Tensor pos, Tensor cos, "
+          "Tensor sin, Tensor(a!) k_cache, Tensor(b!) v_cache, int heads, int key_off, int token_tile, int splits) -> Tensor")
+
+NORM_RMS, NORM_ADARMS, NORM_LN_MODULATE, NORM_LN_AFFINE = 0, 1, 2, 3
+EPI_GEGLU_PACKED = 4
+
 _status: dict[int, torch.Tensor] = {}
 
 
@@ -575,6 +585,126 @@ def qknorm_rope_store(src, *, q_off=-1, k_off=-1, v_off=-1, norm_q=None, norm_k=
     finished q ``[B*L, H*D]`` (empty when ``q_off < 0``); see ``tybok_qknorm_rope_store``."""
     return torch.ops.tybok_b200.qknorm_rope_store(src, q_off, k_off, v_off, norm_q, norm_k, eps, cos, sin, k_cache,
                                                   v_cache, batch, heads, head_dim, key_off)
+
+
+def _norm_planes2_cuda(x, mode, a, b, rows_per_group, eps):
+    lib = _lib.load()
+    if x.dtype != torch.bfloat16:
+        raise TypeError(f"norm_planes2: x must be bf16, got {x.dtype}")
+    x2 = _rows(x)
+    m, w = x2.shape
+    ldmod = 0
+    if mode in (NORM_RMS, NORM_ADARMS):
+        if a.dtype != torch.float32 or a.stride(-1) != 1:
+            raise TypeError("norm_planes2: the RMS weight / AdaRMS modulation must be fp32 with unit inner stride")
+        if mode == NORM_RMS and (a.numel() != w or not a.is_contiguous()):
+            raise TypeError("norm_planes2: weight must be contiguous fp32 [W]")
+        if mode == NORM_ADARMS:
+            if a.shape[-1] < 2 * w:
+                raise TypeError("norm_planes2: mod must be fp32 [groups, >= 2*W]")
+            ldmod = a.stride(-2) if a.dim() > 1 else a.shape[-1]
+    else:
+        for t in (a, b):
+            if t is None or t.dtype != torch.bfloat16 or t.numel() != w or not t.is_contiguous():
+                raise TypeError("norm_planes2: the LayerNorm forms take two contiguous bf16 [W] vectors")
+    planes = torch.empty((2, m, w), dtype=torch.uint8, device=x.device)
+    row_scale = torch.empty(m, dtype=torch.float32, device=x.device)
+    rc = lib.tybok_norm_planes2(x2.data_ptr(), x2.stride(0), int(mode), a.data_ptr(), _ptr(b), ldmod, int(rows_per_group),
+                                m, w, float(eps), planes.data_ptr(), row_scale.data_ptr(), _stream(x))
+    _lib.check(rc, "tybok_norm_planes2")
+    return planes, row_scale
+
+
+def _check_planes2(planes, row_scale, k, what):
+    if planes.dtype != torch.uint8 or planes.dim() != 3 or planes.shape[0] != 2 or not planes.is_contiguous():
+        raise TypeError(f"{what}: planes must be a contiguous uint8 [2, M, K] tensor")
+    if planes.shape[2] != k:
+        raise ValueError(f"{what}: planes have K={planes.shape[2]}, weight has K={k}")
+    if row_scale.dtype != torch.float32 or row_scale.numel() != planes.shape[1] or not row_scale.is_contiguous():
+        raise TypeError(f"{what}: row_scale must be contiguous fp32 [M]")
+
+
+def _w8x2_gemm_cuda(planes, row_scale, w8, scale, bias, epilogue, residual, gate, rows_per_gate, out_bf16, out_planes,
+                    out_shift, token_tile, splits):
+    lib = _lib.load()
+    _check_w8(w8, "w8x2_gemm")
+    n, k = w8.shape
+    _check_planes2(planes, row_scale, k, "w8x2_gemm")
+    m = planes.shape[1]
+    n_out = n // 2 if epilogue == EPI_GEGLU_PACKED else n
+    y, yp = _outputs(m, n_out, planes.device, out_bf16, out_planes)
+    res2 = None
+    if residual is not None:
+        res2 = _rows(residual)
+        if res2.shape != (m, n) or res2.dtype != torch.bfloat16:
+            raise ValueError("w8x2_gemm: residual must be bf16 [M, N]")
+    gate_bf16 = ldgate = 0
+    if gate is not None:
+        if gate.dtype not in (torch.float32, torch.bfloat16) or gate.stride(-1) != 1 or gate.shape[-1] != n:
+            raise TypeError("w8x2_gemm: gate must be fp32 or bf16 [groups, N] with unit inner stride")
+        gate_bf16 = int(gate.dtype == torch.bfloat16)
+        ldgate = gate.stride(-2) if gate.dim() > 1 else n
+    rc = lib.tybok_w8x2_gemm(planes.data_ptr(), row_scale.data_ptr(), w8.data_ptr(), scale.data_ptr(), _ptr(bias),
+                             y.data_ptr() if out_bf16 else None, n_out, yp.data_ptr() if out_planes else None,
+                             int(out_shift), m, n, k, int(epilogue), _ptr(res2), res2.stride(0) if res2 is not None else 0,
+                             _ptr(gate), ldgate, int(rows_per_gate), gate_bf16, int(token_tile), int(splits),
+                             status_word(planes.device).data_ptr(), _stream(planes))
+    _lib.check(rc, "tybok_w8x2_gemm")
+    return y, yp
+
+
+def _w8x2_qkv_rope_cuda(planes, row_scale, w8_paired, scale_paired, pos, cos, sin, k_cache, v_cache, heads, key_off,
+                        token_tile, splits):
+    lib = _lib.load()
+    _check_w8(w8_paired, "w8x2_qkv_rope")
+    b, g, lcap, d = k_cache.shape
+    m, k = planes.shape[1], planes.shape[2]
+    _check_planes2(planes, row_scale, w8_paired.shape[1], "w8x2_qkv_rope")
+    if w8_paired.shape != ((heads + 2 * g) * d, k) or scale_paired.numel() != w8_paired.shape[0] or d % 128 != 0:
+        raise ValueError("w8x2_qkv_rope: weight must be [(H+2G)*D, K] with head_dim % 128 == 0")
+    if pos.dtype != torch.int32 or pos.numel() != m or not pos.is_contiguous() or m % b != 0:
+        raise TypeError("w8x2_qkv_rope: pos must be contiguous int32 [B*L]")
+    for t in (k_cache, v_cache, cos, sin):
+        if t.dtype != torch.bfloat16 or not t.is_contiguous():
+            raise TypeError("w8x2_qkv_rope: caches and cos/sin tables must be contiguous bf16")
+    if v_cache.shape != k_cache.shape or cos.shape[-1] != d or sin.shape != cos.shape:
+        raise ValueError("w8x2_qkv_rope: cache / table shapes disagree")
+    q = torch.empty((m, heads * d), dtype=torch.bfloat16, device=planes.device)
+    rc = lib.tybok_w8x2_qkv_rope(planes.data_ptr(), row_scale.data_ptr(), w8_paired.data_ptr(), scale_paired.data_ptr(),
+                                 pos.data_ptr(), cos.data_ptr(), sin.data_ptr(), q.data_ptr(), k_cache.data_ptr(),
+                                 v_cache.data_ptr(), b, m // b, heads, g, d, lcap, int(key_off), k, int(token_tile),
+                                 int(splits), status_word(planes.device).data_ptr(), _stream(planes))
+    _lib.check(rc, "tybok_w8x2_qkv_rope")
+    return q
+
+
+_L.impl("norm_planes2", _norm_planes2_cuda, "CUDA")
+_L.impl("w8x2_gemm", _w8x2_gemm_cuda, "CUDA")
+_L.impl("w8x2_qkv_rope", _w8x2_qkv_rope_cuda, "CUDA")
+
+
+def norm_planes2(x, mode, a, b=None, *, rows_per_group=1, eps=1e-6):
+    """A norm of this package with its output as two e4m3 planes of ``y * 2**k(row)`` plus
+    ``row_scale = 2**-k(row)``: ``(planes [2, M, W] uint8, row_scale [M] fp32)``; ``mode`` is one of
+    ``NORM_RMS`` (``a`` = fp32 weight), ``NORM_ADARMS`` (``a`` = fp32 modulation rows),
+    ``NORM_LN_MODULATE`` (``a`` = shift, ``b`` = scale, bf16), ``NORM_LN_AFFINE`` (``a`` = weight,
+    ``b`` = bias, bf16); see ``tybok_norm_planes2``."""
+    return torch.ops.tybok_b200.norm_planes2(x, mode, a, b, rows_per_group, eps)
+
+
+def w8x2_gemm(planes2, row_scale, w8, scale, bias=None, *, epilogue=EPI_NONE, residual=None, gate=None, rows_per_gate=1,
+              out_bf16=True, out_planes=False, out_shift=DEFAULT_SHIFT, token_tile=0, splits=0):
+    """W8 linear (or, with ``EPI_GEGLU_PACKED``, the gated FFN front half on a ``pack_gate_up`` weight)
+    on two-plane activations; returns ``(y_bf16, y_planes)`` like ``w8x3_linear``; see ``tybok_w8x2_gemm``."""
+    return torch.ops.tybok_b200.w8x2_gemm(planes2, row_scale, w8, scale, bias, epilogue, residual, gate, rows_per_gate,
+                                          out_bf16, out_planes, out_shift, token_tile, splits)
+
+
+def w8x2_qkv_rope(planes2, row_scale, w8_paired, scale_paired, pos, cos, sin, k_cache, v_cache, *, heads, key_off,
+                  token_tile=0, splits=0):
+    """``w8x3_qkv_rope`` on two-plane activations; see ``tybok_w8x2_qkv_rope``."""
+    return torch.ops.tybok_b200.w8x2_qkv_rope(planes2, row_scale, w8_paired, scale_paired, pos, cos, sin, k_cache,
+                                              v_cache, heads, key_off, token_tile, splits)
 
 
 def launch_count() -> int:

@@ -32,6 +32,10 @@ from .weights import EXPERT, PROJECTOR, VISION, VLM, quantize_w8
 SHIFT_NORMED = 4  # RMS-normalised activations, O(1)
 SHIFT_ATTN = 6  # attention outputs (convex combinations of V rows)
 SHIFT_FFN = 4  # gelu(gate) * up
+#: From this many token rows a GEMM fed by a norm takes its activations as two e4m3 planes with a
+#: per-row power-of-two scale (a third less tensor work, token tiles to 128); below it the GEMMs are
+#: bound by launch latency and keep the three-plane form.
+TWO_PLANE_MIN_TOKENS = 128
 
 
 class _Layer:
@@ -290,23 +294,37 @@ class PI05Model:
         this layer's ``(K, V)`` cache; the layer appends its keys at ``key_off``."""
         w = spec.width
         m = x.shape[0]
-        if mods is None:
-            _, xp = ops.rmsnorm(x, weight=lay.norm_in, out_shift=SHIFT_NORMED)
-            gate_in = gate_post = None
-        else:
-            _, xp = ops.rmsnorm(x, mod=mods[0], rows_per_group=m, out_shift=SHIFT_NORMED)
+        two = m >= TWO_PLANE_MIN_TOKENS and lay.gate_up is not None
+        gate_in = gate_post = None
+        if mods is not None:
             gate_in, gate_post = mods[0][:, 2 * w :], mods[1][:, 2 * w :]
-        q = ops.w8x3_qkv_rope(xp, SHIFT_NORMED, *lay.qkv_paired, pos, self.cos, self.sin, cache[0], cache[1],
-                              heads=spec.num_heads, key_off=key_off)
+
+        def norm(which):
+            """This layer's input (0) or post-attention (1) norm -> the activation form the next GEMM takes."""
+            if two:
+                if mods is None:
+                    return ops.norm_planes2(x, ops.NORM_RMS, lay.norm_in if which == 0 else lay.norm_post)
+                return ops.norm_planes2(x, ops.NORM_ADARMS, mods[which], rows_per_group=m)
+            if mods is None:
+                return ops.rmsnorm(x, weight=lay.norm_in if which == 0 else lay.norm_post, out_shift=SHIFT_NORMED)[1], None
+            return ops.rmsnorm(x, mod=mods[which], rows_per_group=m, out_shift=SHIFT_NORMED)[1], None
+
+        xp, rs = norm(0)
+        if two:
+            q = ops.w8x2_qkv_rope(xp, rs, *lay.qkv_paired, pos, self.cos, self.sin, cache[0], cache[1],
+                                  heads=spec.num_heads, key_off=key_off)
+        else:
+            q = ops.w8x3_qkv_rope(xp, SHIFT_NORMED, *lay.qkv_paired, pos, self.cos, self.sin, cache[0], cache[1],
+                                  heads=spec.num_heads, key_off=key_off)
         _, ap = ops.attention(q, cache[0], cache[1], key_valid, tokens=l, keys=key_off + l,
                               scale=spec.head_dim**-0.5, out_bf16=False, out_planes=True, out_shift=SHIFT_ATTN)
         x, _ = ops.w8x3_linear(ap, SHIFT_ATTN, *lay.o, epilogue=ops.EPI_RESIDUAL, residual=x, gate=gate_in,
                                rows_per_gate=m)
-        if mods is None:
-            _, xp = ops.rmsnorm(x, weight=lay.norm_post, out_shift=SHIFT_NORMED)
-        else:
-            _, xp = ops.rmsnorm(x, mod=mods[1], rows_per_group=m, out_shift=SHIFT_NORMED)
-        if lay.gate_up is not None:
+        xp, rs = norm(1)
+        if two:
+            _, hp = ops.w8x2_gemm(xp, rs, *lay.gate_up, epilogue=ops.EPI_GEGLU_PACKED, out_bf16=False, out_planes=True,
+                                  out_shift=SHIFT_FFN)
+        elif lay.gate_up is not None:
             _, hp = ops.w8x3_geglu_packed(xp, SHIFT_NORMED, *lay.gate_up, out_bf16=False, out_planes=True,
                                           out_shift=SHIFT_FFN)
         else:
