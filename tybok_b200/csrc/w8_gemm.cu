@@ -876,6 +876,7 @@ static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, co
   p.M = M; p.N = N; p.K = K; p.n_out = n_out;
   p.bt = pl.bt; p.nw = nw; p.splits = pl.splits; p.kb_total = pl.kb_total; p.kb_per_split = pl.kb_per_split;
   p.nstages = pl.nstages; p.tmem_cols = pl.tmem_cols; p.merge = pl.merge; p.pair = pl.pair; p.stage_off = pl.stage_off; p.epi = epi; p.pdl = host::pdl_enabled() ? 1 : 0;
+  p.np = np; p.row_scale = row_scale;
   p.out_scale = row_scale ? 1.0f : ldexpf(1.0f, -x_shift);
   p.plane_scale = ldexpf(1.0f, out_shift);
   p.scale0 = s0; p.scale1 = s1; p.bias0 = static_cast<const __nv_bfloat16*>(bias);
