@@ -453,6 +453,9 @@ def run_ours(args, rank: int, world: int) -> None:
     engine = PI05B200Engine(f"synthetic:pi05_full@{rank}", device=f"cuda:{local}", graph=False, warmup=True,
                             seed=rank, batch_size=args.batch, overlap=not args.no_overlap,
                             vision_precision=args.vision_precision)
+    if args.no_fold:  # comparison run: every AdaRMS norm as its own kernel
+        engine.model.fold = None
+    adarms_folded = engine.model.fold is not None
     l1 = ops.launch_count()
     engine._capture()
     launches_per_chunk = (ops.launch_count() - l1) // 3  # two warm-up passes + the captured pass
@@ -551,7 +554,8 @@ def run_ours(args, rank: int, world: int) -> None:
             "warmup": max(3, args.warmup), "ms_per_step": round(total_ms / args.steps, 4), "higher_is_better": False,
             "scaling": "weak", "vs_baseline": None, "dtype": DTYPE + " (activations as 3 exact e5m2 planes)",
             "data": "synthetic", "config": _config(args.batch, world),
-            "run": {"cuda_graph": True, "overlap_step0": not args.no_overlap, "vision_tower": args.vision_precision},
+            "run": {"cuda_graph": True, "overlap_step0": not args.no_overlap, "vision_tower": args.vision_precision,
+                    "adarms_folded": adarms_folded},
             "chunks_per_s": round(world * args.batch / (total_ms / args.steps) * 1e3, 2),
             "clocks": clocks, "gpu_launches": launches_per_chunk * args.steps,
             "e2e": {"value": round(e2e_p50, 4), "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -857,14 +861,21 @@ def run_profile_case(args) -> None:
         nbuf = max(2, int(260e6 // (n * args.k)) + 1)
         ws = [torch.randint(0, 120, (n, args.k), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn) for _ in range(nbuf)]
         sc = torch.rand(n, device=dev)
-        xp = ops.split3(torch.randn(args.m, args.k, device=dev).to(torch.bfloat16), 4)
+        x = torch.randn(args.m, args.k, device=dev).to(torch.bfloat16)
+        xp = ops.split3(x, 4)
+        if args.two_plane:
+            x2, rs = ops.norm_planes2(x, ops.NORM_RMS, torch.ones(args.k, device=dev))
         for i in range(nbuf + args.launches):
-            if args.gated:
+            if args.two_plane:
+                ops.w8x2_gemm(x2, rs, ws[i % nbuf], sc, epilogue=ops.EPI_GEGLU_PACKED if args.gated else ops.EPI_NONE,
+                              out_bf16=not args.gated, out_planes=args.gated)
+            elif args.gated:
                 ops.w8x3_geglu_packed(xp, 4, ws[i % nbuf], sc, out_bf16=False, out_planes=True)
             else:
                 ops.w8x3_linear(xp, 4, ws[i % nbuf], sc)
-        launches = nbuf + args.launches + 1
-        what = {"workload": f"gemm M={args.m} N={args.n} K={args.k} gated={args.gated}", "weight_copies": nbuf}
+        launches = nbuf + args.launches + 1 + int(args.two_plane)
+        what = {"workload": f"gemm M={args.m} N={args.n} K={args.k} gated={args.gated} two_plane={args.two_plane}",
+                "weight_copies": nbuf}
     else:
         d, lk, heads = args.head_dim, args.prefix + args.tokens, args.heads
         kv_heads = heads if args.mha else 1
@@ -897,6 +908,9 @@ def main() -> None:
         ap.add_argument(f"--{name}", type=int, default=default)
     ap.add_argument("--gated", action="store_true")
     ap.add_argument("--mha", action="store_true")
+    ap.add_argument("--no-fold", action="store_true",
+                    help="pi05_chunk: run the expert's AdaRMS norms as kernels instead of folding them into the GEMMs around them")
+    ap.add_argument("--two-plane", action="store_true", help="gemm workload: the two-plane e4m3 activation form")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))

@@ -265,6 +265,36 @@ int tybok_w8x3_geglu_packed(const void* x_planes, int x_shift, const void* w8_pa
                             int64_t ldh, void* h_planes, int out_shift, int M, int I, int K, int token_tile, int splits,
                             int* status_word, void* stream);
 
+/* AdaRMS norm folded into the GEMMs on either side of it (the action expert below 128 tokens, where
+ * a norm kernel between two latency-bound GEMMs costs as much as either of them):
+ *   y = W (x r (1 + scale) + shift) = r * W (x (1 + scale)) + W shift,   r = rsqrt(mean(x^2) + eps).
+ * tybok_w8x3_residual_next_adarms is tybok_w8x3_linear with the gated residual epilogue
+ * (x_new = residual + gate * (W8 a), gate fp32 [N], one group) that also writes the next norm's
+ * input in consumable form: u_planes [3][M][N] = planes of bf16(x_new * (1 + next_scale)) * 2^u_shift
+ * and ss_part [N / 128][M] = per channel tile, the row sums of squares of the bf16 x_new (N % 128 == 0).
+ * tybok_w8x3_qkv_rope_adarms / tybok_w8x3_geglu_packed_adarms are tybok_w8x3_qkv_rope /
+ * tybok_w8x3_geglu_packed on those planes: every accumulator row is multiplied by
+ * rsqrt(sum_t ss_part[t][m] / K + eps) and bias_rows [weight rows] fp32 = W shift (dequantised weight
+ * times the norm's shift row, in the order of the packed / paired weight rows) is added before the
+ * first bf16 rounding.  Against the norm kernel followed by the plain GEMM the only difference is
+ * the rounding point (x (1 + scale) instead of the normalised value is rounded to bf16).  Same role
+ * as the norm prologues of the reference's fused expert kernels
+ * (tybok/policies/pi05/models/triton_expert_fused_qkv_rope_attn.py:103-251); math of
+ * GemmaRMSNorm.forward with cond (tybok/policies/pi05/models/layers.py:34-84). */
+int tybok_w8x3_residual_next_adarms(const void* x_planes, int x_shift, const void* w8, const float* scale, void* y,
+                                    int64_t ldy, const void* residual, int64_t ldres, const float* gate,
+                                    const float* next_scale, void* u_planes, int u_shift, float* ss_part, int M, int N,
+                                    int K, int token_tile, int splits, int* status_word, void* stream);
+int tybok_w8x3_geglu_packed_adarms(const void* u_planes, int u_shift, const float* ss_part, int ss_tiles, float eps,
+                                   const float* bias_rows, const void* w8_packed, const float* scale_packed, void* h,
+                                   int64_t ldh, void* h_planes, int out_shift, int M, int I, int K, int token_tile,
+                                   int splits, int* status_word, void* stream);
+int tybok_w8x3_qkv_rope_adarms(const void* u_planes, int u_shift, const float* ss_part, int ss_tiles, float eps,
+                               const float* bias_rows, const void* w8_paired, const float* scale_paired, const int* pos,
+                               const void* cos_table, const void* sin_table, void* q_out, void* k_cache, void* v_cache,
+                               int B, int L, int H, int G, int D, int Lcap, int key_off, int K, int token_tile,
+                               int splits, int* status_word, void* stream);
+
 /* Enable (1) / disable (0) programmatic dependent launch for every kernel of this library
  * (process-wide; default 1).  With it, a kernel's weight prefetch overlaps the tail of the
  * previous kernel in the stream. */

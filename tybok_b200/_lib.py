@@ -78,6 +78,21 @@ SIGNATURES = {
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
          c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     ),
+    "tybok_w8x3_residual_next_adarms": (
+        c_int,
+        [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_i64, c_void_p, c_i64, c_void_p, c_void_p, c_void_p, c_int,
+         c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    ),
+    "tybok_w8x3_geglu_packed_adarms": (
+        c_int,
+        [c_void_p, c_int, c_void_p, c_int, ctypes.c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_i64, c_void_p, c_int, c_int,
+         c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    ),
+    "tybok_w8x3_qkv_rope_adarms": (
+        c_int,
+        [c_void_p, c_int, c_void_p, c_int, ctypes.c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    ),
     "tybok_w8a16_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "tybok_w8a16_linear": (
         c_int,

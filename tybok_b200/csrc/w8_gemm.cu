@@ -85,6 +85,16 @@ struct GemmParams {
                   // behind the ring with split-K, because peers write into it while this CTA still streams
   int np;        // activation planes: 3 (e5m2, fixed exponent shift) or 2 (e4m3, per-token scale row_scale[m])
   const float* row_scale;  // [M] 2^-k of every token row (two-plane form), else NULL
+  // AdaRMS norm folded into its neighbours (action expert below the two-plane threshold).  The GEMM
+  // that writes the residual stream also writes planes of bf16(x * (1 + scale_next)) and, per channel
+  // tile, the row sums of squares of x; the GEMM that follows multiplies its accumulator rows by
+  // rsqrt(mean(x^2) + eps) and adds W * shift as an fp32 bias: y = W (x r (1 + scale) + shift).
+  const float* nn_scale;  // producer: [N] fp32 scale row of the next norm, or NULL
+  float* nn_part;         // producer: [N / 128][M] partial sums of squares of the bf16 output rows
+  const float* dn_part;   // consumer: [dn_tiles][M] partial sums written by the producer, or NULL
+  int dn_tiles;
+  float dn_inv_w, dn_eps;
+  const float* bias_f32;  // consumer: [N] fp32 bias in weight-row order, or NULL
   int merge;     // 1: the planes are one UMMA of N = np*bt whose column groups the epilogue adds
   int pair;      // 1: CTA pairs (cluster of 2 along the channel tiles) run one UMMA of M = 256; each CTA
                  // loads its own weight tile and half of the activation planes (tm_w1 = half-tile map)
@@ -142,6 +152,22 @@ __device__ __forceinline__ void fail(Barriers* b, int* status, int code) {
 // them to use clusters of two, so it is an instantiation of its own).
 // EW: epilogue warps.  A split-K CTA has the SM to itself and a long serial epilogue per thread
 // (accumulator groups to push, rows to finish): sixteen warps halve both.
+// rsqrt(mean(x^2) + eps) of token row m from the producer's per-channel-tile partial sums (fixed order).
+// The partial sums were written by other SMs a moment ago (an L2 round trip each), so eight loads are
+// in flight at a time.
+__device__ __forceinline__ float deferred_rstd(const GemmParams& p, int m) {
+  float t = 0.f;
+  for (int i0 = 0; i0 < p.dn_tiles; i0 += 8) {
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      v[i] = i0 + i < p.dn_tiles ? __ldcg(p.dn_part + static_cast<long long>(i0 + i) * p.M + m) : 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += v[i];
+  }
+  return rsqrtf(t * p.dn_inv_w + p.dn_eps);
+}
+
 template <bool PAIR, int EW = EPI_WARPS>
 __global__ void __launch_bounds__(32 * (2 + EW), EW == EPI_WARPS ? 2 : 1)
 w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1,
@@ -215,6 +241,9 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
   const uint32_t tmem = bars.tmem_base;
   // Per-thread epilogue constants (4 consecutive channels), fetched while the main loop runs.
   float s0[4] = {0, 0, 0, 0}, s1[4] = {0, 0, 0, 0}, b0[4] = {0, 0, 0, 0};
+  float b1[4] = {0, 0, 0, 0};   // bias of the second half tile (packed forms, fp32 bias only)
+  float nsc[4] = {0, 0, 0, 0};  // 1 + scale of the next norm for this thread's channels (producer form)
+  float rs_pf = 1.0f;           // deferred norm: rstd of this thread's first token row
   uint2 res_pf[4] = {};  // residual of this thread's first four token rows, fetched early
   float4 gate_pf = make_float4(0.f, 0.f, 0.f, 0.f);  // gate values of the first token row's group (fp32 form)
   int gate_pf_group = -1;
@@ -405,6 +434,18 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
 #pragma unroll
           for (int e = 0; e < 4; ++e) b0[e] = __bfloat162float(p.bias0[n + e]);
         }
+        if (p.bias_f32) {  // weight-row order: the second half tile of a packed form has its own rows
+          const float4 t0 = *reinterpret_cast<const float4*>(p.bias_f32 + n_tile * BN + col0);
+          b0[0] = t0.x; b0[1] = t0.y; b0[2] = t0.z; b0[3] = t0.w;
+          if (packed) {
+            const float4 t1 = *reinterpret_cast<const float4*>(p.bias_f32 + n_tile * BN + BN / 2 + col0);
+            b1[0] = t1.x; b1[1] = t1.y; b1[2] = t1.z; b1[3] = t1.w;
+          }
+        }
+        if (p.nn_scale) {
+          const float4 t0 = *reinterpret_cast<const float4*>(p.nn_scale + n);
+          nsc[0] = 1.0f + t0.x; nsc[1] = 1.0f + t0.y; nsc[2] = 1.0f + t0.z; nsc[3] = 1.0f + t0.w;
+        }
         if (p.epi == EPI_RESIDUAL && p.gate && !p.gate_bf16) {
           // fp32 gates are per-step constants (precomputed modulations), touched once per chunk
           // and therefore cold in L2: fetch them now, not between the accumulator and the stores.
@@ -430,6 +471,10 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
       // kernel now, under the main loop, not between the accumulator and the stores.
       if (p.pdl) pdl_wait();
       if (n < p.n_out) {
+        if (p.dn_part) {  // written by the previous GEMM: this thread's first row, under the main loop
+          const int rl = packed ? ((tid - 64) >> 5) * 2 + (v4p >> 4) : (tid - 64) >> 5;
+          if (rl < own_rows) rs_pf = deferred_rstd(p, m_base + rank * rpr + rl);
+        }
         if (p.epi == EPI_RESIDUAL) {
           // The residual was written by an earlier kernel: fetch the rows this thread will finish
           // first, long before the accumulator is ready.
@@ -552,8 +597,9 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
           a1.x += g.x; a1.y += g.y; a1.z += g.z; a1.w += g.w;
         }
       }
-      if (p.row_scale) {  // two-plane form: undo the token's power-of-two pre-scale (exact)
-        const float rs = p.row_scale[m];
+      if (p.row_scale || p.dn_part) {
+        // two-plane form: undo the token's power-of-two pre-scale (exact); deferred norm: the row's rstd
+        const float rs = p.row_scale ? p.row_scale[m] : (rl == row0 ? rs_pf : deferred_rstd(p, m));
         a0.x *= rs; a0.y *= rs; a0.z *= rs; a0.w *= rs;
         a1.x *= rs; a1.y *= rs; a1.z *= rs; a1.w *= rs;
       }
@@ -566,16 +612,16 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[e] = gelu_tanh_fast(o[e]);
       } else if (p.epi == EPI_GEGLU || p.epi == EPI_GEGLU_PACKED) {
-        const float u[4] = {bf16_round(a1.x * s1[0]), bf16_round(a1.y * s1[1]), bf16_round(a1.z * s1[2]),
-                            bf16_round(a1.w * s1[3])};
+        const float u[4] = {bf16_round(a1.x * s1[0] + b1[0]), bf16_round(a1.y * s1[1] + b1[1]),
+                            bf16_round(a1.z * s1[2] + b1[2]), bf16_round(a1.w * s1[3] + b1[3])};
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[e] = bf16_round(gelu_tanh_fast(o[e])) * u[e];
       } else if (p.epi == EPI_QKV_ROPE) {
         // o = dimensions d..d+3 of one head slot, u = their partners d + D/2; rotate q and k
         // slots (bf16 rounding points of rope.py:67-75), pass v through, store both halves.
         const RopeEpi& r = p.rope;
-        float u[4] = {bf16_round(a1.x * s1[0]), bf16_round(a1.y * s1[1]), bf16_round(a1.z * s1[2]),
-                      bf16_round(a1.w * s1[3])};
+        float u[4] = {bf16_round(a1.x * s1[0] + b1[0]), bf16_round(a1.y * s1[1] + b1[1]),
+                      bf16_round(a1.z * s1[2] + b1[2]), bf16_round(a1.w * s1[3] + b1[3])};
         const int tps = r.D >> 7;  // 128-row tiles per head slot
         const int slot = n_tile / tps;
         const int d = (n_tile - slot * tps) * 64 + col0;
@@ -652,8 +698,19 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
       }
       if (p.y_planes) {
         // The next GEMM's activation planes, from the bf16-rounded values just produced.
-        const float xs[4] = {__bfloat162float(o01.x) * p.plane_scale, __bfloat162float(o01.y) * p.plane_scale,
-                             __bfloat162float(o23.x) * p.plane_scale, __bfloat162float(o23.y) * p.plane_scale};
+        float xs[4] = {__bfloat162float(o01.x), __bfloat162float(o01.y), __bfloat162float(o23.x), __bfloat162float(o23.y)};
+        if (p.nn_scale) {
+          // Next norm folded in: this tile's share of the row's sum of squares (the warp holds the 128
+          // channels of one row) and planes of bf16(x * (1 + scale)) instead of planes of x.
+          float ss = (xs[0] * xs[0] + xs[1] * xs[1]) + (xs[2] * xs[2] + xs[3] * xs[3]);
+#pragma unroll
+          for (int sh = 16; sh > 0; sh >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, sh);
+          if (v4 == 0) p.nn_part[static_cast<long long>(n_tile) * p.M + m] = ss;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) xs[e] = bf16_round(xs[e] * nsc[e]);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) xs[e] *= p.plane_scale;
         uint32_t w1, w2, w3;
         split3_quad(xs, w1, w2, w3);
         uint8_t* dst = p.y_planes + static_cast<long long>(m) * p.n_out + n;
@@ -824,12 +881,23 @@ static bool make_plan(int M, int N, int K, int nw, int force_bt, int force_split
   return true;
 }
 
+// AdaRMS norm folded into the GEMMs on either side of it (see GemmParams).
+struct NormFold {
+  const float* next_scale = nullptr;  // producer
+  float* part_out = nullptr;
+  const float* part_in = nullptr;     // consumer
+  int part_tiles = 0;
+  int norm_width = 0;
+  float eps = 0.f;
+  const float* bias_rows = nullptr;
+};
+
 static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, const float* s0, const float* s1,
                        const void* bias, void* y, void* y_planes, int M, int N, int K, long long ldy, int epi,
                        const void* res, long long ldres, const void* gate, long long ldgate, int rows_per_gate,
                        int gate_bf16, int x_shift, int out_shift, int force_bt, int force_splits, int* status,
                        cudaStream_t stream, const RopeEpi* rope = nullptr, bool check_only = false,
-                       const float* row_scale = nullptr) {
+                       const float* row_scale = nullptr, const NormFold* fold = nullptr) {
   const int np = row_scale ? 2 : 3;  // two e4m3 planes with a per-token scale, or three e5m2 planes
   const int nw = w1 ? 2 : 1;
   if (!planes || !w0 || !s0 || (!y && !y_planes && !rope)) return host::fail(TYBOK_ERR_ARG, "w8 gemm: null pointer argument");
@@ -850,6 +918,19 @@ static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, co
   if (gate && rows_per_gate <= 0) return host::fail(TYBOK_ERR_ARG, "w8 gemm: rows_per_gate must be positive");
   if (x_shift < -60 || x_shift > 60 || out_shift < -60 || out_shift > 60)
     return host::fail(TYBOK_ERR_ARG, "w8 gemm: exponent shift out of range");
+  if (fold && (fold->next_scale || fold->part_out)) {
+    if (!fold->next_scale || !fold->part_out || epi != EPI_RESIDUAL || !y_planes || N % BN != 0 || w1)
+      return host::fail(TYBOK_ERR_ARG, "w8 gemm: the next-norm form needs the residual epilogue, output planes, N % 128 == 0");
+    if ((reinterpret_cast<uintptr_t>(fold->next_scale) & 15) || (reinterpret_cast<uintptr_t>(fold->part_out) & 3))
+      return host::fail(TYBOK_ERR_ARG, "w8 gemm: next_scale must be 16-byte aligned");
+  }
+  if (fold && (fold->part_in || fold->bias_rows)) {
+    if (!fold->part_in || !fold->bias_rows || fold->part_tiles <= 0 || fold->norm_width <= 0 || row_scale || w1 || bias ||
+        (epi != EPI_QKV_ROPE && epi != EPI_GEGLU_PACKED && epi != EPI_NONE))
+      return host::fail(TYBOK_ERR_ARG, "w8 gemm: the folded-norm form takes row sums, their tile count, the norm width and an fp32 bias");
+    if (reinterpret_cast<uintptr_t>(fold->bias_rows) & 15)
+      return host::fail(TYBOK_ERR_ARG, "w8 gemm: bias_rows must be 16-byte aligned");
+  }
   if (int rc = host::require_sm100()) return rc;
 
   Plan pl;
@@ -888,6 +969,12 @@ static int launch_gemm(const uint8_t* planes, const void* w0, const void* w1, co
   p.dbg = host::counter_buffer();
   p.epi_wait_limit = host::epilogue_wait_limit() > 0 ? host::epilogue_wait_limit() : kWaitLimitCycles;
   if (rope) p.rope = *rope;
+  if (fold) {
+    p.nn_scale = fold->next_scale; p.nn_part = fold->part_out;
+    p.dn_part = fold->part_in; p.dn_tiles = fold->part_tiles;
+    p.dn_inv_w = fold->norm_width > 0 ? 1.0f / static_cast<float>(fold->norm_width) : 0.f;
+    p.dn_eps = fold->eps; p.bias_f32 = fold->bias_rows;
+  }
 
   static bool attr_set[64] = {};
   const int dev = host::current_device();
@@ -1068,6 +1155,57 @@ int tybok_w8x2_qkv_rope(const void* x_planes2, const float* row_scale, const voi
   return tb::launch_gemm(static_cast<const uint8_t*>(x_planes2), w8_paired, nullptr, scale_paired, nullptr, nullptr,
                          nullptr, nullptr, B * L, (H + 2 * G) * D, K, 0, tb::EPI_QKV_ROPE, nullptr, 0, nullptr, 0, 1, 0, 0,
                          0, token_tile, splits, status_word, static_cast<cudaStream_t>(stream), &r, false, row_scale);
+}
+
+int tybok_w8x3_residual_next_adarms(const void* x_planes, int x_shift, const void* w8, const float* scale, void* y,
+                                    int64_t ldy, const void* residual, int64_t ldres, const float* gate,
+                                    const float* next_scale, void* u_planes, int u_shift, float* ss_part, int M, int N,
+                                    int K, int token_tile, int splits, int* status_word, void* stream) {
+  if (!y || !gate || !next_scale || !u_planes || !ss_part)
+    return tb::host::fail(TYBOK_ERR_ARG, "w8x3_residual_next_adarms: null pointer argument");
+  tb::NormFold f;
+  f.next_scale = next_scale; f.part_out = ss_part;
+  return tb::launch_gemm(static_cast<const uint8_t*>(x_planes), w8, nullptr, scale, nullptr, nullptr, y, u_planes, M, N, K,
+                         ldy, tb::EPI_RESIDUAL, residual, ldres, gate, 0, M, 0, x_shift, u_shift, token_tile, splits,
+                         status_word, static_cast<cudaStream_t>(stream), nullptr, false, nullptr, &f);
+}
+
+int tybok_w8x3_geglu_packed_adarms(const void* u_planes, int u_shift, const float* ss_part, int ss_tiles, float eps,
+                                   const float* bias_rows, const void* w8_packed, const float* scale_packed, void* h,
+                                   int64_t ldh, void* h_planes, int out_shift, int M, int I, int K, int token_tile,
+                                   int splits, int* status_word, void* stream) {
+  tb::NormFold f;
+  f.part_in = ss_part; f.part_tiles = ss_tiles; f.norm_width = K; f.eps = eps; f.bias_rows = bias_rows;
+  if (!ss_part || !bias_rows) return tb::host::fail(TYBOK_ERR_ARG, "w8x3_geglu_packed_adarms: null pointer argument");
+  return tb::launch_gemm(static_cast<const uint8_t*>(u_planes), w8_packed, nullptr, scale_packed, nullptr, nullptr, h,
+                         h_planes, M, 2 * I, K, ldh, tb::EPI_GEGLU_PACKED, nullptr, 0, nullptr, 0, 1, 0, u_shift,
+                         out_shift, token_tile, splits, status_word, static_cast<cudaStream_t>(stream), nullptr, false,
+                         nullptr, &f);
+}
+
+int tybok_w8x3_qkv_rope_adarms(const void* u_planes, int u_shift, const float* ss_part, int ss_tiles, float eps,
+                               const float* bias_rows, const void* w8_paired, const float* scale_paired, const int* pos,
+                               const void* cos_table, const void* sin_table, void* q_out, void* k_cache, void* v_cache,
+                               int B, int L, int H, int G, int D, int Lcap, int key_off, int K, int token_tile,
+                               int splits, int* status_word, void* stream) {
+  if (!ss_part || !bias_rows || !pos || !cos_table || !sin_table || !q_out || !k_cache || !v_cache)
+    return tb::host::fail(TYBOK_ERR_ARG, "w8x3_qkv_rope_adarms: null pointer argument");
+  if (B <= 0 || L <= 0 || H <= 0 || G <= 0 || D <= 0 || D % 128 != 0 || key_off < 0 || key_off + L > Lcap)
+    return tb::host::fail(TYBOK_ERR_ARG, "w8x3_qkv_rope_adarms: needs head_dim % 128 == 0 and key_off + L <= Lcap");
+  if ((reinterpret_cast<uintptr_t>(cos_table) | reinterpret_cast<uintptr_t>(sin_table) |
+       reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 7)
+    return tb::host::fail(TYBOK_ERR_ARG, "w8x3_qkv_rope_adarms: tables, q and caches must be 8-byte aligned");
+  tb::RopeEpi r{};
+  r.pos = pos; r.cos = static_cast<const __nv_bfloat16*>(cos_table); r.sin = static_cast<const __nv_bfloat16*>(sin_table);
+  r.q = static_cast<__nv_bfloat16*>(q_out); r.kcache = static_cast<__nv_bfloat16*>(k_cache);
+  r.vcache = static_cast<__nv_bfloat16*>(v_cache);
+  r.L = L; r.H = H; r.G = G; r.D = D; r.Lcap = Lcap; r.key_off = key_off;
+  tb::NormFold f;
+  f.part_in = ss_part; f.part_tiles = ss_tiles; f.norm_width = K; f.eps = eps; f.bias_rows = bias_rows;
+  return tb::launch_gemm(static_cast<const uint8_t*>(u_planes), w8_paired, nullptr, scale_paired, nullptr, nullptr,
+                         nullptr, nullptr, B * L, (H + 2 * G) * D, K, 0, tb::EPI_QKV_ROPE, nullptr, 0, nullptr, 0, 1, 0,
+                         u_shift, 0, token_tile, splits, status_word, static_cast<cudaStream_t>(stream), &r, false,
+                         nullptr, &f);
 }
 
 int tybok_w8a16_linear(const void* x, const void* w8, const float* scale, const void* bias, void* y, int M, int N,

@@ -67,6 +67,15 @@ _L.define("w8x2_gemm(Tensor planes2, Tensor row_scale, Tensor w8, Tensor scale, 
 _L.define("w8x2_qkv_rope(Tensor planes2, Tensor row_scale, Tensor w8_paired, Tensor scale_paired, Tensor pos, Tensor cos, "
           "Tensor sin, Tensor(a!) k_cache, Tensor(b!) v_cache, int heads, int key_off, int token_tile, int splits) -> Tensor")
 
+_L.define("w8x3_residual_next_adarms(Tensor planes, int shift, Tensor w8, Tensor scale, Tensor residual, Tensor gate, "
+          "Tensor next_scale, int out_shift, int token_tile, int splits) -> (Tensor, Tensor, Tensor)")
+_L.define("w8x3_geglu_packed_adarms(Tensor u_planes, int shift, Tensor ss_part, float eps, Tensor bias_rows, "
+          "Tensor w8_packed, Tensor scale_packed, bool out_bf16, bool out_planes, int out_shift, int token_tile, "
+          "int splits) -> (Tensor, Tensor)")
+_L.define("w8x3_qkv_rope_adarms(Tensor u_planes, int shift, Tensor ss_part, float eps, Tensor bias_rows, Tensor w8_paired, "
+          "Tensor scale_paired, Tensor pos, Tensor cos, Tensor sin, Tensor(a!) k_cache, Tensor(b!) v_cache, int heads, "
+          "int key_off, int token_tile, int splits) -> Tensor")
+
 NORM_RMS, NORM_ADARMS, NORM_LN_MODULATE, NORM_LN_AFFINE = 0, 1, 2, 3
 EPI_GEGLU_PACKED = 4
 
@@ -705,6 +714,120 @@ def w8x2_qkv_rope(planes2, row_scale, w8_paired, scale_paired, pos, cos, sin, k_
     """``w8x3_qkv_rope`` on two-plane activations; see ``tybok_w8x2_qkv_rope``."""
     return torch.ops.tybok_b200.w8x2_qkv_rope(planes2, row_scale, w8_paired, scale_paired, pos, cos, sin, k_cache,
                                               v_cache, heads, key_off, token_tile, splits)
+
+
+def _check_fold_in(u_planes, ss_part, bias_rows, rows, what):
+    if u_planes.dtype != torch.uint8 or u_planes.dim() != 3 or u_planes.shape[0] != 3 or not u_planes.is_contiguous():
+        raise TypeError(f"{what}: u_planes must be a contiguous uint8 [3, M, K] tensor")
+    m = u_planes.shape[1]
+    if ss_part.dtype != torch.float32 or ss_part.dim() != 2 or ss_part.shape[1] != m or not ss_part.is_contiguous():
+        raise TypeError(f"{what}: ss_part must be contiguous fp32 [tiles, M]")
+    if bias_rows.dtype != torch.float32 or bias_rows.numel() != rows or not bias_rows.is_contiguous():
+        raise TypeError(f"{what}: bias_rows must be contiguous fp32 [weight rows]")
+
+
+def _w8x3_residual_next_adarms_cuda(planes, shift, w8, scale, residual, gate, next_scale, out_shift, token_tile, splits):
+    lib = _lib.load()
+    _check_w8(w8, "w8x3_residual_next_adarms")
+    n, k = w8.shape
+    if planes.dtype != torch.uint8 or planes.dim() != 3 or planes.shape[0] != 3 or planes.shape[2] != k:
+        raise TypeError("w8x3_residual_next_adarms: planes must be uint8 [3, M, K]")
+    m = planes.shape[1]
+    res2 = _rows(residual)
+    if res2.shape != (m, n) or res2.dtype != torch.bfloat16 or n % 128 != 0:
+        raise ValueError("w8x3_residual_next_adarms: residual must be bf16 [M, N], N % 128 == 0")
+    for t, name in ((gate, "gate"), (next_scale, "next_scale")):
+        if t.dtype != torch.float32 or t.numel() != n or t.stride(-1) != 1:
+            raise TypeError(f"w8x3_residual_next_adarms: {name} must be fp32 [N] with unit stride")
+    y = torch.empty((m, n), dtype=torch.bfloat16, device=planes.device)
+    up = torch.empty((3, m, n), dtype=torch.uint8, device=planes.device)
+    part = torch.empty((n // 128, m), dtype=torch.float32, device=planes.device)
+    rc = lib.tybok_w8x3_residual_next_adarms(planes.data_ptr(), int(shift), w8.data_ptr(), scale.data_ptr(), y.data_ptr(), n,
+                                             res2.data_ptr(), res2.stride(0), gate.data_ptr(), next_scale.data_ptr(),
+                                             up.data_ptr(), int(out_shift), part.data_ptr(), m, n, k, int(token_tile),
+                                             int(splits), status_word(planes.device).data_ptr(), _stream(planes))
+    _lib.check(rc, "tybok_w8x3_residual_next_adarms")
+    return y, up, part
+
+
+def _w8x3_geglu_packed_adarms_cuda(u_planes, shift, ss_part, eps, bias_rows, w8_packed, scale_packed, out_bf16, out_planes,
+                                   out_shift, token_tile, splits):
+    lib = _lib.load()
+    _check_w8(w8_packed, "w8x3_geglu_packed_adarms")
+    n2, k = w8_packed.shape
+    _check_fold_in(u_planes, ss_part, bias_rows, n2, "w8x3_geglu_packed_adarms")
+    if u_planes.shape[2] != k:
+        raise ValueError("w8x3_geglu_packed_adarms: planes and weight disagree on K")
+    m = u_planes.shape[1]
+    h, hp = _outputs(m, n2 // 2, u_planes.device, out_bf16, out_planes)
+    rc = lib.tybok_w8x3_geglu_packed_adarms(u_planes.data_ptr(), int(shift), ss_part.data_ptr(), ss_part.shape[0], float(eps),
+                                            bias_rows.data_ptr(), w8_packed.data_ptr(), scale_packed.data_ptr(),
+                                            h.data_ptr() if out_bf16 else None, n2 // 2, hp.data_ptr() if out_planes else None,
+                                            int(out_shift), m, n2 // 2, k, int(token_tile), int(splits),
+                                            status_word(u_planes.device).data_ptr(), _stream(u_planes))
+    _lib.check(rc, "tybok_w8x3_geglu_packed_adarms")
+    return h, hp
+
+
+def _w8x3_qkv_rope_adarms_cuda(u_planes, shift, ss_part, eps, bias_rows, w8_paired, scale_paired, pos, cos, sin, k_cache,
+                               v_cache, heads, key_off, token_tile, splits):
+    lib = _lib.load()
+    _check_w8(w8_paired, "w8x3_qkv_rope_adarms")
+    b, g, lcap, d = k_cache.shape
+    _check_fold_in(u_planes, ss_part, bias_rows, w8_paired.shape[0], "w8x3_qkv_rope_adarms")
+    m, k = u_planes.shape[1], u_planes.shape[2]
+    if w8_paired.shape != ((heads + 2 * g) * d, k) or scale_paired.numel() != w8_paired.shape[0] or d % 128 != 0:
+        raise ValueError("w8x3_qkv_rope_adarms: weight must be [(H+2G)*D, K] with head_dim % 128 == 0")
+    if pos.dtype != torch.int32 or pos.numel() != m or not pos.is_contiguous() or m % b != 0:
+        raise TypeError("w8x3_qkv_rope_adarms: pos must be contiguous int32 [B*L]")
+    for t in (k_cache, v_cache, cos, sin):
+        if t.dtype != torch.bfloat16 or not t.is_contiguous():
+            raise TypeError("w8x3_qkv_rope_adarms: caches and cos/sin tables must be contiguous bf16")
+    if v_cache.shape != k_cache.shape or cos.shape[-1] != d or sin.shape != cos.shape:
+        raise ValueError("w8x3_qkv_rope_adarms: cache / table shapes disagree")
+    q = torch.empty((m, heads * d), dtype=torch.bfloat16, device=u_planes.device)
+    rc = lib.tybok_w8x3_qkv_rope_adarms(u_planes.data_ptr(), int(shift), ss_part.data_ptr(), ss_part.shape[0], float(eps),
+                                        bias_rows.data_ptr(), w8_paired.data_ptr(), scale_paired.data_ptr(), pos.data_ptr(),
+                                        cos.data_ptr(), sin.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                        b, m // b, heads, g, d, lcap, int(key_off), k, int(token_tile), int(splits),
+                                        status_word(u_planes.device).data_ptr(), _stream(u_planes))
+    _lib.check(rc, "tybok_w8x3_qkv_rope_adarms")
+    return q
+
+
+_L.impl("w8x3_residual_next_adarms", _w8x3_residual_next_adarms_cuda, "CUDA")
+_L.impl("w8x3_geglu_packed_adarms", _w8x3_geglu_packed_adarms_cuda, "CUDA")
+_L.impl("w8x3_qkv_rope_adarms", _w8x3_qkv_rope_adarms_cuda, "CUDA")
+
+
+def w8x3_residual_next_adarms(planes, shift, w8, scale, residual, gate, next_scale, *, out_shift=0, token_tile=0, splits=0):
+    """``x_new = residual + gate * (W8 a)`` with the next AdaRMS norm's input prepared in the epilogue:
+    returns ``(x_new bf16 [M, N], u_planes [3, M, N] of bf16(x_new * (1 + next_scale)) * 2**out_shift,
+    ss_part [N / 128, M])``; see ``tybok_w8x3_residual_next_adarms``."""
+    return torch.ops.tybok_b200.w8x3_residual_next_adarms(planes, shift, w8, scale, residual, gate, next_scale, out_shift,
+                                                          token_tile, splits)
+
+
+def w8x3_geglu_packed_adarms(u_planes, shift, ss_part, bias_rows, w8_packed, scale_packed, *, eps=1e-6, out_bf16=True,
+                             out_planes=False, out_shift=DEFAULT_SHIFT, token_tile=0, splits=0):
+    """``w8x3_geglu_packed`` on the output of ``w8x3_residual_next_adarms`` (the norm's rstd and ``W shift``
+    applied in the epilogue); see ``tybok_w8x3_geglu_packed_adarms``."""
+    return torch.ops.tybok_b200.w8x3_geglu_packed_adarms(u_planes, shift, ss_part, eps, bias_rows, w8_packed, scale_packed,
+                                                         out_bf16, out_planes, out_shift, token_tile, splits)
+
+
+def w8x3_qkv_rope_adarms(u_planes, shift, ss_part, bias_rows, w8_paired, scale_paired, pos, cos, sin, k_cache, v_cache, *,
+                         heads, key_off, eps=1e-6, token_tile=0, splits=0):
+    """``w8x3_qkv_rope`` on the output of ``w8x3_residual_next_adarms``; see ``tybok_w8x3_qkv_rope_adarms``."""
+    return torch.ops.tybok_b200.w8x3_qkv_rope_adarms(u_planes, shift, ss_part, eps, bias_rows, w8_paired, scale_paired, pos,
+                                                     cos, sin, k_cache, v_cache, heads, key_off, token_tile, splits)
+
+
+def shift_bias_rows(w8_rows: torch.Tensor, scale_rows: torch.Tensor, shift_row: torch.Tensor) -> torch.Tensor:
+    """``W shift`` for the folded AdaRMS form: dequantised weight rows (in the order the kernel streams
+    them) times the norm's shift row, fp32 ``[rows]``."""
+    w = w8_rows.view(torch.float8_e4m3fn).float() if w8_rows.dtype == torch.uint8 else w8_rows.float()
+    return ((w @ shift_row.reshape(-1).float()) * scale_rows.reshape(-1).float()).contiguous()
 
 
 def launch_count() -> int:

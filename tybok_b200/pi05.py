@@ -32,6 +32,7 @@ from .weights import EXPERT, PROJECTOR, VISION, VLM, quantize_w8
 SHIFT_NORMED = 4  # RMS-normalised activations, O(1)
 SHIFT_ATTN = 6  # attention outputs (convex combinations of V rows)
 SHIFT_FFN = 4  # gelu(gate) * up
+SHIFT_FOLD = 0  # residual stream times (1 + scale), not normalised: exact from 2^-7 to 57344
 #: From this many token rows a GEMM fed by a norm takes its activations as two e4m3 planes with a
 #: per-row power-of-two scale (a third less tensor work, token tiles to 128); below it the GEMMs are
 #: bound by launch latency and keep the three-plane form.
@@ -170,6 +171,23 @@ class PI05Model:
             mods, final = self._layer_mods(cond[i : i + 1])
             self.mods.append(mods)
             self.final_mods.append(final)
+        # W * shift of both norms of every layer and step, for the form that folds the AdaRMS norm
+        # into the GEMMs around it: fold[step][layer] = (bias of the paired qkv rows, bias of the packed gate/up rows).
+        self.fold = None
+        w = s.expert.width
+        if w % 128 == 0 and all(lay.gate_up is not None for lay in self.exp_layers):
+            per_layer = []
+            for li, lay in enumerate(self.exp_layers):
+                sh_in = torch.stack([self.mods[i][li][0][0, w : 2 * w] for i in range(s.steps)])    # [steps, W]
+                sh_post = torch.stack([self.mods[i][li][1][0, w : 2 * w] for i in range(s.steps)])
+                per_layer.append((self._shift_bias(lay.qkv_paired, sh_in), self._shift_bias(lay.gate_up, sh_post)))
+            self.fold = [[(bq[i].contiguous(), bg[i].contiguous()) for bq, bg in per_layer] for i in range(s.steps)]
+
+    @staticmethod
+    def _shift_bias(w8_scale, shifts: torch.Tensor) -> torch.Tensor:
+        """``[steps, rows]`` fp32: dequantised weight rows times each step's shift row."""
+        w8, scale = w8_scale
+        return (shifts.float() @ w8.view(torch.float8_e4m3fn).float().t()) * scale.reshape(1, -1).float()
 
     # ------------------------------------------------------------------ non-fp8 front end
     def _pack_vision(self):
@@ -334,6 +352,49 @@ class PI05Model:
                                rows_per_gate=m)
         return x
 
+    def _expert_pass(self, mods, fold, x, b, l, pos, caches, key_off, key_valid, wait=None):
+        """All expert layers of one denoise step on the suffix embedding ``x [B*L, W]``; ``wait(i)`` runs
+        before layer ``i``.  Below the two-plane threshold, and with the step's ``W shift`` constants at
+        hand (``fold``), only the first norm of the pass is a kernel: every later AdaRMS norm is folded
+        into the GEMM that writes its input (sums of squares, planes of ``x (1 + scale)``) and the GEMM
+        that reads its output (rstd and ``W shift`` in the epilogue)."""
+        spec = self.shape.expert
+        m, w = x.shape[0], spec.width
+        if fold is None or m >= TWO_PLANE_MIN_TOKENS:
+            for i, lay in enumerate(self.exp_layers):
+                if wait is not None:
+                    wait(i)
+                x = self._layer(spec, lay, x, b, l, pos, caches[i], key_off, key_valid, mods[i])
+            return x
+        carry = None  # (u_planes, ss_part) of the residual stream, written by the previous layer's down projection
+        last = len(self.exp_layers) - 1
+        for i, lay in enumerate(self.exp_layers):
+            if wait is not None:
+                wait(i)
+            mod_in, mod_post = mods[i]
+            cache = caches[i]
+            if carry is None:
+                xp = ops.rmsnorm(x, mod=mod_in, rows_per_group=m, out_shift=SHIFT_NORMED)[1]
+                q = ops.w8x3_qkv_rope(xp, SHIFT_NORMED, *lay.qkv_paired, pos, self.cos, self.sin, cache[0], cache[1],
+                                      heads=spec.num_heads, key_off=key_off)
+            else:
+                q = ops.w8x3_qkv_rope_adarms(carry[0], SHIFT_FOLD, carry[1], fold[i][0], *lay.qkv_paired, pos, self.cos,
+                                             self.sin, cache[0], cache[1], heads=spec.num_heads, key_off=key_off)
+            _, ap = ops.attention(q, cache[0], cache[1], key_valid, tokens=l, keys=key_off + l,
+                                  scale=spec.head_dim**-0.5, out_bf16=False, out_planes=True, out_shift=SHIFT_ATTN)
+            x, up, part = ops.w8x3_residual_next_adarms(ap, SHIFT_ATTN, *lay.o, x, mod_in[0, 2 * w :], mod_post[0, :w],
+                                                        out_shift=SHIFT_FOLD)
+            _, hp = ops.w8x3_geglu_packed_adarms(up, SHIFT_FOLD, part, fold[i][1], *lay.gate_up, out_bf16=False,
+                                                 out_planes=True, out_shift=SHIFT_FFN)
+            if i == last:
+                x, _ = ops.w8x3_linear(hp, SHIFT_FFN, *lay.down, epilogue=ops.EPI_RESIDUAL, residual=x,
+                                       gate=mod_post[:, 2 * w :], rows_per_gate=m)
+            else:
+                x, up, part = ops.w8x3_residual_next_adarms(hp, SHIFT_FFN, *lay.down, x, mod_post[0, 2 * w :],
+                                                            mods[i + 1][0][0, :w], out_shift=SHIFT_FOLD)
+                carry = (up, part)
+        return x
+
     # ------------------------------------------------------------------ prefix + denoise
     def prefill(self, prefix_embs: torch.Tensor, pad: torch.Tensor, layer_done=None):
         """VLM prefix pass filling the per-layer post-RoPE (K, V) caches (gemma.py:61-125,
@@ -370,20 +431,16 @@ class PI05Model:
         allowed = torch.cat([pad, torch.ones(b, l, dtype=torch.bool, device=x.device)], dim=1)  # [B, Lp+L]
         key_valid = allowed.to(torch.uint8).contiguous()
         pos = (pad.sum(dim=-1, keepdim=True) + torch.arange(l, device=x.device)[None, :]).to(torch.int32).reshape(-1)
-        for i, lay in enumerate(self.exp_layers):
-            x = self._layer(spec, lay, x, b, l, pos, caches[i], lp, key_valid, layer_mods[i])
+        fold = self.fold[step] if mods is None and self.fold is not None else None
+        x = self._expert_pass(layer_mods, fold, x, b, l, pos, caches, lp, key_valid)
         y, _ = ops.rmsnorm(x, mod=final_mod, rows_per_group=b * l, out_bf16=True, out_planes=False)
         y = y.view(b, l, spec.width)[:, -s.chunk :].float()
         return F.linear(y, *self.action_out)
 
     def _expert_layers(self, step: int, h: torch.Tensor, b: int, l: int, pad: torch.Tensor, key_valid, pos):
         """All expert layers of one denoise step on the suffix embedding ``h [B*L, W]``."""
-        caches = self._caches(b)
-        lp = pad.shape[1]
-        x = h
-        for i, lay in enumerate(self.exp_layers):
-            x = self._layer(self.shape.expert, lay, x, b, l, pos, caches[i], lp, key_valid, self.mods[step][i])
-        return x
+        fold = self.fold[step] if self.fold is not None else None
+        return self._expert_pass(self.mods[step], fold, h, b, l, pos, self._caches(b), pad.shape[1], key_valid)
 
     @torch.no_grad()
     def sample_actions(self, images, img_masks, tokens, masks, noise: torch.Tensor) -> torch.Tensor:
@@ -448,10 +505,8 @@ class PI05Model:
 
         self.prefill(embs, pad, layer_done)
         with torch.cuda.stream(side):
-            x = h
-            for i, lay in enumerate(self.exp_layers):
-                side.wait_event(done[i])
-                x = self._layer(s.expert, lay, x, b, l, pos, caches[i], lp, key_valid, self.mods[0][i])
+            x = self._expert_pass(self.mods[0], self.fold[0] if self.fold is not None else None, h, b, l, pos, caches,
+                                  lp, key_valid, wait=lambda i: side.wait_event(done[i]))
             h = ops.action_tail(x, self.final_mods[0], *self.action_out, x_t, dt, *self.action_in,
                                 rows_per_group=b * l, embed=s.steps > 1)
             join = torch.cuda.Event()
