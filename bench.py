@@ -244,6 +244,7 @@ def _gemm_roofline(shape, batch: int, dev, peaks, peaks_kind, sweep: bool) -> di
     ``achieved`` aggregates the action-expert launches (M = 50*batch, HBM-bound, 720 of the 792
     launches of a chunk); the prefix launches (M = 544*batch, tensor-bound) are reported beside."""
     from tybok_b200 import ops
+    from tybok_b200.pi05 import TWO_PLANE_MIN_TOKENS
 
     s = shape
 
@@ -262,11 +263,19 @@ def _gemm_roofline(shape, batch: int, dev, peaks, peaks_kind, sweep: bool) -> di
             ws = _rotating_weights(nw * n, k, dev)  # the gated form streams gate and up as one interleaved [2N, K] matrix
             nbuf = len(ws)
             sc = torch.rand(nw * n, device=dev)
-            xp = ops.split3(torch.randn(m, k, device=dev).to(torch.bfloat16), 4)
+            x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+            xp = ops.split3(x, 4)
             res = torch.randn(m, n, device=dev).to(torch.bfloat16)
+            # the GEMMs fed by a norm take two e4m3 planes from the model's two-plane threshold on
+            two = m >= TWO_PLANE_MIN_TOKENS and name in ("qkv", "geglu")
+            if two:
+                x2, rs = ops.norm_planes2(x, ops.NORM_RMS, torch.zeros(k, device=dev))
 
             def call(i):
                 w = ws[i % nbuf]
+                if two:
+                    return ops.w8x2_gemm(x2, rs, w, sc, epilogue=ops.EPI_GEGLU_PACKED if nw == 2 else ops.EPI_NONE,
+                                         out_bf16=nw == 1, out_planes=nw == 2)
                 if nw == 2:
                     return ops.w8x3_geglu_packed(xp, 4, w, sc, out_bf16=False, out_planes=True)
                 if name == "qkv":
@@ -275,7 +284,7 @@ def _gemm_roofline(shape, batch: int, dev, peaks, peaks_kind, sweep: bool) -> di
 
             us = _time_graph(call, 2 * nbuf)
             byts = nw * (n * k + 4 * n) + 2 * m * k + 2 * m * n
-            rows.append({"gemm": name, "M": m, "N": n, "K": k, "nw": nw, "us": round(us, 2), "count": count,
+            rows.append({"gemm": name, "M": m, "N": n, "K": k, "nw": nw, "planes": 2 if two else 3, "us": round(us, 2), "count": count,
                          "GBps": round(byts / us / 1e3, 1), "TFps": round(2.0 * nw * m * n * k / us / 1e6, 1),
                          "bytes": byts, "flops": 2.0 * nw * m * n * k})
             del ws
@@ -322,10 +331,16 @@ def _w8_sweep(dev, peaks) -> list[dict]:
             xp = ops.split3(x, 4)
             us = _time_graph(lambda i: ops.w8x3_linear(xp, 4, ws[i % nbuf], sc), 2 * nbuf)
             us2 = _time_graph(lambda i: ops.w8a16_linear(x, ws[i % nbuf], sc), 2 * nbuf)
+            us_two = None
+            if m >= 128:  # the two-plane form a norm kernel can feed (per-row power-of-two scale)
+                x2, rs = ops.norm_planes2(x, ops.NORM_RMS, torch.zeros(k, device=dev))
+                us_two = _time_graph(lambda i: ops.w8x2_gemm(x2, rs, ws[i % nbuf], sc), 2 * nbuf)
             byts = n * k + 4 * n + 2 * m * k + 2 * m * n
             flops = 2.0 * m * n * k
             t_hbm, t_tc = byts / peaks["hbm_gbs"] / 1e3, flops / peaks["bf16_tflops"] / 1e6  # us
             rows.append({"N": n, "K": k, "M": m, "us": round(us, 2), "us_bf16_in": round(us2, 2),
+                         "us_two_plane": None if us_two is None else round(us_two, 2),
+                         "frac_tensor_two_plane": None if us_two is None else round(t_tc / us_two, 4),
                          "GBps": round(byts / us / 1e3, 1), "TFps": round(flops / us / 1e6, 1),
                          "frac_hbm": round(t_hbm / us, 4), "frac_tensor": round(t_tc / us, 4),
                          "binds": "hbm" if t_hbm >= t_tc else "tensor", "frac_of_binding": round(max(t_hbm, t_tc) / us, 4)})
@@ -552,7 +567,7 @@ def run_ours(args, rank: int, world: int) -> None:
         line = {
             "metric": METRIC, "value": round(p50, 4), "unit": "ms", "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": round(total_ms / args.steps, 4), "higher_is_better": False,
-            "scaling": "weak", "vs_baseline": None, "dtype": DTYPE + " (activations as 3 exact e5m2 planes)",
+            "scaling": "weak", "vs_baseline": None, "dtype": DTYPE + " (activations as 3 exact e5m2 planes; norm-fed GEMMs of 128+ tokens: 2 e4m3 planes with a per-row power-of-two scale)",
             "data": "synthetic", "config": _config(args.batch, world),
             "run": {"cuda_graph": True, "overlap_step0": not args.no_overlap, "vision_tower": args.vision_precision,
                     "adarms_folded": adarms_folded},
@@ -825,7 +840,7 @@ def run_dit(args, rank: int, world: int) -> None:
         print(json.dumps({
             "metric": DIT_METRIC, "value": round(ms, 3), "unit": "ms", "n_gpus": world, "steps": steps,
             "warmup": max(1, min(args.warmup, 3)), "ms_per_step": round(ms, 3), "higher_is_better": False,
-            "scaling": "strong", "vs_baseline": None, "dtype": DTYPE + " (activations as 3 exact e5m2 planes), bf16 attention",
+            "scaling": "strong", "vs_baseline": None, "dtype": DTYPE + " (norm-fed GEMMs: 2 e4m3 planes with a per-row power-of-two scale, others 3 exact e5m2 planes), bf16 attention",
             "data": "synthetic", "config": {"workload": DIT_WORKLOAD, "tensor_parallel_ffn": world},
             "run": {"cuda_graph": False, "l2": "4.3 GB of e4m3 weights per step exceed the 126 MB L2"},
             "clocks": clocks, "gpu_launches": launches_per_pass * steps,
