@@ -379,6 +379,65 @@ def run_reference(args, rank: int) -> None:
     print(json.dumps(line), flush=True)
 
 
+def _phases(engine) -> dict:
+    """Where a chunk's time goes: the three phases of ``sample_actions`` (vision tower + projector,
+    prefix pass, the denoise passes) each captured as its own CUDA graph on the engine's static
+    inputs and timed with CUDA events (median of 10 replays); the expert passes also with every AdaRMS
+    norm as its own kernel, for the effect of folding them into the GEMMs."""
+    from tybok_b200 import ops
+
+    m = engine.model
+    s = m.shape
+    st = engine._static
+
+    def timed(fn):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            out = fn()
+        g.replay()
+        ts = []
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return round(statistics.median(ts), 4), out
+
+    with torch.no_grad():
+        out = {}
+        out["tower_projector_ms"], (embs, pad) = timed(lambda: m.embed_prefix(st["images"], st["img_masks"], st["tokens"], st["masks"]))
+        out["prefix_ms"], _ = timed(lambda: m.prefill(embs, pad))
+        b, l = st["noise"].shape[0], st["noise"].shape[1]
+        key_valid, pos = m._suffix_constants(pad, b, l)
+        x_t = st["noise"].float().contiguous().clone()
+        dt = -1.0 / s.steps
+
+        def expert():
+            h = ops.action_tail(None, None, None, None, x_t, dt, *m.action_in)
+            for step in range(s.steps):
+                x = m._expert_layers(step, h, b, l, pad, key_valid, pos)
+                h = ops.action_tail(x, m.final_mods[step], *m.action_out, x_t, dt, *m.action_in, rows_per_group=b * l,
+                                    embed=step + 1 < s.steps)
+            return x_t
+
+        out["expert_passes_ms"], _ = timed(expert)
+        out["expert_us_per_layer_step"] = round(out["expert_passes_ms"] * 1e3 / (s.steps * s.expert.depth), 2)
+        if m.fold is not None:
+            fold, m.fold = m.fold, None
+            try:
+                out["expert_passes_norm_kernels_ms"], _ = timed(expert)
+            finally:
+                m.fold = fold
+    return out
+
+
 def _batch_sweep(rank: int, local: int, overlap: bool, vision: str, batches=(8, 32, 64)) -> list[dict]:
     """Batched throughput of one replica: ``b`` requests per graph replay (the data-parallel serving
     configuration at batch {8, 32, 64} per GPU); chunks/s from 5 event-timed replays."""
@@ -541,6 +600,8 @@ def run_ours(args, rank: int, world: int) -> None:
             gpu_chunk = torch.from_numpy(got).reshape(args.batch, s.chunk, -1)
         roof = _gemm_roofline(s, args.batch, torch.device("cuda", local), peaks, peaks_kind,
                               sweep=world == 1 and not args.no_extras)
+        if world == 1 and args.batch == 1 and not args.no_extras:
+            extra["phases"] = _phases(engine)
         ops.check_status()
         del engine, graph
         torch.cuda.empty_cache()
