@@ -787,18 +787,23 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
 // ------------------------------------------------------------------------------ prefill form
 // Long query sequences (more than one query tile): one CTA per (query tile, head, batch) walks
-// over the keys in blocks of 64 and keeps the running output in tensor memory, so nothing is
-// exchanged between CTAs.  Warp 0 streams K and V blocks through two-deep rings, warp 1 issues
-// S_j = Q K_j^T one block ahead and O += P_j V_j, warps 2..5 hold one query row per thread:
-// block maximum, P_j = exp2(s * c - m) as bf16 over the S_j columns, row sum.  The reference
+// over the keys in blocks (64 keys at head_dim 256, 128 at head_dim 128) and keeps the running
+// output in tensor memory, so nothing is exchanged between CTAs.  Warp 0 streams K and V blocks
+// through two-deep rings, warp 1 issues S_j = Q K_j^T one block ahead and O += P_j V_j, warps 2..9
+// hold two threads per query row (half of a block's keys each): block maximum,
+// P_j = exp2(s * c - m) as bf16 over the S_j columns, row sum.  The reference
 // maximum m of a row only moves when the block maximum exceeds it by more than 2^8 (P stays
 // below 256, exact enough in bf16 and fp32); then the thread rescales its O row and its sum.
 // All eight epilogue warps normalise and write the output at the end.
-constexpr int PF_BK = 64;                    // keys per block
-constexpr int PF_KCHUNK = PF_BK * 128;       // one 64-column chunk of a K or V block
+// Keys per block: 64 at head_dim 256 (two K and two V blocks of 32 KB each beside the Q tile), 128 at
+// head_dim 128, where the same shared memory holds blocks twice as long: every block pays one chain of
+// tensor-memory round trips and one named barrier whatever its length, and at 64 keys that chain,
+// not the special-function unit, set the pace of the DiT self-attention (65 blocks per CTA).
+__host__ __device__ constexpr int pf_bk(int d) { return d == 128 ? 128 : 64; }
+__host__ __device__ constexpr int pf_kchunk(int d) { return pf_bk(d) * 128; }  // one 64-column chunk of a K or V block
 constexpr int PF_MAX_KEYS = 8192;
 // Shared memory of the key-loop kernel: the Q tile and two K and two V blocks, D / 64 chunks each.
-constexpr int pf_smem(int d) { return (d / 64) * (AT_CHUNK + 4 * PF_KCHUNK) + 1024; }
+constexpr int pf_smem(int d) { return (d / 64) * (AT_CHUNK + 4 * pf_kchunk(d)) + 1024; }
 constexpr float PF_RESCALE = 8.0f;
 // 2^x by the special-function unit alone (results below 2^-126 flush to zero).
 __device__ __forceinline__ float pf_exp2(float x) {
@@ -839,9 +844,12 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
   constexpr int KID = HD == 256 ? 5 : 6;
   if (tid == 0) dbg_stage(p.dbg, KID, 0);
   constexpr int NCH = HD / 64;              // 64-column chunks of a Q, K or V row
-  constexpr int PF_KV = NCH * PF_KCHUNK;    // one K or V block: 64 keys x HD
+  constexpr int PF_BK = pf_bk(HD);          // keys per block
+  constexpr int PF_KCHUNK = pf_kchunk(HD);
+  constexpr int PF_KV = NCH * PF_KCHUNK;    // one K or V block: PF_BK keys x HD
+  constexpr int KW = PF_BK / 64;            // 32-key words per thread and block (two threads per query row)
   constexpr int Q_TILE = NCH * AT_CHUNK;    // 128 query rows x HD
-  constexpr int T_COLS = 512;               // tensor memory: S / P at columns 0 and 64, O behind them
+  constexpr int T_COLS = 512;               // tensor memory: S / P at columns 0 and PF_BK, O from column 256
   constexpr int OCH = HD / 64;              // 32-column chunks of O per thread (its half of the row)
   uint8_t* sq = smem;
   uint8_t* sk = smem + Q_TILE;               // two K blocks
@@ -877,7 +885,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
   }
   if (warp >= 2 && warp < 6) {  // validity bits of every key, 32 per word
     if (p.key_valid && p.pdl) pdl_wait();
-    for (int w = warp - 2; w < 2 * nkb; w += 4) {
+    for (int w = warp - 2; w < (PF_BK / 32) * nkb; w += 4) {
       const int j = w * 32 + lane;
       bool ok = j < p.Lk;
       if (ok && p.key_valid) ok = p.key_valid[static_cast<long long>(b) * p.Lk + j] != 0;
@@ -889,7 +897,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bars.tmem_base;
-  const uint32_t t_o = tmem + (HD == 256 ? 256 : 128);  // S_j (and P_j over it) at columns 64 * (j & 1)
+  const uint32_t t_o = tmem + 256;  // S_j (and P_j over it) at columns PF_BK * (j & 1)
   if (tid == 0) dbg_stage(p.dbg, KID, 1);
   long long* tr = p.trace ? p.trace + 16ll * ((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) : nullptr;
   const long long t_start = clock64();
@@ -921,7 +929,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
     const uint32_t idesc_o = idesc_bf16_f32(AT_BQ, HD) | (1u << 16);
     const uint32_t q16 = (smem_u32(sq) & 0x3FFFFu) >> 4;
     bool ok = __all_sync(0xffffffffu, at_wait(&bars.q_full, 0, &bars.abort));
-    auto issue_s = [&](int j) {  // S_j = Q K_j^T into columns 64 * (j & 1); frees the K slot when done
+    auto issue_s = [&](int j) {  // S_j = Q K_j^T into columns PF_BK * (j & 1); frees the K slot when done
       const int s = j & 1;
       ok = ok && __all_sync(0xffffffffu, at_wait(&bars.k_full[s], (j >> 1) & 1, &bars.abort));
       if (!ok) return;
@@ -930,7 +938,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
 #pragma unroll
       for (int ks = 0; ks < HD / 16; ++ks) {  // the head dimension in steps of 16: chunk ks / 4, 32 bytes per step
         const uint32_t qo = (ks >> 2) * (AT_CHUNK >> 4) + (ks & 3) * 2, ko = (ks >> 2) * (PF_KCHUNK >> 4) + (ks & 3) * 2;
-        if (leader) umma_ss_bf16(tmem + s * 64, dk | (q16 + qo), dk | (k16 + ko), idesc_s, ks > 0 ? 1u : 0u);
+        if (leader) umma_ss_bf16(tmem + s * PF_BK, dk | (q16 + qo), dk | (k16 + ko), idesc_s, ks > 0 ? 1u : 0u);
       }
       if (leader) {
         tc_commit(&bars.k_empty[s]);
@@ -951,7 +959,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
 #pragma unroll
       for (int ks = 0; ks < PF_BK / 16; ++ks) {  // 16 keys per step: 16 rows x 128 bytes inside every chunk
         const uint64_t bd = smem_desc_sw128_mn(v_addr + ks * 2048, PF_KCHUNK);
-        if (leader) umma_ts_bf16(t_o, tmem + s * 64 + ks * 8, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+        if (leader) umma_ts_bf16(t_o, tmem + s * PF_BK + ks * 8, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
       }
       if (leader) {
         tc_commit(&bars.v_empty[s]);
@@ -977,7 +985,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
   else {
     // -------------------------------------------------------------- softmax: two threads per query row
     const int q = warp & 3;          // tensor-memory lane quadrant of this warp
-    const int hf = (warp - 2) >> 2;  // which 32 keys of a block / which 128 output columns
+    const int hf = (warp - 2) >> 2;  // which half of a block's keys / which half of the output columns
     const int row = q * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     const bool live = q * 32 < nvalid;  // warp-uniform: this quadrant holds real query rows
@@ -993,20 +1001,26 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
         bars.abort = 1;
       }
       if (tr && tid == 128 && j < 6) tr[1 + 2 * j] = clock64();
-      uint32_t v[32];
-      const uint32_t bits = bars.valid[2 * j + hf];
+      uint32_t v[KW][32];
+      uint32_t bits[KW];
+#pragma unroll
+      for (int w = 0; w < KW; ++w) bits[w] = bars.valid[(2 * j + hf) * KW + w];
       float mx = -1e30f;
       if (ok && live) {
         tc_fence_after();
-        tmem_ld32(tmem + lane_addr + s * 64 + hf * 32, v);
+#pragma unroll
+        for (int w = 0; w < KW; ++w) tmem_ld32(tmem + lane_addr + s * PF_BK + (hf * KW + w) * 32, v[w]);
         tc_wait_ld();
-        if (bits == 0xffffffffu) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
-        } else if (bits != 0u) {
+        for (int w = 0; w < KW; ++w) {
+          if (bits[w] == 0xffffffffu) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if ((bits >> e) & 1u) mx = fmaxf(mx, __uint_as_float(v[e]));
+            for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[w][e]));
+          } else if (bits[w] != 0u) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if ((bits[w] >> e) & 1u) mx = fmaxf(mx, __uint_as_float(v[w][e]));
+          }
         }
       }
       bars.hmax[s][hf][row] = mx;
@@ -1046,32 +1060,37 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
         }
       }
       if (ok && live) {
-        uint32_t pk[16];
         float sum = 0.f;
-        if (bits == 0xffffffffu) {
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const float p0 = pf_exp2(__uint_as_float(v[e]) * p.scale_log2e - m_ref);
-            const float p1 = pf_exp2(__uint_as_float(v[e + 1]) * p.scale_log2e - m_ref);
-            sum += p0 + p1;
-            const __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
-            pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&pp);
+        for (int w = 0; w < KW; ++w) {
+          uint32_t pk[16];
+          if (bits[w] == 0xffffffffu) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+              const float p0 = pf_exp2(__uint_as_float(v[w][e]) * p.scale_log2e - m_ref);
+              const float p1 = pf_exp2(__uint_as_float(v[w][e + 1]) * p.scale_log2e - m_ref);
+              sum += p0 + p1;
+              const __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
+              pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&pp);
+            }
+          } else if (bits[w] == 0u) {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) pk[e] = 0u;
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+              const float p0 = ((bits[w] >> e) & 1u) ? pf_exp2(__uint_as_float(v[w][e]) * p.scale_log2e - m_ref) : 0.f;
+              const float p1 = ((bits[w] >> (e + 1)) & 1u) ? pf_exp2(__uint_as_float(v[w][e + 1]) * p.scale_log2e - m_ref) : 0.f;
+              sum += p0 + p1;
+              const __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
+              pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&pp);
+            }
           }
-        } else if (bits == 0u) {
-#pragma unroll
-          for (int e = 0; e < 16; ++e) pk[e] = 0u;
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const float p0 = ((bits >> e) & 1u) ? pf_exp2(__uint_as_float(v[e]) * p.scale_log2e - m_ref) : 0.f;
-            const float p1 = ((bits >> (e + 1)) & 1u) ? pf_exp2(__uint_as_float(v[e + 1]) * p.scale_log2e - m_ref) : 0.f;
-            sum += p0 + p1;
-            const __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
-            pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&pp);
-          }
+          // P_j as bf16 pairs over the start of S_j: 16 columns per 32 keys (every thread of the row
+          // has read its scores before the named barrier above)
+          tmem_st16(tmem + lane_addr + s * PF_BK + (hf * KW + w) * 16, pk);
         }
         l += sum;
-        tmem_st16(tmem + lane_addr + s * 64 + hf * 16, pk);  // P_j: 32 columns over the start of S_j
         tc_wait_st();
       }
       tc_fence_before();
@@ -1282,7 +1301,7 @@ int tybok_attention(const void* q, const void* k_cache, const void* v_cache, con
   if (int rc = host::tensor_map_2d(&tm_q, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, hd, static_cast<uint64_t>(B) * L, hd * 2, 64, q_rows))
     return rc;
   const uint64_t krows = static_cast<uint64_t>(B) * G * Lcap;
-  const int kbox = prefill ? PF_BK : AT_BK;
+  const int kbox = prefill ? pf_bk(D) : AT_BK;
   if (int rc = host::tensor_map_2d(&tm_k, k_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, krows, D * 2, 64, kbox)) return rc;
   if (int rc = host::tensor_map_2d(&tm_v, v_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, krows, D * 2, 64, kbox)) return rc;
 
