@@ -332,7 +332,7 @@ def _w8_sweep(dev, peaks) -> list[dict]:
             us = _time_graph(lambda i: ops.w8x3_linear(xp, 4, ws[i % nbuf], sc), 2 * nbuf)
             us2 = _time_graph(lambda i: ops.w8a16_linear(x, ws[i % nbuf], sc), 2 * nbuf)
             us_two = None
-            if m >= 128:  # the two-plane form a norm kernel can feed (per-row power-of-two scale)
+            if m >= 128 and k <= 4096:  # the two-plane form a norm kernel (rows of up to 4096 channels) can feed
                 x2, rs = ops.norm_planes2(x, ops.NORM_RMS, torch.zeros(k, device=dev))
                 us_two = _time_graph(lambda i: ops.w8x2_gemm(x2, rs, ws[i % nbuf], sc), 2 * nbuf)
             byts = n * k + 4 * n + 2 * m * k + 2 * m * n
