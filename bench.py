@@ -594,7 +594,7 @@ def run_ours(args, rank: int, world: int) -> None:
         # parity of the timed engine: a zero-noise request against the CPU oracle (computed below)
         zero = torch.zeros(args.batch, s.chunk, s.max_action_dim)
         gpu_chunk = None
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:  # the CPU leg (and with it the parity field) runs at N = 1 only
             got = engine.predict_action_chunk(frames[0][0], noise=zero) if args.batch == 1 else \
                 engine.predict_action_chunks(frames[0], noise=zero)
             gpu_chunk = torch.from_numpy(got).reshape(args.batch, s.chunk, -1)
@@ -608,7 +608,7 @@ def run_ours(args, rank: int, world: int) -> None:
         if world == 1 and args.batch == 1 and not args.no_extras:
             extra["batch_sweep"] = _batch_sweep(rank, local, not args.no_overlap, args.vision_precision)
         cpu = parity = None
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:  # the CPU leg (and with it the parity field) runs at N = 1 only
             cores = _all_host_threads()
             deq = _oracle_weights(seed=rank, device="cuda")
             unpinned = [[{k: (v.clone() if isinstance(v, torch.Tensor) else v) for k, v in fr.items()} for fr in fl]
@@ -822,7 +822,7 @@ def run_dit(args, rank: int, world: int) -> None:
     bp0 = None
     for i in range(S.blocks):  # the same seeded weights on every rank; bf16 masters are dropped block by block
         bp = quantize_dit_block(random_dit_block_params(S, seed=i, device=dev))
-        if i == 0 and rank == 0 and not args.no_cpu_baseline:
+        if i == 0 and rank == 0 and world == 1 and not args.no_cpu_baseline:  # CPU leg at N = 1 only
             bp0 = {k: v.cpu() for k, v in bp.items()}
         den.blocks.append(DiTBlock(bp, S, device=dev, rank=rank, world=world))
         del bp
