@@ -480,6 +480,8 @@ def _batch_sweep(rank: int, local: int, overlap: bool, vision: str, batches=(8, 
         ms = statistics.median(a.elapsed_time(c) for a, c in evs)
         rows.append({"batch": b, "ms_per_batch": round(ms, 3), "chunks_per_s": round(b / ms * 1e3, 1),
                      "ms_per_chunk": round(ms / b, 3)})
+        if b == 32:  # where a batched chunk's time goes (tower / prefix / expert passes as separate graphs)
+            rows[-1]["phases"] = {k: v for k, v in _phases(eng).items() if k.endswith("_ms")}
         del eng
         torch.cuda.empty_cache()
     return rows
