@@ -192,6 +192,10 @@ int tybok_add_layernorm(const void* x, const void* y, const void* weight, const 
  * (W % 8 == 0, W <= 2048).  A bf16 tower run this way never rounds its stream to bf16. */
 int tybok_add_layernorm_mixed(const float* x, const void* y, const void* weight, const void* bias, int M, int W, float eps,
                               float* x_out, void* h, void* stream);
+/* The mixed form with y / weight / bias / h in fp16 instead of bf16, for a tower whose GEMMs and attention
+ * run on fp16 operands (11 significant bits, as TF32, at the speed of bf16). */
+int tybok_add_layernorm_mixed_f16(const float* x, const void* y, const void* weight, const void* bias, int M, int W,
+                                  float eps, float* x_out, void* h, void* stream);
 /* The same in fp32 (all six tensors fp32; W % 4 == 0, W <= 2048), for a tower run in fp32 / TF32. */
 int tybok_add_layernorm_f32(const float* x, const float* y, const float* weight, const float* bias, int M, int W,
                             float eps, float* x_out, float* h, void* stream);

@@ -232,22 +232,22 @@ def test_add_layernorm_kernel():
 
 @pytest.mark.parametrize("m,w", [(512, 1152), (37, 128), (5, 2048)])
 def test_add_layernorm_with_an_fp32_stream(m, w):
-    """The two forms that keep the residual stream in fp32: bf16 sublayer output / weights (a bf16
-    tower) and all-fp32 (a TF32 tower), against torch in fp32."""
+    """The forms that keep the residual stream in fp32: bf16 or fp16 sublayer output / weights (a bf16
+    or fp16 tower) and all-fp32 (a TF32 tower), against torch in fp32."""
     from tybok_b200 import ops
 
     g = torch.Generator().manual_seed(m + w)
     x = torch.empty(m, w).normal_(0, 3, generator=g)
     y = torch.empty(m, w).normal_(0, 1, generator=g)
     wt, b = (1 + torch.empty(w).normal_(0, 0.3, generator=g)), torch.empty(w).normal_(0, 0.3, generator=g)
-    for dt in (torch.bfloat16, torch.float32):
+    for dt in (torch.bfloat16, torch.float16, torch.float32):
         yd, wd, bd = y.to(dt), wt.to(dt), b.to(dt)
         xs = x + yd.float()
         ref = torch.nn.functional.layer_norm(xs, (w,), wd.float(), bd.float(), 1e-6)
         x_new, h = ops.add_layernorm(x.cuda(), yd.cuda(), wd.cuda(), bd.cuda())
         assert x_new.dtype == torch.float32 and h.dtype == dt
         assert torch.equal(x_new.cpu(), xs)
-        tol = 2.0**-7 if dt == torch.bfloat16 else 1e-5
+        tol = {torch.bfloat16: 2.0**-7, torch.float16: 2.0**-10}.get(dt, 1e-5)
         assert float((h.cpu().float() - ref).abs().max()) <= tol * max(1.0, float(ref.abs().max()))
         _, h0 = ops.add_layernorm(xs.cuda(), None, wd.cuda(), bd.cuda())
         assert torch.equal(h0, h)

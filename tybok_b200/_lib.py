@@ -59,6 +59,8 @@ SIGNATURES = {
                                     c_void_p, c_void_p]),
     "tybok_add_layernorm_mixed": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, ctypes.c_float, c_void_p,
                                           c_void_p, c_void_p]),
+    "tybok_add_layernorm_mixed_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, ctypes.c_float, c_void_p,
+                                          c_void_p, c_void_p]),
     "tybok_add_layernorm_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, ctypes.c_float, c_void_p,
                                         c_void_p, c_void_p]),
     "tybok_layernorm_affine": (c_int, [c_void_p, c_i64, c_void_p, c_void_p, c_int, c_int, ctypes.c_float, c_void_p,

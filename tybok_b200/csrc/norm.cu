@@ -8,6 +8,7 @@
 // ([groups, 3*W] or [groups, 2*W], fp32), one row per group of `rows_per_group` tokens.
 // Algorithmic bytes per row: 2*W read, 3*W (+2*W) written.
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include "../../include/tybok_b200.h"
@@ -489,18 +490,31 @@ __global__ void __launch_bounds__(256) add_layernorm_row_kernel(const AddLnParam
 // output y, weight, bias and the normalised h bf16.  The stream is then never rounded to bf16
 // (only the GEMM inputs are), which is where a bf16 tower loses most of its accuracy: the stream is
 // several times larger than what a sublayer adds to it.  One CTA per row, eight elements per thread.
+// T16 = __nv_bfloat16 or __half: the 16-bit type of the sublayer output, the norm's weight / bias and h.
+template <typename T16>
 struct AddLnMixedParams {
   const float* x;
-  const __nv_bfloat16* y;  // or NULL
-  const __nv_bfloat16* w;
-  const __nv_bfloat16* b;
-  float* x_out;            // or NULL
-  __nv_bfloat16* h;
+  const T16* y;  // or NULL
+  const T16* w;
+  const T16* b;
+  float* x_out;  // or NULL
+  T16* h;
   int M, W;
   float eps;
 };
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+__device__ __forceinline__ uint32_t pack2(float a, float b, __nv_bfloat16) {
+  const __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&t);
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b, __half) {
+  const __half2 t = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&t);
+}
 
-__global__ void __launch_bounds__(256) add_layernorm_mixed_kernel(const AddLnMixedParams p) {
+template <typename T16>
+__global__ void __launch_bounds__(256) add_layernorm_mixed_kernel(const AddLnMixedParams<T16> p) {
   __shared__ float red[2][8];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int c = threadIdx.x * 8;
@@ -517,9 +531,9 @@ __global__ void __launch_bounds__(256) add_layernorm_mixed_kernel(const AddLnMix
     v[0] = a0.x; v[1] = a0.y; v[2] = a0.z; v[3] = a0.w; v[4] = a1.x; v[5] = a1.y; v[6] = a1.z; v[7] = a1.w;
     if (p.y) {
       const uint4 ry = *reinterpret_cast<const uint4*>(p.y + base + c);
-      const __nv_bfloat16* hy = reinterpret_cast<const __nv_bfloat16*>(&ry);
+      const T16* hy = reinterpret_cast<const T16*>(&ry);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) v[e] += __bfloat162float(hy[e]);
+      for (int e = 0; e < 8; ++e) v[e] += to_f32(hy[e]);
       if (p.x_out) {
         *reinterpret_cast<float4*>(p.x_out + base + c) = make_float4(v[0], v[1], v[2], v[3]);
         *reinterpret_cast<float4*>(p.x_out + base + c + 4) = make_float4(v[4], v[5], v[6], v[7]);
@@ -551,13 +565,13 @@ __global__ void __launch_bounds__(256) add_layernorm_mixed_kernel(const AddLnMix
   for (int w = 0; w < nwarps; ++w) tot += red[1][w];
   const float rstd = rsqrtf(tot / static_cast<float>(p.W) + p.eps);
   if (live) {
-    const __nv_bfloat16* pw = reinterpret_cast<const __nv_bfloat16*>(&rw);
-    const __nv_bfloat16* pb = reinterpret_cast<const __nv_bfloat16*>(&rb);
-    __nv_bfloat162 o[4];
+    const T16* pw = reinterpret_cast<const T16*>(&rw);
+    const T16* pb = reinterpret_cast<const T16*>(&rb);
+    uint32_t o[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e)
-      o[e] = __floats2bfloat162_rn(v[2 * e] * rstd * __bfloat162float(pw[2 * e]) + __bfloat162float(pb[2 * e]),
-                                   v[2 * e + 1] * rstd * __bfloat162float(pw[2 * e + 1]) + __bfloat162float(pb[2 * e + 1]));
+      o[e] = pack2(v[2 * e] * rstd * to_f32(pw[2 * e]) + to_f32(pb[2 * e]),
+                   v[2 * e + 1] * rstd * to_f32(pw[2 * e + 1]) + to_f32(pb[2 * e + 1]), T16());
     *reinterpret_cast<uint4*>(p.h + base + c) = *reinterpret_cast<const uint4*>(o);
   }
 }
@@ -721,8 +735,8 @@ int tybok_add_layernorm(const void* x, const void* y, const void* weight, const 
   return TYBOK_OK;
 }
 
-int tybok_add_layernorm_mixed(const float* x, const void* y, const void* weight, const void* bias, int M, int W, float eps,
-                              float* x_out, void* h, void* stream) {
+static int launch_add_layernorm_mixed(const float* x, const void* y, const void* weight, const void* bias, int M, int W,
+                                      float eps, float* x_out, void* h, void* stream, bool half) {
   using namespace tb;
   if (!x || !weight || !bias || !h) return host::fail(TYBOK_ERR_ARG, "add_layernorm_mixed: null pointer argument");
   if (M <= 0 || W <= 0 || W % 8 != 0 || W > 2048) return host::fail(TYBOK_ERR_ARG, "add_layernorm_mixed: W must be a multiple of 8 and <= 2048");
@@ -730,12 +744,29 @@ int tybok_add_layernorm_mixed(const float* x, const void* y, const void* weight,
        reinterpret_cast<uintptr_t>(bias) | reinterpret_cast<uintptr_t>(x_out) | reinterpret_cast<uintptr_t>(h)) & 15)
     return host::fail(TYBOK_ERR_ARG, "add_layernorm_mixed: tensors must be 16-byte aligned");
   if (int rc = host::require_sm100()) return rc;
-  AddLnMixedParams p{x, static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(weight),
-                     static_cast<const __nv_bfloat16*>(bias), x_out, static_cast<__nv_bfloat16*>(h), M, W, eps};
-  add_layernorm_mixed_kernel<<<M, ((W / 8) + 31) / 32 * 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  const int threads = ((W / 8) + 31) / 32 * 32;
+  if (half) {
+    AddLnMixedParams<__half> p{x, static_cast<const __half*>(y), static_cast<const __half*>(weight),
+                               static_cast<const __half*>(bias), x_out, static_cast<__half*>(h), M, W, eps};
+    add_layernorm_mixed_kernel<__half><<<M, threads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  } else {
+    AddLnMixedParams<__nv_bfloat16> p{x, static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(weight),
+                                      static_cast<const __nv_bfloat16*>(bias), x_out, static_cast<__nv_bfloat16*>(h), M, W, eps};
+    add_layernorm_mixed_kernel<__nv_bfloat16><<<M, threads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  }
   if (cudaGetLastError() != cudaSuccess) return host::fail_cuda("launch add_layernorm_mixed_kernel");
   host::count_launch();
   return TYBOK_OK;
+}
+
+int tybok_add_layernorm_mixed(const float* x, const void* y, const void* weight, const void* bias, int M, int W, float eps,
+                              float* x_out, void* h, void* stream) {
+  return launch_add_layernorm_mixed(x, y, weight, bias, M, W, eps, x_out, h, stream, false);
+}
+
+int tybok_add_layernorm_mixed_f16(const float* x, const void* y, const void* weight, const void* bias, int M, int W,
+                                  float eps, float* x_out, void* h, void* stream) {
+  return launch_add_layernorm_mixed(x, y, weight, bias, M, W, eps, x_out, h, stream, true);
 }
 
 int tybok_add_layernorm_f32(const float* x, const float* y, const float* weight, const float* bias, int M, int W,

@@ -175,10 +175,10 @@ class PI05B200Engine(PolicyEngine):
         # SigLIP tower (not an fp8 module in the reference, which runs it in fp32): "tf32" = fp32
         # activations with TF32 tensor-core GEMMs, "bf16" = all bf16 (0.5 ms faster per chunk, ten
         # times the embedding error), "fp32" = plain fp32.
-        if vision_precision not in ("tf32", "bf16", "fp32"):
-            raise ValueError(f"vision_precision {vision_precision!r}: expected 'tf32', 'bf16' or 'fp32'")
+        if vision_precision not in ("tf32", "fp16", "bf16", "fp32"):
+            raise ValueError(f"vision_precision {vision_precision!r}: expected 'tf32', 'fp16', 'bf16' or 'fp32'")
         self.model = PI05Model(params, shape, device=str(self.device), overlap=overlap,
-                               vision_dtype=torch.bfloat16 if vision_precision == "bf16" else torch.float32,
+                               vision_dtype={"bf16": torch.bfloat16, "fp16": torch.float16}.get(vision_precision, torch.float32),
                                vision_tf32=vision_precision == "tf32")
         del params
         self._gen = torch.Generator(device=self.device)

@@ -376,23 +376,25 @@ def _add_layernorm_cuda(x, y, weight, bias, eps):
 
 
 def _add_layernorm_any(x, y, weight, bias, eps):
-    """All bf16, all fp32, or the mixed form (fp32 ``x`` with bf16 ``y`` / ``weight`` / ``bias``)."""
+    """All bf16, all fp32, or the mixed form (fp32 ``x`` with bf16 or fp16 ``y`` / ``weight`` / ``bias``)."""
     if x.dtype != torch.float32:
         return _add_layernorm_cuda(x, y, weight, bias, eps)
     lib = _lib.load()
     w = x.shape[-1]
-    if weight.dtype == torch.bfloat16:
+    if weight.dtype in (torch.bfloat16, torch.float16):
+        t16 = weight.dtype
         for t in (x, y, weight, bias):
             if t is not None and not t.is_contiguous():
                 raise TypeError("add_layernorm: tensors must be contiguous")
-        if (y is not None and (y.shape != x.shape or y.dtype != torch.bfloat16)) or bias.dtype != torch.bfloat16 \
+        if (y is not None and (y.shape != x.shape or y.dtype != t16)) or bias.dtype != t16 \
                 or weight.numel() != w or bias.numel() != w:
-            raise ValueError("add_layernorm (fp32 stream): y / weight / bias must be bf16 with matching shapes")
+            raise ValueError("add_layernorm (fp32 stream): y / weight / bias must share one 16-bit dtype and match in shape")
         m = x.numel() // w
         x_out = torch.empty_like(x) if y is not None else x.new_empty(0)
-        h = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
-        rc = lib.tybok_add_layernorm_mixed(x.data_ptr(), _ptr(y), weight.data_ptr(), bias.data_ptr(), m, w, float(eps),
-                                           x_out.data_ptr() if y is not None else None, h.data_ptr(), _stream(x))
+        h = torch.empty(x.shape, dtype=t16, device=x.device)
+        fn = lib.tybok_add_layernorm_mixed if t16 == torch.bfloat16 else lib.tybok_add_layernorm_mixed_f16
+        rc = fn(x.data_ptr(), _ptr(y), weight.data_ptr(), bias.data_ptr(), m, w, float(eps),
+                x_out.data_ptr() if y is not None else None, h.data_ptr(), _stream(x))
         _lib.check(rc, "tybok_add_layernorm_mixed")
         return x_out, h
     for t in (x, y, weight, bias):

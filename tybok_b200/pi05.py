@@ -120,8 +120,11 @@ class PI05Model:
         #: prefix embeddings then agree with an fp32 tower to ~2e-3 rel-L2 where a bf16 tower is at 1.4e-2
         self.vision_tf32 = bool(vision_tf32) and vision_dtype == torch.float32
         self.vision = {k: v.to(dev, vision_dtype) for k, v in params.items() if k.startswith(VISION)}
-        # the 7-kernel-per-layer form: bf16, or fp32 with TF32 GEMMs; plain fp32 keeps the unfused torch chain
-        self.vis_layers = self._pack_vision() if (vision_dtype == torch.bfloat16 or self.vision_tf32) else None
+        # the 7-kernel-per-layer form: bf16 or fp16 operands, or fp32 with TF32 GEMMs; plain fp32 keeps the
+        # unfused torch chain.  fp16 carries 11 significant bits like TF32 (the tower's weights need them, see
+        # vision_tf32) at the speed of bf16, with the residual stream in fp32 either way; its exponent range
+        # (65504) is the price, so a checkpoint with larger sublayer outputs should run the TF32 form.
+        self.vis_layers = self._pack_vision() if (vision_dtype in (torch.bfloat16, torch.float16) or self.vision_tf32) else None
         self.pos_embed_f32 = params[f"{VISION}.embeddings.position_embedding.weight"].to(dev).float()
         self.proj_w = params[f"{PROJECTOR}.weight"].to(dev, vision_dtype)
         self.proj_b = params[f"{PROJECTOR}.bias"].to(dev, vision_dtype)
@@ -211,8 +214,8 @@ class PI05Model:
     def _embed_image_fused(self, image: torch.Tensor) -> torch.Tensor:
         """The tower with 7 kernels per encoder layer instead of 14: each residual add runs inside
         the LayerNorm kernel that follows it, q/k/v are one GEMM, GELU is the epilogue of fc1 (same
-        layer math as ``embed_image``; vision.py:200-289).  bf16 throughout, or fp32 activations
-        with TF32 GEMMs."""
+        layer math as ``embed_image``; vision.py:200-289).  bf16 or fp16 operands, or fp32 activations
+        with TF32 GEMMs; the residual stream is fp32 in every form."""
         v, p, dt = self.shape.vision, self.vision, self.vision_dtype
         # Patch embedding as a GEMM over flattened patches (the stride == kernel convolution of
         # vision.py; cuDNN runs it as an fp32 direct convolution that takes longer than 20 layers' GEMMs).
@@ -233,7 +236,10 @@ class PI05Model:
             # attention itself always runs on bf16 operands (the flash kernel; an fp32 tower would take
             # a three times slower one): what it rounds is per-token noise that the 256-token averages
             # after it wash out, unlike a rounded weight, which errs the same way for every token
-            qkv = F.linear(h, lay["qkv_w"], lay["qkv_b"]).to(torch.bfloat16).view(b, l, 3, v.heads, hd)
+            qkv = F.linear(h, lay["qkv_w"], lay["qkv_b"])
+            if qkv.dtype == torch.float32:
+                qkv = qkv.to(torch.bfloat16)
+            qkv = qkv.view(b, l, 3, v.heads, hd)
             q, k, val = (qkv[:, :, j].transpose(1, 2) for j in range(3))
             a = F.scaled_dot_product_attention(q, k, val, scale=hd**-0.5).transpose(1, 2).reshape(b, l, hid)
             y = F.linear(a.to(dt), *lay["o"])
