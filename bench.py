@@ -999,8 +999,9 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle leg (and with it the parity field)")
     ap.add_argument("--no-extras", action="store_true", help="skip the W8 sweep, the batch sweep and the tensor-parallel extra")
     ap.add_argument("--no-overlap", action="store_true", help="run the first denoise step after the prefix, not behind it")
-    ap.add_argument("--vision-precision", default="tf32", choices=["tf32", "fp16", "bf16", "fp32"],
-                    help="SigLIP tower: fp32 activations with TF32 GEMMs (default), fp16 or bf16 operands, or plain fp32")
+    ap.add_argument("--vision-precision", default="fp16", choices=["fp16", "tf32", "bf16", "fp32"],
+                    help="SigLIP tower: fp16 operands with an fp32 residual stream (default), fp32 activations with TF32 "
+                         "GEMMs, bf16 operands, or plain fp32")
     ap.add_argument("--workload", default="pi05_chunk", choices=["pi05_chunk", "dit", "dit_ffn", "gemm", "attention"])
     for name, default in (("m", 50), ("n", 16384), ("k", 2048), ("launches", 6), ("tokens", 50), ("prefix", 544),
                           ("head-dim", 256), ("heads", 8)):

@@ -122,7 +122,7 @@ def test_engine_on_a_checkpoint_directory(ckpt):
     # the same weights handed over in memory, inputs prepared by hand
     st, images, tokens, mask = _expected_inputs(frame, stats, path)
     assert int(tokens[0, 0]) == 2 and int(tokens.max()) < 300  # <bos> first, word-level ids: the checkpoint's tokenizer ran
-    model = PI05Model(params, PI05_TINY, device="cuda", vision_dtype=torch.float32, vision_tf32=True)  # the engine's default tower
+    model = PI05Model(params, PI05_TINY, device="cuda", vision_dtype=torch.float16)  # the engine's default tower
     ones = [torch.ones(1, dtype=torch.bool, device="cuda") for _ in images]
     full_noise = torch.zeros(1, PI05_TINY.chunk, PI05_TINY.max_action_dim, device="cuda")
     raw = model.sample_actions([i.cuda() for i in images], ones, tokens.cuda(), mask.cuda(), full_noise)

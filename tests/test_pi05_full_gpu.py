@@ -62,7 +62,7 @@ def test_benchmarked_configuration_matches_oracle(full_oracle_params):
 
     torch.set_num_threads(max(1, len(__import__("os").sched_getaffinity(0))))
     eng = PI05B200Engine("synthetic:pi05_full@0", device="cuda", graph=True, overlap=True, seed=0)
-    assert eng.graph_enabled and eng.model.overlap and eng.model.vision_tf32
+    assert eng.graph_enabled and eng.model.overlap and eng.model.vision_dtype == torch.float16  # the default tower
     frames = _frames(eng, 1, seed=100)
     noise = torch.zeros(1, PI05_FULL.chunk, PI05_FULL.max_action_dim)
     assert eng._predict_chunk_static(frames[0], noise) is not None  # the path bench.py's e2e leg times

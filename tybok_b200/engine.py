@@ -126,7 +126,7 @@ class PI05B200Engine(PolicyEngine):
                  profile: bool = False, overlap: bool = False, action_fused: bool = True, video_fused: bool = True,
                  action_fused_split: bool = True, video_fused_split: bool = True, require_fused: bool = False,
                  camera_alias: dict[str, str] | None = None, tokenizer_dir: str | None = None, batch_size: int = 1,
-                 vision_precision: str = "tf32", **kwargs: Any):
+                 vision_precision: str = "fp16", **kwargs: Any):
         super().__init__(checkpoint_dir, device=device)
         reject_unsupported_flags(type(self), "pi05_b200", kwargs)
         if compile_model:
@@ -172,9 +172,10 @@ class PI05B200Engine(PolicyEngine):
                                    action_dim=action_dim)
         # overlap: the first denoise step runs layer by layer behind the prefix (the reference's
         # --overlap, tybok/policies/pi05/models/flow_matching.py:609-720)
-        # SigLIP tower (not an fp8 module in the reference, which runs it in fp32): "tf32" = fp32
-        # activations with TF32 tensor-core GEMMs, "bf16" = all bf16 (0.5 ms faster per chunk, ten
-        # times the embedding error), "fp32" = plain fp32.
+        # SigLIP tower (not an fp8 module in the reference): "fp16" = fp16 GEMM / attention operands with an
+        # fp32 residual stream (11 significant bits like TF32 at the speed of bf16; sublayer outputs must
+        # stay below 65504), "tf32" = fp32 activations with TF32 tensor-core GEMMs (0.9 ms slower per
+        # chunk, no range limit), "bf16" = bf16 operands (ten times the embedding error), "fp32" = plain fp32.
         if vision_precision not in ("tf32", "fp16", "bf16", "fp32"):
             raise ValueError(f"vision_precision {vision_precision!r}: expected 'tf32', 'fp16', 'bf16' or 'fp32'")
         self.model = PI05Model(params, shape, device=str(self.device), overlap=overlap,
