@@ -131,6 +131,7 @@ int tybok_w8x3_geglu(const void* x_planes, int x_shift, const void* w8_gate, con
  *   TYBOK_NORM_ADARMS       a = fp32 mod [groups, ldmod], rows_per_group (tybok_rmsnorm, mod form)
  *   TYBOK_NORM_LN_MODULATE  a = bf16 shift [W], b = bf16 scale [W]    (tybok_layernorm_modulate)
  *   TYBOK_NORM_LN_AFFINE    a = bf16 weight [W], b = bf16 bias [W]    (tybok_layernorm_affine)
+ * (W a multiple of 8, at most 4096, as for the norms themselves; x bf16 with row stride ldx).
  * tybok_w8x2_gemm is tybok_w8x3_linear on that form (epilogue TYBOK_EPI_* or
  * TYBOK_EPI_GEGLU_PACKED: N = 2*I packed gate/up rows in, I columns out, as
  * tybok_w8x3_geglu_packed); tybok_w8x2_qkv_rope is tybok_w8x3_qkv_rope on it.  Outputs are as in

@@ -125,6 +125,11 @@ def _check_w8(w8: torch.Tensor, what: str) -> None:
         raise TypeError(f"{what}: weight must be a contiguous e4m3 (or raw uint8) [N, K] tensor")
 
 
+def _check_scale(scale: torch.Tensor, rows: int, what: str) -> None:
+    if scale.dtype != torch.float32 or scale.numel() != rows or not scale.is_contiguous():
+        raise TypeError(f"{what}: scale must be contiguous fp32 [{rows}] (one per weight row)")
+
+
 def _split3_cuda(x: torch.Tensor, shift: int) -> torch.Tensor:
     lib = _lib.load()
     if x.dtype != torch.bfloat16:
@@ -151,9 +156,8 @@ def _w8x3_linear_cuda(planes, shift, w8, scale, bias, epilogue, residual, gate, 
     _check_w8(w8, "w8x3_linear")
     if planes.dtype != torch.uint8 or planes.dim() != 3 or planes.shape[0] != 3 or not planes.is_contiguous():
         raise TypeError("w8x3_linear: planes must be a contiguous uint8 [3, M, K] tensor")
-    if scale.dtype != torch.float32:
-        raise TypeError("w8x3_linear: scale must be fp32")
     n, k = w8.shape
+    _check_scale(scale, n, "w8x3_linear")
     m = planes.shape[1]
     if planes.shape[2] != k:
         raise ValueError(f"w8x3_linear: planes have K={planes.shape[2]}, weight has K={k}")
@@ -640,6 +644,7 @@ def _w8x2_gemm_cuda(planes, row_scale, w8, scale, bias, epilogue, residual, gate
     lib = _lib.load()
     _check_w8(w8, "w8x2_gemm")
     n, k = w8.shape
+    _check_scale(scale, n, "w8x2_gemm")
     _check_planes2(planes, row_scale, k, "w8x2_gemm")
     m = planes.shape[1]
     n_out = n // 2 if epilogue == EPI_GEGLU_PACKED else n
@@ -671,6 +676,7 @@ def _w8x2_qkv_rope_cuda(planes, row_scale, w8_paired, scale_paired, pos, cos, si
     b, g, lcap, d = k_cache.shape
     m, k = planes.shape[1], planes.shape[2]
     _check_planes2(planes, row_scale, w8_paired.shape[1], "w8x2_qkv_rope")
+    _check_scale(scale_paired, w8_paired.shape[0], "w8x2_qkv_rope")
     if w8_paired.shape != ((heads + 2 * g) * d, k) or scale_paired.numel() != w8_paired.shape[0] or d % 128 != 0:
         raise ValueError("w8x2_qkv_rope: weight must be [(H+2G)*D, K] with head_dim % 128 == 0")
     if pos.dtype != torch.int32 or pos.numel() != m or not pos.is_contiguous() or m % b != 0:
@@ -732,8 +738,10 @@ def _w8x3_residual_next_adarms_cuda(planes, shift, w8, scale, residual, gate, ne
     lib = _lib.load()
     _check_w8(w8, "w8x3_residual_next_adarms")
     n, k = w8.shape
-    if planes.dtype != torch.uint8 or planes.dim() != 3 or planes.shape[0] != 3 or planes.shape[2] != k:
-        raise TypeError("w8x3_residual_next_adarms: planes must be uint8 [3, M, K]")
+    _check_scale(scale, n, "w8x3_residual_next_adarms")
+    if planes.dtype != torch.uint8 or planes.dim() != 3 or planes.shape[0] != 3 or planes.shape[2] != k \
+            or not planes.is_contiguous():
+        raise TypeError("w8x3_residual_next_adarms: planes must be contiguous uint8 [3, M, K]")
     m = planes.shape[1]
     res2 = _rows(residual)
     if res2.shape != (m, n) or res2.dtype != torch.bfloat16 or n % 128 != 0:
@@ -757,6 +765,7 @@ def _w8x3_geglu_packed_adarms_cuda(u_planes, shift, ss_part, eps, bias_rows, w8_
     lib = _lib.load()
     _check_w8(w8_packed, "w8x3_geglu_packed_adarms")
     n2, k = w8_packed.shape
+    _check_scale(scale_packed, n2, "w8x3_geglu_packed_adarms")
     _check_fold_in(u_planes, ss_part, bias_rows, n2, "w8x3_geglu_packed_adarms")
     if u_planes.shape[2] != k:
         raise ValueError("w8x3_geglu_packed_adarms: planes and weight disagree on K")
@@ -777,6 +786,7 @@ def _w8x3_qkv_rope_adarms_cuda(u_planes, shift, ss_part, eps, bias_rows, w8_pair
     _check_w8(w8_paired, "w8x3_qkv_rope_adarms")
     b, g, lcap, d = k_cache.shape
     _check_fold_in(u_planes, ss_part, bias_rows, w8_paired.shape[0], "w8x3_qkv_rope_adarms")
+    _check_scale(scale_paired, w8_paired.shape[0], "w8x3_qkv_rope_adarms")
     m, k = u_planes.shape[1], u_planes.shape[2]
     if w8_paired.shape != ((heads + 2 * g) * d, k) or scale_paired.numel() != w8_paired.shape[0] or d % 128 != 0:
         raise ValueError("w8x3_qkv_rope_adarms: weight must be [(H+2G)*D, K] with head_dim % 128 == 0")
