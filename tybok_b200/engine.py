@@ -442,8 +442,14 @@ class PI05B200Engine(PolicyEngine):
         return images, img_masks, tokens, masks, noise
 
     def _warm(self) -> None:
-        self.model.sample_actions(*self._dummy_inputs(self.batch_size))
+        """One chunk on dummy inputs before serving.  Also the place where a checkpoint whose vision tower
+        does not fit the fp16 range shows: sublayer outputs beyond 65504 turn the image features, and with
+        them the chunk, into inf / NaN; the TF32 and bf16 towers have no such limit."""
+        out = self.model.sample_actions(*self._dummy_inputs(self.batch_size))
         torch.cuda.synchronize(self.device)
+        if self.model.vision_dtype == torch.float16 and not bool(torch.isfinite(out).all()):
+            raise RuntimeError("pi05_b200: the warm-up chunk is not finite with the fp16 vision tower; "
+                               "construct the engine with vision_precision='tf32'")
 
     def _capture(self) -> None:
         """Whole ``sample_actions`` (prefix + every denoise step) as one CUDA graph with static
